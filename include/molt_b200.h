@@ -1,0 +1,178 @@
+/*
+ * molt_b200 -- C ABI of the B200 (sm_100a) NF4 + LoRA hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as uintptr_t).  The library never allocates or frees
+ * device memory and keeps no pointer after a call returns.  It never
+ * synchronises the stream or the device (molt_read_status excepted).  All
+ * tensors are row-major and contiguous.  The calling thread's current CUDA
+ * device must be the device that owns the pointers.
+ *
+ * Return value of every int function: 0 = ok, otherwise one of MOLT_E_*; the
+ * message of the last failure on the calling thread is molt_last_error().
+ *
+ * Paths cited as "reference" are files of the MOLT project (src/molt_stream/...).
+ */
+#ifndef MOLT_B200_H_
+#define MOLT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOLT_OK 0
+#define MOLT_E_VALUE 1      /* shape / argument mismatch   -> ValueError      (reference: nf4_backward.py:181-182) */
+#define MOLT_E_CAPABILITY 2 /* unsupported dtype/rank/etc. -> CapabilityError (reference: core/errors.py:5-6)     */
+#define MOLT_E_RUNTIME 3    /* CUDA launch / driver failure -> RuntimeError                                         */
+#define MOLT_E_TIMEOUT 4    /* a bounded device-side wait expired (see molt_read_status)                            */
+
+#define MOLT_ABSMAX_F32 0     /* absmax is float[blocks]                      (reference: streaming/nf4.py:58)      */
+#define MOLT_ABSMAX_NESTED 1  /* absmax is uint8[blocks] + absmax2/code2/offset (reference: nf4_backward.py:154-160) */
+
+#define MOLT_NIBBLE_LOW_FIRST 0  /* element 2i in bits 0-3 (reference: streaming/nf4.py:62)        */
+#define MOLT_NIBBLE_HIGH_FIRST 1 /* element 2i in bits 4-7 (reference: nf4_backward.py:97-98)     */
+
+#define MOLT_DTYPE_BF16 0
+#define MOLT_DTYPE_F32 1
+
+/* kernel selection for the linear ops; AUTO picks GEMV for M <= 16, the tcgen05 kernels for
+ * aligned shapes (K % 64 == 0, N % 64 == 0, blocksize 64, rank <= 64) and the general kernels otherwise. */
+#define MOLT_PATH_AUTO 0
+#define MOLT_PATH_GENERAL 1
+#define MOLT_PATH_TCGEN05 2
+#define MOLT_PATH_GEMV 3
+
+/* operations for molt_workspace_bytes */
+#define MOLT_OP_LORA_FWD 1
+#define MOLT_OP_LORA_BWD 2
+#define MOLT_OP_DX 3
+#define MOLT_OP_MLP_FWD 4
+#define MOLT_OP_MLP_BWD 5
+
+/* A frozen NF4 weight W[n, k] as it lies in device memory.
+ * Replaces the (packed, scales, shape, block_size) payload of reference streaming/nf4.py:21-35 and the
+ * duck-typed bitsandbytes quant_state read at reference methods/nf4_backward.py:147-163. */
+typedef struct molt_nf4_desc {
+  const uint8_t* packed;  /* ceil(n*k / blocksize) * blocksize / 2 bytes, two codes per byte */
+  const void* absmax;     /* float[blocks] or uint8[blocks], see absmax_kind                  */
+  const float* absmax2;   /* nested only: float[ceil(blocks / block2)]                        */
+  const float* code2;     /* nested only: float[256] lookup table                             */
+  float offset;           /* nested only: added after code2[u8] * absmax2                     */
+  int32_t absmax_kind;    /* MOLT_ABSMAX_*                                                    */
+  int32_t block2;         /* nested only: absmax codes per absmax2 entry (256)                */
+  int32_t blocksize;      /* weight elements per absmax (64)                                  */
+  int32_t nibble_order;   /* MOLT_NIBBLE_*                                                    */
+  int32_t reserved;
+  int64_t n;              /* out_features (rows of W)                                         */
+  int64_t k;              /* in_features  (columns of W)                                      */
+  float codebook[16];     /* the 16 NF4 values (reference: streaming/nf4.py:10-18)            */
+} molt_nf4_desc;
+
+int molt_version(void);
+/* Message of the last failing call on this thread ("" if none). */
+const char* molt_last_error(void);
+
+/* Number of kernels this library has launched in this process (all threads, all devices). */
+uint64_t molt_launch_count(void);
+
+/* Device-side status word.  The tcgen05 kernels bound every wait; when one expires the kernel
+ * records a code here and returns.  Reads and clears it (synchronises the given stream). 0 = clean. */
+int molt_read_status(uintptr_t stream, int32_t* status_out);
+
+/* out[n, k] = codebook[code] * absmax, one fp32 multiply, cast last.
+ * Replaces NF4DevicePayload.dequantize (reference streaming/nf4.py:29-35) and
+ * bitsandbytes dequantize_4bit at reference methods/nf4_lora.py:98, nf4_layer_cache.py:51. */
+int molt_nf4_dequant(const molt_nf4_desc* w, void* out, int out_dtype, uintptr_t stream);
+
+/* out[blocks] = fp32 absmax (nested form resolved).  Replaces resolved_nf4_scales
+ * (reference methods/nf4_backward.py:145-164). */
+int molt_nf4_resolve_absmax(const molt_nf4_desc* w, float* out, uintptr_t stream);
+
+/* Scratch bytes the given op needs for these sizes (0 if none). */
+size_t molt_workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank);
+
+/* y[m, n] = x[m, k] . deq(W)^T + scaling * (x . A^T) . B^T      (x, y bf16; A[rank, k], B[n, rank] fp32)
+ * Replaces _ScheduledNF4LoRA.forward (reference methods/nf4_lora.py:23-69), _nf4_lora_forward
+ * (reference methods/gated_replay.py:211-224) and _FrozenNF4LoRA.forward (reference streaming/engine.py:21-31).
+ * t_out (optional, may be NULL): bf16 [m, 64] receives x . A^T zero-padded to 64 columns, for reuse in backward. */
+int molt_nf4_lora_fwd(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
+                      float scaling, int rank, void* y, int64_t m, void* t_out, void* workspace,
+                      size_t workspace_bytes, int path, uintptr_t stream);
+
+/* dx[m, k] = dy . deq(W) + (scaling * dy . B) . A ; da[rank, k] = (scaling * dy . B)^T . x ;
+ * db[n, rank] = scaling * dy^T . (x . A^T).   dx bf16 (may be NULL to skip), da/db fp32 (may both be NULL).
+ * Replaces _ScheduledNF4LoRA.backward (reference methods/nf4_lora.py:71-113), _nf4_lora_backward
+ * (reference methods/gated_replay.py:227-253) and _FrozenNF4LoRA.backward (reference streaming/engine.py:33-48).
+ * t_in (optional): the t_out of the matching forward; recomputed from x when NULL.
+ * accumulate != 0 adds into da/db instead of overwriting them. */
+int molt_nf4_lora_bwd(const molt_nf4_desc* w, const void* x, const void* dy, const float* lora_a,
+                      const float* lora_b, float scaling, int rank, void* dx, float* da, float* db,
+                      int64_t m, const void* t_in, int accumulate, void* workspace, size_t workspace_bytes,
+                      int path, uintptr_t stream);
+
+/* dx[m, k] = dy[m, n] . deq(W) (+ scaling * lora_grad[m, rank] . A[rank, k] when lora_grad != NULL).
+ * Replaces packed_nf4_backward_input and packed_nf4_lora_backward_input
+ * (reference methods/nf4_backward.py:167-284).  lora_a_dtype: MOLT_DTYPE_BF16 or MOLT_DTYPE_F32. */
+int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* lora_grad, const void* lora_a,
+                int lora_a_dtype, float scaling, int rank, void* dx, int64_t m, void* workspace,
+                size_t workspace_bytes, int path, uintptr_t stream);
+
+/* Small-token forward (m <= 16): streams the packed weight once.  Same contract as molt_nf4_lora_fwd.
+ * Replaces the bitsandbytes GEMV that bnb.matmul_4bit dispatches for few tokens (reference methods/nf4_lora.py:43-47). */
+int molt_nf4_gemv(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
+                  float scaling, int rank, void* y, int64_t m, void* workspace, size_t workspace_bytes,
+                  uintptr_t stream);
+
+/* h = silu(g) * u, fp32 internal, one rounding.  Replaces _silu_mul_forward
+ * (reference kernels/gated_activation.py:29-36).  dtype: MOLT_DTYPE_*. */
+int molt_swiglu_fwd(const void* gate, const void* up, void* out, int64_t count, int dtype, uintptr_t stream);
+
+/* dgate = dh * u * sig(g) * (1 + g * (1 - sig(g))), dup = dh * silu(g); optionally also re-emits
+ * h = silu(g) * u (h_out != NULL) for the down-projection backward of the replay schedule.
+ * Replaces _silu_mul_backward (reference kernels/gated_activation.py:38-51) and the eager replay
+ * arithmetic at reference methods/gated_replay.py:373-387. */
+int molt_swiglu_bwd(const void* grad_out, const void* gate, const void* up, void* dgate, void* dup,
+                    void* h_out, int64_t count, int dtype, uintptr_t stream);
+
+/* out = bf16(x * rsqrt(mean(x^2) + eps) * (weight + weight_offset)); x bf16 [rows, width], weight fp32 or bf16.
+ * Replaces _RMSNormReplayRecipe.materialize (reference methods/gated_replay.py:22-29). */
+int molt_rmsnorm_fwd(const void* x, const void* weight, int weight_dtype, float eps, float weight_offset,
+                     void* out, int64_t rows, int64_t width, uintptr_t stream);
+
+/* Gated MLP block: gate = P_g(x), up = P_u(x), y = P_d(silu(gate) * up).
+ * gate_out [m, inter] is always written (it is what the replay schedule saves); up_out may be NULL when the
+ * caller re-materialises `up` in backward.  Replaces _ResidualRecipeGatedNF4LoRA.forward
+ * (reference methods/gated_replay.py:53-133) / _AsymmetricGatedNF4LoRA.forward (:266-339). */
+typedef struct molt_lora_proj {
+  const molt_nf4_desc* w;
+  const float* lora_a;  /* [rank, k] */
+  const float* lora_b;  /* [n, rank] */
+  float scaling;
+  int32_t rank;
+} molt_lora_proj;
+
+/* Scratch bytes of molt_mlp_fwd (op = MOLT_OP_MLP_FWD) / molt_mlp_bwd (op = MOLT_OP_MLP_BWD) for m tokens;
+ * up_given != 0 when the caller passes up_out / up_saved. */
+size_t molt_mlp_workspace_bytes(int op, const molt_lora_proj* gate, const molt_lora_proj* up,
+                                const molt_lora_proj* down, int64_t m, int up_given);
+
+int molt_mlp_fwd(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
+                 const void* x, void* gate_out, void* up_out, void* y, int64_t m, void* workspace,
+                 size_t workspace_bytes, uintptr_t stream);
+
+/* Backward of the block with `up` replayed when up_saved == NULL.  Writes dx [m, hidden] and the six
+ * adapter gradients grads[6] = {gate_a, gate_b, up_a, up_b, down_a, down_b} (fp32).
+ * Replaces _ResidualRecipeGatedNF4LoRA.backward (reference methods/gated_replay.py:135-208) and
+ * _AsymmetricGatedNF4LoRA.backward (:341-407). */
+int molt_mlp_bwd(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
+                 const void* x, const void* gate_saved, const void* up_saved, const void* dy, void* dx,
+                 float* const grads[6], int accumulate, int64_t m, void* workspace, size_t workspace_bytes,
+                 uintptr_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOLT_B200_H_ */

@@ -1,0 +1,552 @@
+// extern "C" entry points of libmolt_b200: argument validation, kernel-path selection and the
+// sequencing of the kernels that make up one linear / MLP-block forward or backward.
+#include <string.h>
+
+#include "internal.h"
+
+namespace molt {
+
+// ---- error channel ---------------------------------------------------------------------------------
+static thread_local char g_error[512] = "";
+char* error_buffer() { return g_error; }
+
+int fail(int code, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+  return code;
+}
+
+static unsigned long long g_launches = 0;
+void count_launch() { __atomic_fetch_add(&g_launches, 1ULL, __ATOMIC_RELAXED); }
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0) count = 148;
+    cached[dev] = count;
+  }
+  return cached[dev];
+}
+
+// One status word per device image of the library; kernels with bounded waits report here.
+__device__ int32_t g_device_status = 0;
+
+int32_t* device_status_word() {
+  static thread_local int32_t* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+    cached[dev] = reinterpret_cast<int32_t*>(p);
+  }
+  return cached[dev];
+}
+
+int check_desc(const molt_nf4_desc* w, int64_t* blocks) {
+  MOLT_REQUIRE(w != nullptr, MOLT_E_VALUE, "weight descriptor is NULL");
+  MOLT_REQUIRE(w->packed != nullptr && w->absmax != nullptr, MOLT_E_VALUE, "weight descriptor holds a NULL pointer");
+  MOLT_REQUIRE(w->n > 0 && w->k > 0, MOLT_E_VALUE, "weight shape must be positive, got [%lld, %lld]",
+               (long long)w->n, (long long)w->k);
+  MOLT_REQUIRE(w->blocksize >= 16 && w->blocksize % 2 == 0, MOLT_E_VALUE, "invalid NF4 block size %d", w->blocksize);
+  MOLT_REQUIRE(w->nibble_order == MOLT_NIBBLE_LOW_FIRST || w->nibble_order == MOLT_NIBBLE_HIGH_FIRST, MOLT_E_VALUE,
+               "invalid nibble order %d", w->nibble_order);
+  MOLT_REQUIRE(w->absmax_kind == MOLT_ABSMAX_F32 || w->absmax_kind == MOLT_ABSMAX_NESTED, MOLT_E_CAPABILITY,
+               "unsupported absmax kind %d", w->absmax_kind);
+  if (w->absmax_kind == MOLT_ABSMAX_NESTED)
+    MOLT_REQUIRE(w->absmax2 != nullptr && w->code2 != nullptr && w->block2 > 0, MOLT_E_VALUE,
+                 "nested absmax needs absmax2, code2 and block2");
+  const int64_t elements = w->n * w->k;
+  *blocks = (elements + w->blocksize - 1) / w->blocksize;
+  return MOLT_OK;
+}
+
+// ---- workspace carving -----------------------------------------------------------------------------
+struct Arena {
+  unsigned char* base;
+  size_t size;
+  size_t used;
+  bool dry;
+  Arena(void* p, size_t bytes, bool sizing_only = false)
+      : base(reinterpret_cast<unsigned char*>(p)), size(bytes), used(0), dry(sizing_only) {}
+  void* take(size_t bytes) {
+    const size_t start = (used + 255) & ~size_t(255);
+    used = start + bytes;
+    if (dry) return reinterpret_cast<void*>(uintptr_t(256));  // non-NULL placeholder while sizing
+    return base + start;
+  }
+  bool fits() const { return dry || (used <= size && (used == 0 || base != nullptr)); }
+};
+
+static int padded_rank(int rank) { return (rank + 15) / 16 * 16; }
+
+__global__ void add_bf16_kernel(const uint4* a, const uint4* b, uint4* out, long long vectors) {
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < vectors;
+       v += (long long)gridDim.x * blockDim.x) {
+    const uint4 x = a[v], y = b[v];
+    const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      r[i] = pack_bf16x2(bf16_lo(xs[i]) + bf16_lo(ys[i]), bf16_hi(xs[i]) + bf16_hi(ys[i]));
+    out[v] = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+int add_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, long long count, cudaStream_t s) {
+  if (count % 8 != 0) return fail(MOLT_E_VALUE, "add_bf16: count must be a multiple of 8");
+  const long long vectors = count / 8;
+  if (vectors == 0) return MOLT_OK;
+  long long blocks = (vectors + 255) / 256;
+  const long long cap = (long long)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  add_bf16_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint4*)a, (const uint4*)b, (uint4*)out, vectors);
+  return launch_status("add_bf16_kernel");
+}
+
+static bool aligned_case(const molt_nf4_desc* w, int rank) {
+  return w->blocksize == 64 && w->k % 64 == 0 && w->n % 64 == 0 && rank >= 1 && rank <= 64;
+}
+
+static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m, bool forward, int* chosen) {
+  const bool aligned = aligned_case(w, rank);
+  if (requested == MOLT_PATH_AUTO) {
+    if (!aligned) *chosen = MOLT_PATH_GENERAL;
+    else if (forward && m <= 16) *chosen = MOLT_PATH_GEMV;
+    else *chosen = MOLT_PATH_TCGEN05;
+    return MOLT_OK;
+  }
+  MOLT_REQUIRE(requested == MOLT_PATH_GENERAL || requested == MOLT_PATH_TCGEN05 || requested == MOLT_PATH_GEMV,
+               MOLT_E_VALUE, "unknown kernel path %d", requested);
+  if (requested != MOLT_PATH_GENERAL)
+    MOLT_REQUIRE(aligned, MOLT_E_CAPABILITY,
+                 "the tcgen05 and GEMV kernels need blocksize 64, K %% 64 == 0, N %% 64 == 0 and rank <= 64 "
+                 "(got N=%lld K=%lld blocksize=%d rank=%d)",
+                 (long long)w->n, (long long)w->k, w->blocksize, rank);
+  if (requested == MOLT_PATH_GEMV)
+    MOLT_REQUIRE(forward && m <= 16, MOLT_E_CAPABILITY, "the GEMV kernel handles forward with at most 16 tokens");
+  *chosen = requested;
+  return MOLT_OK;
+}
+
+// fp32 absmax for the tcgen05 kernels: the descriptor's own array, or the nested form resolved into the arena.
+static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s, const float** out) {
+  if (w->absmax_kind == MOLT_ABSMAX_F32) {
+    *out = reinterpret_cast<const float*>(w->absmax);
+    return MOLT_OK;
+  }
+  const int64_t blocks = (w->n * w->k + w->blocksize - 1) / w->blocksize;
+  float* buf = reinterpret_cast<float*>(arena.take((size_t)blocks * sizeof(float)));
+  *out = buf;
+  if (arena.dry) return MOLT_OK;
+  MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "workspace too small");
+  return molt_nf4_resolve_absmax(w, buf, reinterpret_cast<uintptr_t>(s));
+}
+
+// ---- forward ---------------------------------------------------------------------------------------
+static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
+                         float scaling, int rank, void* y, int64_t m, void* t_out, Arena& arena, int path,
+                         cudaStream_t s) {
+  const WeightView view = make_view(w);
+  const int rp = padded_rank(rank);
+  auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto* yb = reinterpret_cast<__nv_bfloat16*>(y);
+  if (path == MOLT_PATH_GEMV) {
+    void* ws = arena.take(gemv_workspace_bytes(w->n, w->k));
+    if (arena.dry) return MOLT_OK;
+    MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
+    if (t_out != nullptr) {  // keep the contract of t_out also on this path
+      if (int rc = general_rowsum(true, xb, lora_a, 1.0f, m, w->k, rank, reinterpret_cast<__nv_bfloat16*>(t_out), 64, s))
+        return rc;
+    }
+    return gemv_forward(view, xb, lora_a, lora_b, scaling, rank, yb, (int)m, ws, gemv_workspace_bytes(w->n, w->k), s);
+  }
+  __nv_bfloat16* t = t_out != nullptr ? reinterpret_cast<__nv_bfloat16*>(t_out)
+                                      : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));
+  if (path == MOLT_PATH_GENERAL) {
+    if (arena.dry) return MOLT_OK;
+    MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
+    if (int rc = general_rowsum(true, xb, lora_a, 1.0f, m, w->k, rank, t, 64, s)) return rc;
+    return general_forward(view, xb, t, 64, lora_b, scaling, rank, yb, m, s);
+  }
+  // tcgen05 path
+  auto* a16 = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
+  auto* bs = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)w->n * 64 * 2));
+  const float* absmax = nullptr;
+  if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
+  if (arena.dry) return MOLT_OK;
+  MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
+  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, bs, nullptr, s)) return rc;
+  if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t, s)) return rc;
+  return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, s);
+}
+
+// ---- backward --------------------------------------------------------------------------------------
+static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, const float* lora_a,
+                         const float* lora_b, float scaling, int rank, void* dx, float* da, float* db, int64_t m,
+                         const void* t_in, int accumulate, Arena& arena, int path, cudaStream_t s) {
+  const WeightView view = make_view(w);
+  const int rp = padded_rank(rank);
+  auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto* gb = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
+  const bool want_grads = da != nullptr && db != nullptr;
+  auto* u = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));
+  const __nv_bfloat16* t = reinterpret_cast<const __nv_bfloat16*>(t_in);
+  __nv_bfloat16* t_own = nullptr;
+  if (want_grads && t == nullptr) {
+    t_own = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));
+    t = t_own;
+  }
+  if (path == MOLT_PATH_GENERAL) {
+    if (arena.dry) return MOLT_OK;
+    MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace too small");
+    // U = bf16(s * dY . B)
+    if (int rc = general_rowsum(false, gb, lora_b, scaling, m, w->n, rank, u, 64, s)) return rc;
+    if (dxb != nullptr)
+      if (int rc = general_backward_input(view, gb, u, 64, lora_a, MOLT_DTYPE_F32, 1.0f, rank, dxb, m, s)) return rc;
+    if (want_grads) {
+      if (t_own != nullptr)
+        if (int rc = general_rowsum(true, xb, lora_a, 1.0f, m, w->k, rank, t_own, 64, s)) return rc;
+      if (int rc = general_colsum(true, u, 64, xb, 1.0f, m, w->k, rank, da, accumulate, s)) return rc;
+      if (int rc = general_colsum(false, t, 64, gb, scaling, m, w->n, rank, db, accumulate, s)) return rc;
+    }
+    return MOLT_OK;
+  }
+  auto* a16 = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
+  auto* bt = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->n * 2));
+  float* partial = nullptr;
+  if (want_grads) {
+    size_t pa = colsum_partial_bytes(m, w->k, rp), pb = colsum_partial_bytes(m, w->n, rp);
+    partial = reinterpret_cast<float*>(arena.take(pa > pb ? pa : pb));
+  }
+  const float* absmax = nullptr;
+  if (dxb != nullptr)
+    if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
+  if (arena.dry) return MOLT_OK;
+  MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace too small");
+  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, nullptr, bt, s)) return rc;
+  if (int rc = rowsum_mma(gb, bt, rp, m, w->n, u, s)) return rc;  // U = dY . (sB)
+  if (dxb != nullptr)
+    if (int rc = sm100_gemm(true, view, absmax, gb, u, a16, rp, dxb, m, s)) return rc;
+  if (want_grads) {
+    if (t_own != nullptr)
+      if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t_own, s)) return rc;
+    if (int rc = colsum_mma(false, u, xb, rp, rank, m, w->k, 1.0f, partial, da, accumulate, s)) return rc;
+    if (int rc = colsum_mma(true, t, gb, rp, rank, m, w->n, scaling, partial, db, accumulate, s)) return rc;
+  }
+  return MOLT_OK;
+}
+
+static int dx_impl(const molt_nf4_desc* w, const void* dy, const void* lora_grad, const void* lora_a,
+                   int lora_a_dtype, float scaling, int rank, void* dx, int64_t m, Arena& arena, int path,
+                   cudaStream_t s) {
+  const WeightView view = make_view(w);
+  auto* gb = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
+  // The caller's lora_grad is [m, rank] (unpadded); both kernel families read it with its own leading dimension
+  // on the general path.  The tcgen05 path needs the padded [m, 64] layout and a bf16 A scaled by `scaling`,
+  // which only exists for the fused linear backward; the standalone op therefore always runs the general kernels
+  // when a low-rank term is present and the tcgen05 kernel otherwise.
+  if (path == MOLT_PATH_TCGEN05 && lora_grad == nullptr) {
+    const float* absmax = nullptr;
+    if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
+    if (arena.dry) return MOLT_OK;
+    MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_dx: workspace too small");
+    return sm100_gemm(true, view, absmax, gb, nullptr, nullptr, 0, dxb, m, s);
+  }
+  if (arena.dry) return MOLT_OK;
+  return general_backward_input(view, gb, reinterpret_cast<const __nv_bfloat16*>(lora_grad), rank, lora_a,
+                                lora_a_dtype, scaling, rank, dxb, m, s);
+}
+
+}  // namespace molt
+
+using namespace molt;
+
+extern "C" int molt_version(void) { return 100; }
+extern "C" const char* molt_last_error(void) { return error_buffer(); }
+extern "C" uint64_t molt_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
+
+extern "C" int molt_read_status(uintptr_t stream, int32_t* status_out) {
+  MOLT_REQUIRE(status_out != nullptr, MOLT_E_VALUE, "molt_read_status: status_out is NULL");
+  int32_t* word = device_status_word();
+  MOLT_REQUIRE(word != nullptr, MOLT_E_RUNTIME, "molt_read_status: no device status word");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int32_t host = 0;
+  MOLT_CUDA(cudaMemcpyAsync(&host, word, sizeof(host), cudaMemcpyDeviceToHost, s));
+  MOLT_CUDA(cudaStreamSynchronize(s));
+  if (host != 0) MOLT_CUDA(cudaMemsetAsync(word, 0, sizeof(host), s));
+  *status_out = host;
+  return MOLT_OK;
+}
+
+static int check_linear_args(const char* who, const molt_nf4_desc* w, int rank, int64_t m, int64_t* blocks) {
+  if (int rc = check_desc(w, blocks)) return rc;
+  MOLT_REQUIRE(m >= 0, MOLT_E_VALUE, "%s: negative token count", who);
+  MOLT_REQUIRE(rank >= 1, MOLT_E_VALUE, "%s: LoRA rank must be positive", who);
+  MOLT_REQUIRE(rank <= 64, MOLT_E_CAPABILITY, "%s: LoRA rank %d exceeds the supported maximum of 64", who, rank);
+  return MOLT_OK;
+}
+
+extern "C" size_t molt_workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank) {
+  if (m < 0 || n <= 0 || k <= 0 || rank < 1 || rank > 64) return 0;
+  molt_nf4_desc fake;
+  memset(&fake, 0, sizeof(fake));
+  fake.n = n;
+  fake.k = k;
+  fake.blocksize = 64;
+  fake.absmax_kind = MOLT_ABSMAX_NESTED;  // upper bound: room for a resolved absmax copy
+  fake.packed = reinterpret_cast<const uint8_t*>(uintptr_t(256));
+  fake.absmax = fake.packed;
+  size_t best = 0;
+  const int paths[3] = {MOLT_PATH_GENERAL, MOLT_PATH_TCGEN05, MOLT_PATH_GEMV};
+  for (int path : paths) {
+    if (path != MOLT_PATH_GENERAL && !(k % 64 == 0 && n % 64 == 0)) continue;
+    if (path == MOLT_PATH_GEMV && !(op == MOLT_OP_LORA_FWD && m <= 16)) continue;
+    Arena arena(nullptr, 0, true);
+    if (op == MOLT_OP_LORA_FWD) lora_fwd_impl(&fake, nullptr, nullptr, nullptr, 1.f, rank, nullptr, m, nullptr, arena, path, 0);
+    else if (op == MOLT_OP_LORA_BWD)
+      lora_bwd_impl(&fake, nullptr, nullptr, nullptr, nullptr, 1.f, rank, reinterpret_cast<void*>(uintptr_t(256)),
+                    reinterpret_cast<float*>(uintptr_t(256)), reinterpret_cast<float*>(uintptr_t(256)), m, nullptr, 0,
+                    arena, path, 0);
+    else if (op == MOLT_OP_DX) dx_impl(&fake, nullptr, nullptr, nullptr, 0, 1.f, rank, nullptr, m, arena, path, 0);
+    else return 0;
+    if (arena.used > best) best = arena.used;
+  }
+  return best + 256;
+}
+
+extern "C" int molt_nf4_lora_fwd(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
+                                 float scaling, int rank, void* y, int64_t m, void* t_out, void* workspace,
+                                 size_t workspace_bytes, int path, uintptr_t stream) {
+  int64_t blocks = 0;
+  if (int rc = check_linear_args("molt_nf4_lora_fwd", w, rank, m, &blocks)) return rc;
+  MOLT_REQUIRE(x && lora_a && lora_b && y, MOLT_E_VALUE, "molt_nf4_lora_fwd: NULL tensor pointer");
+  MOLT_REQUIRE(aligned16(x) && aligned16(y) && aligned16(w->packed) && (t_out == nullptr || aligned16(t_out)),
+               MOLT_E_VALUE, "molt_nf4_lora_fwd: tensors must be 16-byte aligned");
+  if (m == 0) return MOLT_OK;
+  int chosen = 0;
+  if (int rc = pick_path(path, w, rank, m, true, &chosen)) return rc;
+  MOLT_REQUIRE(workspace != nullptr, MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace is NULL");
+  Arena arena(workspace, workspace_bytes);
+  return lora_fwd_impl(w, x, lora_a, lora_b, scaling, rank, y, m, t_out, arena, chosen,
+                       reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int molt_nf4_gemv(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
+                             float scaling, int rank, void* y, int64_t m, void* workspace, size_t workspace_bytes,
+                             uintptr_t stream) {
+  return molt_nf4_lora_fwd(w, x, lora_a, lora_b, scaling, rank, y, m, nullptr, workspace, workspace_bytes,
+                           MOLT_PATH_GEMV, stream);
+}
+
+extern "C" int molt_nf4_lora_bwd(const molt_nf4_desc* w, const void* x, const void* dy, const float* lora_a,
+                                 const float* lora_b, float scaling, int rank, void* dx, float* da, float* db,
+                                 int64_t m, const void* t_in, int accumulate, void* workspace, size_t workspace_bytes,
+                                 int path, uintptr_t stream) {
+  int64_t blocks = 0;
+  if (int rc = check_linear_args("molt_nf4_lora_bwd", w, rank, m, &blocks)) return rc;
+  MOLT_REQUIRE(dy && lora_a && lora_b, MOLT_E_VALUE, "molt_nf4_lora_bwd: NULL tensor pointer");
+  MOLT_REQUIRE((da == nullptr) == (db == nullptr), MOLT_E_VALUE,
+               "molt_nf4_lora_bwd: da and db must both be given or both be NULL");
+  MOLT_REQUIRE(da == nullptr || x != nullptr, MOLT_E_VALUE, "molt_nf4_lora_bwd: adapter gradients need x");
+  MOLT_REQUIRE(aligned16(dy) && (x == nullptr || aligned16(x)) && (dx == nullptr || aligned16(dx)) &&
+                   aligned16(w->packed) && (t_in == nullptr || aligned16(t_in)),
+               MOLT_E_VALUE, "molt_nf4_lora_bwd: tensors must be 16-byte aligned");
+  if (m == 0) {
+    if (da != nullptr && !accumulate) {
+      cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+      MOLT_CUDA(cudaMemsetAsync(da, 0, (size_t)rank * w->k * sizeof(float), s));
+      MOLT_CUDA(cudaMemsetAsync(db, 0, (size_t)rank * w->n * sizeof(float), s));
+    }
+    return MOLT_OK;
+  }
+  int chosen = 0;
+  if (int rc = pick_path(path, w, rank, m, false, &chosen)) return rc;
+  MOLT_REQUIRE(workspace != nullptr, MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace is NULL");
+  Arena arena(workspace, workspace_bytes);
+  return lora_bwd_impl(w, x, dy, lora_a, lora_b, scaling, rank, dx, da, db, m, t_in, accumulate, arena, chosen,
+                       reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* lora_grad, const void* lora_a,
+                           int lora_a_dtype, float scaling, int rank, void* dx, int64_t m, void* workspace,
+                           size_t workspace_bytes, int path, uintptr_t stream) {
+  int64_t blocks = 0;
+  if (int rc = check_desc(w, &blocks)) return rc;
+  MOLT_REQUIRE(m >= 0, MOLT_E_VALUE, "molt_nf4_dx: negative token count");
+  MOLT_REQUIRE(dy && dx, MOLT_E_VALUE, "molt_nf4_dx: NULL tensor pointer");
+  MOLT_REQUIRE(aligned16(dy) && aligned16(dx) && aligned16(w->packed), MOLT_E_VALUE,
+               "molt_nf4_dx: tensors must be 16-byte aligned");
+  if (lora_grad != nullptr) {
+    MOLT_REQUIRE(lora_a != nullptr, MOLT_E_VALUE, "molt_nf4_dx: lora_grad given without lora_a");
+    MOLT_REQUIRE(rank >= 1, MOLT_E_VALUE, "molt_nf4_dx: LoRA rank must be positive");
+    MOLT_REQUIRE(lora_a_dtype == MOLT_DTYPE_BF16 || lora_a_dtype == MOLT_DTYPE_F32, MOLT_E_CAPABILITY,
+                 "molt_nf4_dx: LoRA A must be bf16 or fp32");
+  }
+  if (m == 0) return MOLT_OK;
+  int chosen = 0;
+  const int rank_for_path = lora_grad != nullptr ? rank : 1;
+  if (path == MOLT_PATH_AUTO) {
+    chosen = (aligned_case(w, rank_for_path <= 64 ? rank_for_path : 1) && lora_grad == nullptr) ? MOLT_PATH_TCGEN05
+                                                                                               : MOLT_PATH_GENERAL;
+  } else {
+    if (int rc = pick_path(path, w, rank_for_path, m, false, &chosen)) return rc;
+  }
+  Arena arena(workspace, workspace_bytes);
+  return dx_impl(w, dy, lora_grad, lora_a, lora_a_dtype, scaling, rank, dx, m, arena, chosen,
+                 reinterpret_cast<cudaStream_t>(stream));
+}
+
+// ---- gated MLP block -------------------------------------------------------------------------------
+static int check_proj(const char* who, const molt_lora_proj* p) {
+  MOLT_REQUIRE(p != nullptr && p->w != nullptr && p->lora_a != nullptr && p->lora_b != nullptr, MOLT_E_VALUE,
+               "%s: NULL projection", who);
+  int64_t blocks = 0;
+  return check_linear_args(who, p->w, p->rank, 0, &blocks);
+}
+
+static int check_block(const char* who, const molt_lora_proj* gate, const molt_lora_proj* up,
+                       const molt_lora_proj* down) {
+  if (int rc = check_proj(who, gate)) return rc;
+  if (int rc = check_proj(who, up)) return rc;
+  if (int rc = check_proj(who, down)) return rc;
+  MOLT_REQUIRE(gate->w->n == up->w->n && gate->w->k == up->w->k, MOLT_E_VALUE,
+               "%s: gate and up projections must have the same shape", who);
+  MOLT_REQUIRE(down->w->k == gate->w->n && down->w->n == gate->w->k, MOLT_E_VALUE,
+               "%s: down projection must map the intermediate width back to the hidden width", who);
+  return MOLT_OK;
+}
+
+static int mlp_fwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
+                        const void* x, void* gate_out, void* up_out, void* y, int64_t m, Arena& arena,
+                        cudaStream_t s) {
+  const int64_t inter = gate->w->n;
+  void* up_buf = up_out != nullptr ? up_out : arena.take((size_t)m * inter * 2);
+  void* hidden = arena.take((size_t)m * inter * 2);
+  const size_t mark = arena.used;
+  size_t high = mark;
+  const molt_lora_proj* projs[3] = {gate, up, down};
+  const void* ins[3] = {x, x, hidden};
+  void* outs[3] = {gate_out, up_buf, y};
+  for (int i = 0; i < 3; ++i) {
+    arena.used = mark;  // the three linears run one after another on the stream and reuse the same scratch
+    int chosen = 0;
+    if (int rc = pick_path(MOLT_PATH_AUTO, projs[i]->w, projs[i]->rank, m, true, &chosen)) return rc;
+    if (i == 2 && !arena.dry)
+      if (int rc = molt_swiglu_fwd(gate_out, up_buf, hidden, m * inter, MOLT_DTYPE_BF16, reinterpret_cast<uintptr_t>(s)))
+        return rc;
+    if (int rc = lora_fwd_impl(projs[i]->w, ins[i], projs[i]->lora_a, projs[i]->lora_b, projs[i]->scaling,
+                               projs[i]->rank, outs[i], m, nullptr, arena, chosen, s))
+      return rc;
+    if (arena.used > high) high = arena.used;
+  }
+  arena.used = high;
+  return MOLT_OK;
+}
+
+static int mlp_bwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
+                        const void* x, const void* gate_saved, const void* up_saved, const void* dy, void* dx,
+                        float* const grads[6], int accumulate, int64_t m, Arena& arena, cudaStream_t s) {
+  const int64_t inter = gate->w->n, hidden_width = gate->w->k;
+  const size_t act = (size_t)m * inter * 2;
+  void* up_buf = up_saved != nullptr ? nullptr : arena.take(act);   // replayed `up`, later reused for dup
+  void* dup_buf = up_saved != nullptr ? arena.take(act) : up_buf;
+  void* hidden = arena.take(act);
+  void* dh = arena.take(act);                                       // dh, overwritten in place by dgate
+  void* dx_up = arena.take((size_t)m * hidden_width * 2);
+  const size_t mark = arena.used;
+  size_t high = mark;
+  const uintptr_t st = reinterpret_cast<uintptr_t>(s);
+  int chosen = 0;
+  // 1. replay the up projection (reference gated_replay.py:360-368)
+  const void* up_val = up_saved;
+  if (up_saved == nullptr) {
+    if (int rc = pick_path(MOLT_PATH_AUTO, up->w, up->rank, m, true, &chosen)) return rc;
+    if (int rc = lora_fwd_impl(up->w, x, up->lora_a, up->lora_b, up->scaling, up->rank, up_buf, m, nullptr, arena,
+                               chosen, s))
+      return rc;
+    up_val = up_buf;
+    if (arena.used > high) high = arena.used;
+  }
+  // 2. rebuild h = silu(gate) * up (:373-375)
+  if (!arena.dry)
+    if (int rc = molt_swiglu_fwd(gate_saved, up_val, hidden, m * inter, MOLT_DTYPE_BF16, st)) return rc;
+  // 3. down projection backward (:376-384)
+  arena.used = mark;
+  if (int rc = pick_path(MOLT_PATH_AUTO, down->w, down->rank, m, false, &chosen)) return rc;
+  if (int rc = lora_bwd_impl(down->w, hidden, dy, down->lora_a, down->lora_b, down->scaling, down->rank, dh, grads[4],
+                             grads[5], m, nullptr, accumulate, arena, chosen, s))
+    return rc;
+  if (arena.used > high) high = arena.used;
+  // 4. dup = dh * silu(gate), dgate = silu'(gate) * dh * up (:385-387); dgate overwrites dh
+  if (!arena.dry)
+    if (int rc = molt_swiglu_bwd(dh, gate_saved, up_val, dh, dup_buf, nullptr, m * inter, MOLT_DTYPE_BF16, st)) return rc;
+  // 5. gate and up projection backwards, dx = dx_gate + dx_up (:155-186)
+  arena.used = mark;
+  if (int rc = pick_path(MOLT_PATH_AUTO, gate->w, gate->rank, m, false, &chosen)) return rc;
+  if (int rc = lora_bwd_impl(gate->w, x, dh, gate->lora_a, gate->lora_b, gate->scaling, gate->rank, dx, grads[0],
+                             grads[1], m, nullptr, accumulate, arena, chosen, s))
+    return rc;
+  if (arena.used > high) high = arena.used;
+  arena.used = mark;
+  if (int rc = pick_path(MOLT_PATH_AUTO, up->w, up->rank, m, false, &chosen)) return rc;
+  if (int rc = lora_bwd_impl(up->w, x, dup_buf, up->lora_a, up->lora_b, up->scaling, up->rank, dx_up, grads[2],
+                             grads[3], m, nullptr, accumulate, arena, chosen, s))
+    return rc;
+  if (arena.used > high) high = arena.used;
+  arena.used = high;
+  if (arena.dry) return MOLT_OK;
+  return add_bf16(reinterpret_cast<const __nv_bfloat16*>(dx), reinterpret_cast<const __nv_bfloat16*>(dx_up),
+                  reinterpret_cast<__nv_bfloat16*>(dx), m * hidden_width, s);
+}
+
+extern "C" size_t molt_mlp_workspace_bytes(int op, const molt_lora_proj* gate, const molt_lora_proj* up,
+                                           const molt_lora_proj* down, int64_t m, int up_given) {
+  if (check_block("molt_mlp_workspace_bytes", gate, up, down) != MOLT_OK || m < 0) return 0;
+  Arena arena(nullptr, 0, true);
+  void* fake = reinterpret_cast<void*>(uintptr_t(256));
+  float* fake_grads[6];
+  for (int i = 0; i < 6; ++i) fake_grads[i] = reinterpret_cast<float*>(fake);
+  int rc = MOLT_E_VALUE;
+  if (op == MOLT_OP_MLP_FWD) rc = mlp_fwd_impl(gate, up, down, fake, fake, up_given ? fake : nullptr, fake, m, arena, 0);
+  else if (op == MOLT_OP_MLP_BWD)
+    rc = mlp_bwd_impl(gate, up, down, fake, fake, up_given ? fake : nullptr, fake, fake, fake_grads, 0, m, arena, 0);
+  return rc == MOLT_OK ? arena.used + 256 : 0;
+}
+
+extern "C" int molt_mlp_fwd(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
+                            const void* x, void* gate_out, void* up_out, void* y, int64_t m, void* workspace,
+                            size_t workspace_bytes, uintptr_t stream) {
+  if (int rc = check_block("molt_mlp_fwd", gate, up, down)) return rc;
+  MOLT_REQUIRE(m >= 0, MOLT_E_VALUE, "molt_mlp_fwd: negative token count");
+  MOLT_REQUIRE(x && gate_out && y && workspace, MOLT_E_VALUE, "molt_mlp_fwd: NULL tensor pointer");
+  MOLT_REQUIRE(aligned16(x) && aligned16(gate_out) && aligned16(y) && (up_out == nullptr || aligned16(up_out)),
+               MOLT_E_VALUE, "molt_mlp_fwd: tensors must be 16-byte aligned");
+  if (m == 0) return MOLT_OK;
+  Arena arena(workspace, workspace_bytes);
+  return mlp_fwd_impl(gate, up, down, x, gate_out, up_out, y, m, arena, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int molt_mlp_bwd(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
+                            const void* x, const void* gate_saved, const void* up_saved, const void* dy, void* dx,
+                            float* const grads[6], int accumulate, int64_t m, void* workspace, size_t workspace_bytes,
+                            uintptr_t stream) {
+  if (int rc = check_block("molt_mlp_bwd", gate, up, down)) return rc;
+  MOLT_REQUIRE(m >= 0, MOLT_E_VALUE, "molt_mlp_bwd: negative token count");
+  MOLT_REQUIRE(x && gate_saved && dy && dx && grads && workspace, MOLT_E_VALUE, "molt_mlp_bwd: NULL tensor pointer");
+  for (int i = 0; i < 6; ++i) MOLT_REQUIRE(grads[i] != nullptr, MOLT_E_VALUE, "molt_mlp_bwd: NULL gradient pointer");
+  MOLT_REQUIRE(aligned16(x) && aligned16(gate_saved) && aligned16(dy) && aligned16(dx) &&
+                   (up_saved == nullptr || aligned16(up_saved)),
+               MOLT_E_VALUE, "molt_mlp_bwd: tensors must be 16-byte aligned");
+  if (m == 0) return MOLT_OK;
+  Arena arena(workspace, workspace_bytes);
+  return mlp_bwd_impl(gate, up, down, x, gate_saved, up_saved, dy, dx, grads, accumulate, m, arena,
+                      reinterpret_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,319 @@
+// HBM-bound kernels: NF4 dequantisation, absmax resolution, SwiGLU forward/backward, RMSNorm replay.
+// Each thread moves 16-byte vectors; grids are sized in multiples of the SM count.
+#include "common.cuh"
+
+namespace molt {
+
+// ------------------------------------------------------------------------------------------------
+// NF4 dequantisation.  One thread expands 16 packed bytes (32 codes).  Bit-exact contract:
+// value = fp32(codebook[code]) * fp32(absmax) with one IEEE multiply, then one round-to-nearest cast.
+// ------------------------------------------------------------------------------------------------
+template <typename OutT>
+__device__ __forceinline__ void store_pair(OutT* out, long long idx, float a, float b, long long elements);
+
+template <>
+__device__ __forceinline__ void store_pair<float>(float* out, long long idx, float a, float b, long long elements) {
+  if (idx < elements) out[idx] = a;
+  if (idx + 1 < elements) out[idx + 1] = b;
+}
+template <>
+__device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16* out, long long idx, float a, float b,
+                                                          long long elements) {
+  if (idx < elements) out[idx] = __float2bfloat16_rn(a);
+  if (idx + 1 < elements) out[idx + 1] = __float2bfloat16_rn(b);
+}
+
+template <typename OutT, bool ALIGNED>
+__global__ void __launch_bounds__(256) nf4_dequant_kernel(WeightView w, OutT* __restrict__ out, long long elements,
+                                                          long long packed_bytes) {
+  __shared__ float lut[16];
+  if (threadIdx.x < 16) lut[threadIdx.x] = w.codebook[threadIdx.x];
+  __syncthreads();
+  const int lo_shift = w.nibble_order == MOLT_NIBBLE_LOW_FIRST ? 0 : 4;
+  const int hi_shift = 4 - lo_shift;
+  const long long vectors = (packed_bytes + 15) / 16;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < vectors;
+       v += (long long)gridDim.x * blockDim.x) {
+    const long long byte0 = v * 16;
+    const long long elem0 = byte0 * 2;
+    if (ALIGNED) {
+      // 32 elements, all inside one absmax block (blocksize % 32 == 0) and inside the tensor.
+      uint4 raw = __ldcs(reinterpret_cast<const uint4*>(w.packed + byte0));
+      const float scale = load_absmax(w, elem0 / w.blocksize);
+      uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+      float vals[32];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          uint32_t byte = (words[i] >> (8 * b)) & 0xffu;
+          vals[i * 8 + b * 2] = __fmul_rn(lut[(byte >> lo_shift) & 15u], scale);
+          vals[i * 8 + b * 2 + 1] = __fmul_rn(lut[(byte >> hi_shift) & 15u], scale);
+        }
+      }
+      if (sizeof(OutT) == 2) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + elem0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          o.x = pack_bf16x2(vals[q * 8 + 0], vals[q * 8 + 1]);
+          o.y = pack_bf16x2(vals[q * 8 + 2], vals[q * 8 + 3]);
+          o.z = pack_bf16x2(vals[q * 8 + 4], vals[q * 8 + 5]);
+          o.w = pack_bf16x2(vals[q * 8 + 6], vals[q * 8 + 7]);
+          __stcs(dst + q, o);
+        }
+      } else {
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + elem0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          __stcs(dst + q, make_float4(vals[q * 4], vals[q * 4 + 1], vals[q * 4 + 2], vals[q * 4 + 3]));
+      }
+    } else {
+      for (int b = 0; b < 16; ++b) {
+        const long long byte_idx = byte0 + b;
+        if (byte_idx >= packed_bytes) break;
+        const long long e = byte_idx * 2;
+        if (e >= elements) break;
+        const uint32_t byte = w.packed[byte_idx];
+        const float s0 = load_absmax(w, e / w.blocksize);
+        const float s1 = (e + 1 < elements) ? load_absmax(w, (e + 1) / w.blocksize) : 0.f;
+        store_pair<OutT>(out, e, __fmul_rn(lut[(byte >> lo_shift) & 15u], s0),
+                         __fmul_rn(lut[(byte >> hi_shift) & 15u], s1), elements);
+      }
+    }
+  }
+}
+
+__global__ void resolve_absmax_kernel(WeightView w, float* __restrict__ out, long long blocks) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < blocks;
+       i += (long long)gridDim.x * blockDim.x)
+    out[i] = load_absmax(w, i);
+}
+
+// ------------------------------------------------------------------------------------------------
+// SwiGLU.  fp32 arithmetic from the stored dtype, a single rounding on store.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sigmoidf_(float g) { return 1.0f / (1.0f + expf(-g)); }
+
+template <bool WRITE_H>
+__global__ void __launch_bounds__(256) swiglu_bf16_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up,
+                                                          const uint4* __restrict__ grad, uint4* __restrict__ out_h,
+                                                          uint4* __restrict__ dgate, uint4* __restrict__ dup,
+                                                          long long vectors, bool backward) {
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < vectors;
+       v += (long long)gridDim.x * blockDim.x) {
+    const uint4 g4 = __ldcs(gate + v);
+    const uint4 u4 = __ldcs(up + v);
+    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+    const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
+    if (!backward) {
+      uint32_t hw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float g0 = bf16_lo(gw[i]), g1 = bf16_hi(gw[i]);
+        const float u0 = bf16_lo(uw[i]), u1 = bf16_hi(uw[i]);
+        hw[i] = pack_bf16x2(g0 * sigmoidf_(g0) * u0, g1 * sigmoidf_(g1) * u1);
+      }
+      __stcs(out_h + v, make_uint4(hw[0], hw[1], hw[2], hw[3]));
+    } else {
+      const uint4 d4 = __ldcs(grad + v);
+      const uint32_t dw[4] = {d4.x, d4.y, d4.z, d4.w};
+      uint32_t og[4], ou[4], oh[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float g[2] = {bf16_lo(gw[i]), bf16_hi(gw[i])};
+        float u[2] = {bf16_lo(uw[i]), bf16_hi(uw[i])};
+        float d[2] = {bf16_lo(dw[i]), bf16_hi(dw[i])};
+        float rg[2], ru[2], rh[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float sig = sigmoidf_(g[j]);
+          const float silu = g[j] * sig;
+          rg[j] = d[j] * u[j] * (sig * (1.0f + g[j] * (1.0f - sig)));
+          ru[j] = d[j] * silu;
+          rh[j] = silu * u[j];
+        }
+        og[i] = pack_bf16x2(rg[0], rg[1]);
+        ou[i] = pack_bf16x2(ru[0], ru[1]);
+        oh[i] = pack_bf16x2(rh[0], rh[1]);
+      }
+      __stcs(dgate + v, make_uint4(og[0], og[1], og[2], og[3]));
+      __stcs(dup + v, make_uint4(ou[0], ou[1], ou[2], ou[3]));
+      if (WRITE_H) __stcs(out_h + v, make_uint4(oh[0], oh[1], oh[2], oh[3]));
+    }
+  }
+}
+
+// Scalar kernel: fp32 tensors, and the unaligned head/tail of bf16 tensors.
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void swiglu_scalar_kernel(const T* __restrict__ gate, const T* __restrict__ up, const T* __restrict__ grad,
+                                     T* __restrict__ out_h, T* __restrict__ dgate, T* __restrict__ dup,
+                                     long long begin, long long count, bool backward) {
+  for (long long i = begin + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float g = to_f32<T>(gate[i]);
+    const float u = to_f32<T>(up[i]);
+    const float sig = sigmoidf_(g);
+    const float silu = g * sig;
+    if (!backward) {
+      out_h[i] = from_f32<T>(silu * u);
+    } else {
+      const float d = to_f32<T>(grad[i]);
+      dgate[i] = from_f32<T>(d * u * (sig * (1.0f + g * (1.0f - sig))));
+      dup[i] = from_f32<T>(d * silu);
+      if (out_h != nullptr) out_h[i] = from_f32<T>(silu * u);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm (norm-replay recipe): one warp per row, fp32 reduction, bf16 out.
+// ------------------------------------------------------------------------------------------------
+template <typename WT>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const WT* __restrict__ weight,
+                                                      float eps, float weight_offset, __nv_bfloat16* __restrict__ out,
+                                                      long long rows, long long width) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp; row < rows; row += warps) {
+    const __nv_bfloat16* src = x + row * width;
+    float sum = 0.f;
+    for (long long c = lane; c < width; c += 32) {
+      const float v = __bfloat162float(src[c]);
+      sum += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = rsqrtf(sum / (float)width + eps);
+    for (long long c = lane; c < width; c += 32) {
+      const float v = __bfloat162float(src[c]);
+      out[row * width + c] = __float2bfloat16_rn(v * inv * (to_f32<WT>(weight[c]) + weight_offset));
+    }
+  }
+}
+
+static int grid_for(long long work_items, int threads, int waves_cap = 8) {
+  long long blocks = (work_items + threads - 1) / threads;
+  long long cap = (long long)sm_count() * waves_cap;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+}  // namespace molt
+
+using namespace molt;
+
+extern "C" int molt_nf4_dequant(const molt_nf4_desc* w, void* out, int out_dtype, uintptr_t stream) {
+  int64_t blocks = 0;
+  if (int rc = check_desc(w, &blocks)) return rc;
+  MOLT_REQUIRE(out != nullptr, MOLT_E_VALUE, "molt_nf4_dequant: out is NULL");
+  MOLT_REQUIRE(out_dtype == MOLT_DTYPE_BF16 || out_dtype == MOLT_DTYPE_F32, MOLT_E_CAPABILITY,
+               "molt_nf4_dequant: output dtype must be bf16 or fp32");
+  const long long elements = w->n * w->k;
+  const long long packed_bytes = blocks * w->blocksize / 2;
+  const bool aligned = (w->blocksize % 32 == 0) && (elements % 32 == 0) && aligned16(w->packed) && aligned16(out);
+  WeightView view = make_view(w);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long vectors = (packed_bytes + 15) / 16;
+  const int grid = grid_for(vectors, 256, 16);
+  if (out_dtype == MOLT_DTYPE_BF16) {
+    auto* o = reinterpret_cast<__nv_bfloat16*>(out);
+    if (aligned) nf4_dequant_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(view, o, elements, packed_bytes);
+    else nf4_dequant_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(view, o, elements, packed_bytes);
+  } else {
+    auto* o = reinterpret_cast<float*>(out);
+    if (aligned) nf4_dequant_kernel<float, true><<<grid, 256, 0, s>>>(view, o, elements, packed_bytes);
+    else nf4_dequant_kernel<float, false><<<grid, 256, 0, s>>>(view, o, elements, packed_bytes);
+  }
+  return launch_status("nf4_dequant_kernel");
+}
+
+extern "C" int molt_nf4_resolve_absmax(const molt_nf4_desc* w, float* out, uintptr_t stream) {
+  int64_t blocks = 0;
+  if (int rc = check_desc(w, &blocks)) return rc;
+  MOLT_REQUIRE(out != nullptr, MOLT_E_VALUE, "molt_nf4_resolve_absmax: out is NULL");
+  resolve_absmax_kernel<<<grid_for(blocks, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_view(w), out,
+                                                                                                  blocks);
+  return launch_status("resolve_absmax_kernel");
+}
+
+static int swiglu_launch(const void* gate, const void* up, const void* grad, void* out_h, void* dgate, void* dup,
+                         int64_t count, int dtype, bool backward, uintptr_t stream) {
+  MOLT_REQUIRE(count >= 0, MOLT_E_VALUE, "swiglu: negative element count");
+  MOLT_REQUIRE(dtype == MOLT_DTYPE_BF16 || dtype == MOLT_DTYPE_F32, MOLT_E_CAPABILITY,
+               "swiglu: dtype must be bf16 or fp32");
+  MOLT_REQUIRE(gate && up && (backward ? (grad && dgate && dup) : out_h != nullptr), MOLT_E_VALUE,
+               "swiglu: NULL tensor pointer");
+  if (count == 0) return MOLT_OK;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == MOLT_DTYPE_F32) {
+    swiglu_scalar_kernel<float><<<grid_for(count, 256, 16), 256, 0, s>>>(
+        (const float*)gate, (const float*)up, (const float*)grad, (float*)out_h, (float*)dgate, (float*)dup, 0, count,
+        backward);
+    return launch_status("swiglu_scalar_kernel<float>");
+  }
+  const bool vec_ok = aligned16(gate) && aligned16(up) && (!backward || (aligned16(grad) && aligned16(dgate) &&
+                                                                         aligned16(dup))) &&
+                      (out_h == nullptr || aligned16(out_h));
+  long long vectors = vec_ok ? count / 8 : 0;
+  if (vectors > 0) {
+    const int grid = grid_for(vectors, 256, 16);
+    if (backward && out_h != nullptr)
+      swiglu_bf16_kernel<true><<<grid, 256, 0, s>>>((const uint4*)gate, (const uint4*)up, (const uint4*)grad,
+                                                    (uint4*)out_h, (uint4*)dgate, (uint4*)dup, vectors, true);
+    else
+      swiglu_bf16_kernel<false><<<grid, 256, 0, s>>>((const uint4*)gate, (const uint4*)up, (const uint4*)grad,
+                                                     (uint4*)out_h, (uint4*)dgate, (uint4*)dup, vectors, backward);
+    if (int rc = launch_status("swiglu_bf16_kernel")) return rc;
+  }
+  if (vectors * 8 < count) {
+    swiglu_scalar_kernel<__nv_bfloat16><<<grid_for(count - vectors * 8, 256), 256, 0, s>>>(
+        (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (const __nv_bfloat16*)grad, (__nv_bfloat16*)out_h,
+        (__nv_bfloat16*)dgate, (__nv_bfloat16*)dup, vectors * 8, count, backward);
+    if (int rc = launch_status("swiglu_scalar_kernel<bf16>")) return rc;
+  }
+  return MOLT_OK;
+}
+
+extern "C" int molt_swiglu_fwd(const void* gate, const void* up, void* out, int64_t count, int dtype,
+                               uintptr_t stream) {
+  return swiglu_launch(gate, up, nullptr, out, nullptr, nullptr, count, dtype, false, stream);
+}
+
+extern "C" int molt_swiglu_bwd(const void* grad_out, const void* gate, const void* up, void* dgate, void* dup,
+                               void* h_out, int64_t count, int dtype, uintptr_t stream) {
+  return swiglu_launch(gate, up, grad_out, h_out, dgate, dup, count, dtype, true, stream);
+}
+
+extern "C" int molt_rmsnorm_fwd(const void* x, const void* weight, int weight_dtype, float eps, float weight_offset,
+                                void* out, int64_t rows, int64_t width, uintptr_t stream) {
+  MOLT_REQUIRE(x && weight && out, MOLT_E_VALUE, "rmsnorm: NULL tensor pointer");
+  MOLT_REQUIRE(rows >= 0 && width > 0, MOLT_E_VALUE, "rmsnorm: bad shape");
+  MOLT_REQUIRE(weight_dtype == MOLT_DTYPE_BF16 || weight_dtype == MOLT_DTYPE_F32, MOLT_E_CAPABILITY,
+               "rmsnorm: weight dtype must be bf16 or fp32");
+  if (rows == 0) return MOLT_OK;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(rows * 32, 256, 8);
+  if (weight_dtype == MOLT_DTYPE_F32)
+    rmsnorm_kernel<float><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (const float*)weight, eps, weight_offset,
+                                               (__nv_bfloat16*)out, rows, width);
+  else
+    rmsnorm_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)weight, eps,
+                                                       weight_offset, (__nv_bfloat16*)out, rows, width);
+  return launch_status("rmsnorm_kernel");
+}

@@ -1,0 +1,45 @@
+// Prototypes shared between the translation units of libmolt_b200.
+#pragma once
+
+#include "common.cuh"
+
+namespace molt {
+
+// general.cu -- any shape
+int general_forward(const WeightView& w, const __nv_bfloat16* x, const __nv_bfloat16* t, int t_ld, const float* lora_b,
+                    float scaling, int rank, __nv_bfloat16* y, long long m, cudaStream_t s);
+int general_backward_input(const WeightView& w, const __nv_bfloat16* dy, const __nv_bfloat16* u, int u_ld,
+                           const void* lora_a, int lora_a_dtype, float scaling, int rank, __nv_bfloat16* dx,
+                           long long m, cudaStream_t s);
+int general_rowsum(bool by_rows, const __nv_bfloat16* in, const float* mat, float scale, long long m, long long cols,
+                   int rank, __nv_bfloat16* low, int low_ld, cudaStream_t s);
+int general_colsum(bool out_by_rows, const __nv_bfloat16* low, int low_ld, const __nv_bfloat16* in, float scale,
+                   long long m, long long cols, int rank, float* grad, int accumulate, cudaStream_t s);
+
+// skinny.cu -- aligned shapes
+int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, long long n, long long k,
+              __nv_bfloat16* a16, __nv_bfloat16* bs, __nv_bfloat16* bt, cudaStream_t s);
+int rowsum_mma(const __nv_bfloat16* in, const __nv_bfloat16* wt, int rp, long long m, long long cols,
+               __nv_bfloat16* out, cudaStream_t s);
+size_t colsum_partial_bytes(long long m, long long cols, int rp);
+int colsum_mma(bool transpose_out, const __nv_bfloat16* low, const __nv_bfloat16* in, int rp, int rank, long long m,
+               long long cols, float scale, float* partial, float* grad, int accumulate, cudaStream_t s);
+
+// gemv.cu
+size_t gemv_workspace_bytes(long long n, long long k);
+int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_a, const float* lora_b, float scaling,
+                 int rank, __nv_bfloat16* y, int m, void* workspace, size_t workspace_bytes, cudaStream_t s);
+
+// gemm_sm100.cu -- tcgen05 / TMEM GEMM with the NF4 decode fused in front of the tensor core
+//   forward : out[m, n] = in[m, k] . deq(W)^T + low[m, 0..rp) . ext[n, 0..rp)^T        (ext = bf16(s B) [n, 64])
+//   backward: out[m, k] = in[m, n] . deq(W)   + low[m, 0..rp) . ext[0..rp, k]           (ext = bf16(A)   [rp, k])
+// low is bf16 [m, 64]; low == nullptr skips the low-rank block.
+int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
+               const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
+               cudaStream_t s);
+bool sm100_gemm_supported(const WeightView& w, int rank);
+
+// elementwise helpers used by the block op
+int add_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, long long count, cudaStream_t s);
+
+}  // namespace molt

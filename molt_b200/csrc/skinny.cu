@@ -1,0 +1,296 @@
+// Low-rank (LoRA) side kernels for aligned shapes.  All are HBM-bound passes over X or dY:
+//   lora_prep      fp32 adapter masters -> bf16 operand layouts
+//   rowsum_mma     T = X . A^T        and   U = dY . (s B)        ([M, C] x [rp, C]^T -> [M, 64] bf16)
+//   colsum_mma     dA = U^T . X       and   dB^T = T^T . dY       ([M, 64]^T x [M, C] -> [rp, C] fp32 partials)
+//   colsum_reduce  deterministic sum of the split-M partials into the fp32 gradient
+// Tensor-core work uses mma.sync m16n8k16 (these passes are bandwidth-bound; the tcgen05 kernels carry the FLOPs).
+#include "common.cuh"
+
+namespace molt {
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Adapter operand preparation.
+//   a16  [rp, k]  bf16(A), rows >= rank zero
+//   bs   [n, 64]  bf16(scaling * B), columns >= rank zero      (forward low-rank k-block, K-major)
+//   bt   [rp, n]  bf16(scaling * B)^T, rows >= rank zero       (U = dY . (sB))
+// Any of the three outputs may be NULL.
+// ------------------------------------------------------------------------------------------------
+__global__ void lora_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, float scaling, int rank,
+                                 int rp, long long n, long long k, __nv_bfloat16* __restrict__ a16,
+                                 __nv_bfloat16* __restrict__ bs, __nv_bfloat16* __restrict__ bt) {
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  if (a16 != nullptr)
+    for (long long i = tid; i < (long long)rp * k; i += stride) {
+      const int r = (int)(i / k);
+      a16[i] = __float2bfloat16_rn(r < rank ? a[i] : 0.f);
+    }
+  if (bs != nullptr)
+    for (long long i = tid; i < n * 64; i += stride) {
+      const long long row = i >> 6;
+      const int r = (int)(i & 63);
+      bs[i] = __float2bfloat16_rn(r < rank ? scaling * b[row * rank + r] : 0.f);
+    }
+  if (bt != nullptr)
+    for (long long i = tid; i < (long long)rp * n; i += stride) {
+      const int r = (int)(i / n);
+      const long long row = i % n;
+      bt[i] = __float2bfloat16_rn(r < rank ? scaling * b[row * rank + r] : 0.f);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// rowsum: out[m, 0..63] = bf16(sum_c in[m, c] * wt[r, c]), zero for r >= RP.
+// One CTA = 16 rows; its 8 warps split the contraction in 32-column chunks and are summed in warp order.
+// The k index inside each MMA is permuted (thread t owns 8 consecutive columns) so that both operands are
+// fetched with 16-byte loads; the permutation is applied to both operands, so the sum is unchanged.
+// ------------------------------------------------------------------------------------------------
+template <int RP>
+__global__ void __launch_bounds__(256) rowsum_mma_kernel(const __nv_bfloat16* __restrict__ in,
+                                                         const __nv_bfloat16* __restrict__ wt, long long m_total,
+                                                         long long cols, __nv_bfloat16* __restrict__ out) {
+  constexpr int NT = RP / 8;
+  __shared__ float partial[8][16][RP + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const long long row0 = blockIdx.x * 16LL;
+  const long long r_lo = row0 + g, r_hi = row0 + g + 8;
+  const bool lo_ok = r_lo < m_total, hi_ok = r_hi < m_total;
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+  const long long chunks = cols / 32;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (long long c = warp; c < chunks; c += 8) {
+    const long long col = c * 32 + t * 8;
+    const uint4 lo = lo_ok ? __ldg(reinterpret_cast<const uint4*>(in + r_lo * cols + col)) : zero;
+    const uint4 hi = hi_ok ? __ldg(reinterpret_cast<const uint4*>(in + r_hi * cols + col)) : zero;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(wt + (long long)(j * 8 + g) * cols + col));
+      mma_bf16_16816(acc[j], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+      mma_bf16_16816(acc[j], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    partial[warp][g][j * 8 + 2 * t] = acc[j][0];
+    partial[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+    partial[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+    partial[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < 16 * 64; idx += 256) {
+    const int row = idx >> 6, r = idx & 63;
+    if (row0 + row >= m_total) continue;
+    float sum = 0.f;
+    if (r < RP) {
+#pragma unroll
+      for (int wv = 0; wv < 8; ++wv) sum += partial[wv][row][r];
+    }
+    out[(row0 + row) * 64 + r] = __float2bfloat16_rn(sum);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// colsum: partial[split][r][c] = sum_{m in split} low[m, r] * in[m, c].
+// CTA = 4 warps on a 64-column slab; rows are streamed in 64-row tiles through a 2-stage cp.async ring
+// and both operands are read transposed with ldmatrix.trans.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+constexpr int kColsumRowBytes = 144;  // 128 data bytes + 16 pad: conflict-free ldmatrix rows
+constexpr int kColsumTileBytes = 64 * kColsumRowBytes;
+
+template <int RP>
+__global__ void __launch_bounds__(128) colsum_mma_kernel(const __nv_bfloat16* __restrict__ low,
+                                                         const __nv_bfloat16* __restrict__ in, long long m_total,
+                                                         long long cols, int tiles_per_split,
+                                                         float* __restrict__ partial) {
+  constexpr int MT = RP / 16;
+  __shared__ __align__(16) unsigned char smem[2][2][kColsumTileBytes];  // [stage][0 = in, 1 = low]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long col0 = blockIdx.x * 64LL;
+  const int split = blockIdx.y;
+  const long long tiles_total = (m_total + 63) / 64;
+  const long long tile_begin = (long long)split * tiles_per_split;
+  long long tile_end = tile_begin + tiles_per_split;
+  if (tile_end > tiles_total) tile_end = tiles_total;
+  const int ntiles = (int)(tile_end > tile_begin ? tile_end - tile_begin : 0);
+
+  float acc[MT][2][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.f;
+
+  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(&smem[0][0][0]);
+  auto issue = [&](int tile_idx, int stage) {
+    const long long m0 = (tile_begin + tile_idx) * 64;
+    const uint32_t in_s = smem_base + (stage * 2 + 0) * kColsumTileBytes;
+    const uint32_t low_s = smem_base + (stage * 2 + 1) * kColsumTileBytes;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int chunk = threadIdx.x + i * 128;  // 512 chunks: 64 rows x 8
+      const int row = chunk >> 3, c16 = chunk & 7;
+      const bool ok = (m0 + row) < m_total;
+      const __nv_bfloat16* src = in + (ok ? (m0 + row) : 0) * cols + col0 + c16 * 8;
+      cp_async16(in_s + row * kColsumRowBytes + c16 * 16, src, ok);
+    }
+    constexpr int LOW_CHUNKS = 64 * (RP / 8);
+    for (int chunk = threadIdx.x; chunk < LOW_CHUNKS; chunk += 128) {
+      const int row = chunk / (RP / 8), c16 = chunk % (RP / 8);
+      const bool ok = (m0 + row) < m_total;
+      const __nv_bfloat16* src = low + (ok ? (m0 + row) : 0) * 64 + c16 * 8;
+      cp_async16(low_s + row * kColsumRowBytes + c16 * 16, src, ok);
+    }
+    cp_async_commit();
+  };
+
+  if (ntiles > 0) issue(0, 0);
+  for (int it = 0; it < ntiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < ntiles) {
+      issue(it + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t in_s = smem_base + (stage * 2 + 0) * kColsumTileBytes;
+    const uint32_t low_s = smem_base + (stage * 2 + 1) * kColsumTileBytes;
+    const int q = lane >> 3, rr = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, in_s + (ks * 16 + (q & 1) * 8 + rr) * kColsumRowBytes + (warp * 16 + (q >> 1) * 8) * 2);
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, low_s + (ks * 16 + (q >> 1) * 8 + rr) * kColsumRowBytes + (i * 16 + (q & 1) * 8) * 2);
+        mma_bf16_16816(acc[i][0], a[0], a[1], a[2], a[3], b[0], b[1]);
+        mma_bf16_16816(acc[i][1], a[0], a[1], a[2], a[3], b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, t = lane & 3;
+  float* dst = partial + (long long)split * RP * cols;
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const long long c = col0 + warp * 16 + j * 8 + 2 * t;
+      *reinterpret_cast<float2*>(dst + (long long)(i * 16 + g) * cols + c) = make_float2(acc[i][j][0], acc[i][j][1]);
+      *reinterpret_cast<float2*>(dst + (long long)(i * 16 + g + 8) * cols + c) =
+          make_float2(acc[i][j][2], acc[i][j][3]);
+    }
+}
+
+// grad (+)= scale * sum_split partial[split][r][c];  TRANSPOSE writes grad[c, r] (dB), else grad[r, c] (dA).
+template <bool TRANSPOSE>
+__global__ void colsum_reduce_kernel(const float* __restrict__ partial, int splits, int rp, int rank, long long cols,
+                                     float scale, float* __restrict__ grad, int accumulate) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= cols * rank) return;
+  const int r = TRANSPOSE ? (int)(idx % rank) : (int)(idx / cols);
+  const long long c = TRANSPOSE ? idx / rank : idx % cols;
+  float sum = 0.f;
+  for (int s = 0; s < splits; ++s) sum += partial[((long long)s * rp + r) * cols + c];
+  sum *= scale;
+  grad[idx] = accumulate ? grad[idx] + sum : sum;
+}
+
+// ---- host wrappers --------------------------------------------------------------------------------
+int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, long long n, long long k,
+              __nv_bfloat16* a16, __nv_bfloat16* bs, __nv_bfloat16* bt, cudaStream_t s) {
+  long long work = 0;
+  if (a16) work = (long long)rp * k;
+  if (bs && n * 64 > work) work = n * 64;
+  if (bt && (long long)rp * n > work) work = (long long)rp * n;
+  if (work == 0) return MOLT_OK;
+  long long blocks = (work + 255) / 256;
+  const long long cap = (long long)sm_count() * 4;
+  if (blocks > cap) blocks = cap;
+  lora_prep_kernel<<<(unsigned)blocks, 256, 0, s>>>(a, b, scaling, rank, rp, n, k, a16, bs, bt);
+  return launch_status("lora_prep_kernel");
+}
+
+int rowsum_mma(const __nv_bfloat16* in, const __nv_bfloat16* wt, int rp, long long m, long long cols,
+               __nv_bfloat16* out, cudaStream_t s) {
+  if (m == 0) return MOLT_OK;
+  const unsigned grid = (unsigned)((m + 15) / 16);
+  switch (rp) {
+    case 16: rowsum_mma_kernel<16><<<grid, 256, 0, s>>>(in, wt, m, cols, out); break;
+    case 32: rowsum_mma_kernel<32><<<grid, 256, 0, s>>>(in, wt, m, cols, out); break;
+    case 48: rowsum_mma_kernel<48><<<grid, 256, 0, s>>>(in, wt, m, cols, out); break;
+    case 64: rowsum_mma_kernel<64><<<grid, 256, 0, s>>>(in, wt, m, cols, out); break;
+    default: return fail(MOLT_E_CAPABILITY, "rowsum_mma: padded rank %d unsupported", rp);
+  }
+  return launch_status("rowsum_mma_kernel");
+}
+
+int colsum_splits(long long m, long long cols) {
+  const long long tiles = (m + 63) / 64;
+  const long long slabs = cols / 64;
+  long long want = ((long long)sm_count() * 4 + slabs - 1) / slabs;
+  if (want > tiles) want = tiles;
+  if (want > 64) want = 64;
+  if (want < 1) want = 1;
+  // make every split non-empty
+  const long long per = (tiles + want - 1) / want;
+  return (int)((tiles + per - 1) / per);
+}
+
+size_t colsum_partial_bytes(long long m, long long cols, int rp) {
+  return (size_t)colsum_splits(m, cols) * rp * cols * sizeof(float);
+}
+
+int colsum_mma(bool transpose_out, const __nv_bfloat16* low, const __nv_bfloat16* in, int rp, int rank, long long m,
+               long long cols, float scale, float* partial, float* grad, int accumulate, cudaStream_t s) {
+  if (cols == 0 || rank == 0) return MOLT_OK;
+  const int splits = colsum_splits(m, cols);
+  const long long tiles = (m + 63) / 64;
+  const int per = (int)((tiles + splits - 1) / splits);
+  dim3 grid((unsigned)(cols / 64), (unsigned)splits);
+  switch (rp) {
+    case 16: colsum_mma_kernel<16><<<grid, 128, 0, s>>>(low, in, m, cols, per, partial); break;
+    case 32: colsum_mma_kernel<32><<<grid, 128, 0, s>>>(low, in, m, cols, per, partial); break;
+    case 48: colsum_mma_kernel<48><<<grid, 128, 0, s>>>(low, in, m, cols, per, partial); break;
+    case 64: colsum_mma_kernel<64><<<grid, 128, 0, s>>>(low, in, m, cols, per, partial); break;
+    default: return fail(MOLT_E_CAPABILITY, "colsum_mma: padded rank %d unsupported", rp);
+  }
+  if (int rc = launch_status("colsum_mma_kernel")) return rc;
+  const long long total = cols * rank;
+  const unsigned rgrid = (unsigned)((total + 255) / 256);
+  if (transpose_out)
+    colsum_reduce_kernel<true><<<rgrid, 256, 0, s>>>(partial, splits, rp, rank, cols, scale, grad, accumulate);
+  else
+    colsum_reduce_kernel<false><<<rgrid, 256, 0, s>>>(partial, splits, rp, rank, cols, scale, grad, accumulate);
+  return launch_status("colsum_reduce_kernel");
+}
+
+}  // namespace molt

@@ -1,0 +1,128 @@
+"""Data-parallel training of the LoRA adapters: token batches are sharded over ranks, the frozen NF4
+weights are replicated, and only the adapter gradients are exchanged.
+
+The reference is single-GPU (its model is pinned to device 0, reference training/qlora.py:343), so this
+file has no counterpart there; the invariant it maintains is "sum over ranks of the per-shard adapter
+gradients == the full-batch adapter gradients".
+
+``GradArena`` lays every trainable adapter parameter's gradient out in ONE flat fp32 buffer, in registration
+order.  The backward kernels accumulate dA/dB straight into their slice (no per-parameter autograd
+accumulation, no pack/unpack copy), and ``all_reduce`` hands contiguous, layer-ordered buckets of that same
+buffer to the process group (NCCL over NVLink on GPUs, gloo in CPU tests) on a side stream so the exchange
+overlaps the remaining backward.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from molt_b200.methods._linear import GRAD_SLOT
+
+
+class GradArena:
+    """One flat fp32 gradient buffer shared by a list of parameters."""
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], bucket_bytes: int = 32 << 20):
+        self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
+        if not self.params:
+            raise ValueError("GradArena needs at least one trainable parameter")
+        device = self.params[0].device
+        offsets = []
+        total = 0
+        for p in self.params:
+            if p.dtype != torch.float32 or p.device != device:
+                raise ValueError("GradArena parameters must be float32 on one device")
+            offsets.append(total)
+            total += (p.numel() + 63) // 64 * 64  # 256-byte aligned slices
+        self.flat = torch.zeros(total, dtype=torch.float32, device=device)
+        self.offsets = offsets
+        self.views: List[torch.Tensor] = []
+        for p, off in zip(self.params, offsets):
+            view = self.flat[off:off + p.numel()].view_as(p)
+            self.views.append(view)
+            p.grad = view
+            setattr(p, GRAD_SLOT, view)
+        self.buckets = self._make_buckets(bucket_bytes)
+        self._comm_stream: Optional[torch.cuda.Stream] = None
+
+    def _make_buckets(self, bucket_bytes: int) -> List[Tuple[int, int]]:
+        """Contiguous [begin, end) element ranges, cut at parameter boundaries, walked from the LAST
+        parameter to the first (the order in which backward produces gradients)."""
+        limit = max(1, bucket_bytes // 4)
+        bounds = self.offsets + [self.flat.numel()]
+        buckets: List[Tuple[int, int]] = []
+        end = len(self.params)
+        while end > 0:
+            begin = end - 1
+            while begin > 0 and bounds[end] - bounds[begin - 1] <= limit:
+                begin -= 1
+            buckets.append((bounds[begin], bounds[end]))
+            end = begin
+        return buckets
+
+    def zero(self) -> None:
+        self.flat.zero_()
+
+    def bucket_of_param(self, index: int) -> int:
+        off = self.offsets[index]
+        for b, (lo, hi) in enumerate(self.buckets):
+            if lo <= off < hi:
+                return b
+        raise IndexError(index)
+
+    def all_reduce_bucket(self, bucket: int, group=None, async_stream: bool = True) -> None:
+        """Sum one bucket over the group.  On CUDA the collective is enqueued on a side stream that first
+        waits for the current stream (the producer of the gradients)."""
+        lo, hi = self.buckets[bucket]
+        chunk = self.flat[lo:hi]
+        if self.flat.is_cuda and async_stream:
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=self.flat.device)
+            self._comm_stream.wait_stream(torch.cuda.current_stream(self.flat.device))
+            with torch.cuda.stream(self._comm_stream):
+                dist.all_reduce(chunk, op=dist.ReduceOp.SUM, group=group)
+        else:
+            dist.all_reduce(chunk, op=dist.ReduceOp.SUM, group=group)
+
+    def all_reduce(self, group=None, average: bool = False) -> None:
+        """Sum (or average) the whole arena over the group, bucket by bucket, then rejoin the main stream."""
+        if not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return
+        for b in range(len(self.buckets)):
+            self.all_reduce_bucket(b, group)
+        self.wait()
+        if average:
+            self.flat.div_(dist.get_world_size(group))
+
+    def wait(self) -> None:
+        """Make the current stream wait for the collectives issued so far."""
+        if self._comm_stream is not None:
+            torch.cuda.current_stream(self.flat.device).wait_stream(self._comm_stream)
+
+
+def shard_rows(total_rows: int, rank: int, world_size: int) -> Tuple[int, int]:
+    """Row range [begin, end) of ``rank`` when ``total_rows`` tokens are split as evenly as possible."""
+    base, extra = divmod(total_rows, world_size)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def lora_parameters(model: torch.nn.Module) -> List[torch.nn.Parameter]:
+    """Trainable parameters in module registration order (frozen NF4 bases are skipped)."""
+    return [p for p in model.parameters() if p.requires_grad]
+
+
+def check_replicas_equal(tensors: Sequence[torch.Tensor], group=None) -> bool:
+    """True when every rank holds bit-identical copies of ``tensors`` (used after an optimiser step)."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return True
+    ok = True
+    for t in tensors:
+        lo = t.detach().clone()
+        hi = t.detach().clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+        ok = ok and bool(torch.equal(lo, hi))
+    return ok
