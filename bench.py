@@ -1,0 +1,430 @@
+"""Benchmark of the NF4-LoRA hot path.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5                       # this repository's CUDA path
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference --steps 3 --warmup 1                # the reference's eager path on host cores
+
+One "step" is one forward + backward of a frozen NF4 linear with its LoRA adapter on one batch of tokens.
+Workload (BASELINE config 2's weight, at the M the targets are quoted for): W [14336, 4096] ~ N(0, 0.02),
+NF4 blocksize 64 with the absmax double-quantised to 8 bit in blocks of 256, LoRA r=16 alpha=32,
+M = 4096 tokens per GPU, X and dY ~ N(0, 1) in bf16, seeded synthetic data.  With N > 1 GPUs the token batch is
+sharded (4096 tokens per GPU, weak scaling) and the LoRA gradients are all-reduced over NCCL every step.
+Prints exactly one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+N_OUT, K_IN, RANK, ALPHA, M_PER_GPU = 14336, 4096, 16, 32.0, 4096
+SCALING = ALPHA / RANK
+METRIC = "nf4_lora_linear_fwd_bwd_tflops"
+WORKLOAD = ("NF4-LoRA linear fwd+bwd, W[14336,4096] NF4 bs64 double-quant absmax, r=16 alpha=32, "
+            "M=4096 tokens per GPU, bf16")
+
+
+def linear_flops(m: int, n: int = N_OUT, k: int = K_IN, r: int = RANK, backward: bool = True) -> float:
+    """Algorithmic FLOPs: fwd 2MNK + 2Mr(K+N); fwd+bwd 4MNK + 6Mr(K+N) (recomputation not counted)."""
+    return (4.0 if backward else 2.0) * m * n * k + (6.0 if backward else 2.0) * m * r * (k + n)
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {"bf16_tflops": float(data["bf16_tflops"]), "bf16_tflops_sustained": float(data["bf16_tflops_sustained"]),
+                "hbm_gbs": float(data["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            handle = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = handle.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=handle, stderr=subprocess.DEVNULL)
+            time.sleep(0.3)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        clocks, reasons, sm_max = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                sm_max = float(parts[2])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if clocks:
+            clocks.sort()
+            busy = clocks[len(clocks) // 2:]  # upper half = samples under load
+            out["sm_mhz"] = busy[len(busy) // 2]
+            out["sm_max_mhz"] = sm_max
+            out["reasons"] = sorted(reasons)
+        return out
+
+
+# ------------------------------------------------------------------------------------------------------
+# reference arm: the reference's eager CPU path (oracle restatement) on the host cores
+# ------------------------------------------------------------------------------------------------------
+
+def synthetic_quantized_weight_cpu(n: int, k: int, seed: int):
+    """Seeded synthetic NF4 weight made directly on the host (nearest level through the midpoints of the
+    codebook; ties do not matter for timing)."""
+    from oracle import molt_oracle as oracle
+
+    gen = torch.Generator().manual_seed(seed)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    blocks = w.reshape(-1, 64)
+    scales = blocks.abs().amax(dim=1).clamp_min(torch.finfo(torch.float32).tiny)
+    mids = (oracle.NF4_CODEBOOK[1:] + oracle.NF4_CODEBOOK[:-1]) / 2
+    codes = torch.bucketize(blocks / scales[:, None], mids).to(torch.uint8)
+    packed = ((codes[:, 0::2] << 4) | codes[:, 1::2]).reshape(-1)
+    q = oracle.OracleNF4(packed, scales, (n, k), 64, n * k, oracle.HIGH_FIRST)
+    nested = oracle.nest_absmax(scales)
+    return q, oracle.resolve_nested_absmax(nested)
+
+
+def time_cpu_reference(sample_rows: int, steps: int, warmup: int, q=None, scales=None):
+    """Times dequantise + forward + backward (which dequantises again) exactly as the reference's eager path does."""
+    from oracle import molt_oracle as oracle
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    if q is None:
+        q, scales = synthetic_quantized_weight_cpu(N_OUT, K_IN, 1337)
+    gen = torch.Generator().manual_seed(1340)
+    a = torch.randn(RANK, K_IN, generator=gen) * 0.01
+    b = torch.randn(N_OUT, RANK, generator=gen) * 0.01
+    x = torch.randn(sample_rows, K_IN, generator=gen)
+    dy = torch.randn(sample_rows, N_OUT, generator=gen)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        oracle.nf4_lora_fwd_bwd(q, x, dy, a, b, SCALING, scales)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    seconds = sum(times) / len(times)
+    return {"value": linear_flops(sample_rows) / seconds / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"{sample_rows} of {M_PER_GPU} token rows per step, full weight, fp32, torch {torch.__version__} "
+                      f"on {cores} host threads; {steps} timed steps",
+            "ms_per_step": seconds * 1e3}
+
+
+def run_reference_arm(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    sample_rows = 1024
+    base = time_cpu_reference(sample_rows, max(1, args.steps), max(1, args.warmup))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample_rows_per_step": sample_rows},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------------
+# this repository's arm
+# ------------------------------------------------------------------------------------------------------
+
+def event_time_ms(fn, iters: int, warmup: int = 0) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / iters
+
+
+def run_ours(args) -> int:
+    import torch.distributed as dist
+
+    from molt_b200 import _native
+    from molt_b200.methods import QuantState, quantize_nf4, resolved_nf4_scales, scheduled_nf4_lora
+    from molt_b200.methods._linear import weight_desc
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _native.library()
+    peaks = measured_peaks()
+
+    # ---- synthetic workload (seeded; identical weight on every rank, different tokens per rank) ----
+    gen = torch.Generator(device=device).manual_seed(1337)
+    w = torch.randn(N_OUT, K_IN, device=device, generator=gen) * 0.02
+    packed, state = quantize_nf4(w, 64, compress_statistics=True)
+    del w
+    lora_a = torch.randn(RANK, K_IN, device=device, generator=gen) * 0.01
+    lora_b = torch.randn(N_OUT, RANK, device=device, generator=gen) * 0.01
+    tok_gen = torch.Generator(device=device).manual_seed(4242 + rank)
+    m = M_PER_GPU
+    x = torch.randn(m, K_IN, device=device, generator=tok_gen).bfloat16()
+    dy = torch.randn(m, N_OUT, device=device, generator=tok_gen).bfloat16()
+    desc = weight_desc(packed, state)
+
+    y = torch.empty(m, N_OUT, device=device, dtype=torch.bfloat16)
+    dx = torch.empty(m, K_IN, device=device, dtype=torch.bfloat16)
+    t_buf = torch.empty(m, 64, device=device, dtype=torch.bfloat16)
+    grads = torch.zeros(RANK * K_IN + N_OUT * RANK, device=device, dtype=torch.float32)
+    da, db = grads[: RANK * K_IN].view(RANK, K_IN), grads[RANK * K_IN:].view(N_OUT, RANK)
+    ws_bytes = max(lib.molt_workspace_bytes(_native.OP_LORA_FWD, m, N_OUT, K_IN, RANK),
+                   lib.molt_workspace_bytes(_native.OP_LORA_BWD, m, N_OUT, K_IN, RANK))
+    ws = torch.empty(ws_bytes, device=device, dtype=torch.uint8)
+    stream = _native.stream_handle(device)
+
+    def step_device():
+        _native.check(lib.molt_nf4_lora_fwd(ctypes.byref(desc), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
+                                            SCALING, RANK, y.data_ptr(), m, t_buf.data_ptr(), ws.data_ptr(), ws_bytes,
+                                            _native.PATH_AUTO, stream))
+        _native.check(lib.molt_nf4_lora_bwd(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), lora_a.data_ptr(),
+                                            lora_b.data_ptr(), SCALING, RANK, dx.data_ptr(), da.data_ptr(),
+                                            db.data_ptr(), m, t_buf.data_ptr(), 0, ws.data_ptr(), ws_bytes,
+                                            _native.PATH_AUTO, stream))
+        if world > 1:
+            dist.all_reduce(grads, op=dist.ReduceOp.SUM)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- timed region: device-resident inputs -------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    barrier()
+    launches_before = lib.molt_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as sampler:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            step_device()
+        stop.record()
+        barrier()
+    elapsed_ms = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(elapsed_ms.item())
+    launches = int(lib.molt_launch_count() - launches_before)
+    status = _native.read_status(device)
+    if status:
+        raise SystemExit(f"a bounded device wait expired during the timed region (status 0x{status:08x})")
+    clocks = sampler.summary()
+    ms_per_step = elapsed_ms / args.steps
+    value = world * linear_flops(m) / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the Python API, host buffers, copies inside the timed region -------------
+    x_host = x.cpu().pin_memory()
+    dy_host = dy.cpu().pin_memory()
+    grads_host = torch.empty(grads.shape, dtype=torch.float32).pin_memory()
+    a_param = lora_a.clone().requires_grad_()
+    b_param = lora_b.clone().requires_grad_()
+    x_dev = torch.empty_like(x)
+    dy_dev = torch.empty_like(dy)
+
+    def step_e2e():
+        x_dev.copy_(x_host, non_blocking=True)
+        dy_dev.copy_(dy_host, non_blocking=True)
+        a_param.grad = None
+        b_param.grad = None
+        xin = x_dev.detach().requires_grad_()
+        out = scheduled_nf4_lora(xin, packed, a_param, b_param, state, SCALING)
+        out.backward(dy_dev)
+        flat = torch.cat([a_param.grad.reshape(-1), b_param.grad.reshape(-1)])
+        if world > 1:
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+        grads_host.copy_(flat, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    start.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    stop.record()
+    barrier()
+    e2e_ms = torch.tensor([start.elapsed_time(stop) / e2e_steps], device=device)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = world * linear_flops(m) / (float(e2e_ms.item()) * 1e-3) / 1e12
+    e2e = {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": float(e2e_ms.item()),
+           "h2d_bytes_per_step": x_host.numel() * 2 + dy_host.numel() * 2, "d2h_bytes_per_step": grads_host.numel() * 4}
+
+    # ---- roofline of the dominant kernel: the tcgen05 GEMM, timed alone with CUDA events ---------------
+    plain_state = QuantState(absmax=resolved_nf4_scales(state), shape=(N_OUT, K_IN), nibble_order=state.nibble_order)
+    plain_desc = weight_desc(packed, plain_state)
+
+    def gemm_only():  # exactly one launch of nf4_gemm_sm100_kernel<backward>: dx = dy . deq(W)
+        _native.check(lib.molt_nf4_dx(ctypes.byref(plain_desc), dy.data_ptr(), None, None, 0, 0.0, 0, dx.data_ptr(), m,
+                                      ws.data_ptr(), ws_bytes, _native.PATH_TCGEN05, stream))
+
+    gemm_ms = event_time_ms(gemm_only, iters=max(5, args.steps), warmup=3)
+    achieved = 2.0 * m * N_OUT * K_IN / (gemm_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "nf4_gemm_sm100_kernel<backward> (dX = dY . deq(W), M=4096)",
+                "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_tflops"], "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                "peak_source": f"{peaks['source']} (cuBLAS bf16 burst)", "ms_per_launch": gemm_ms, "traffic": None}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens_per_gpu": m, "n": N_OUT, "k": K_IN, "rank": RANK,
+                   "parallelism": f"dp{world}", "l2": "per-step working set (X, dY, Y, dX = 300 MB) exceeds the 126 MB L2"},
+        "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
+        "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+    }
+
+    if rank == 0 and not args.no_extras:
+        line["extra"] = extras(lib, device, desc, packed, state, lora_a, lora_b, peaks)
+    if rank == 0 and world == 1:
+        base = time_cpu_reference(1024, steps=5, warmup=1)
+        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+    return 0
+
+
+def extras(lib, device, desc, packed, state, lora_a, lora_b, peaks):
+    """Secondary measurements: BASELINE config 2's forward M-sweep, SwiGLU bandwidth, config 3's MLP block."""
+    from molt_b200 import _native
+    from molt_b200.kernels.gated_activation import swiglu_backward, swiglu_forward
+    from molt_b200.methods._linear import linear_forward
+    from molt_b200.modules import GatedMLP, NF4LoRALinear
+
+    out = {}
+    gen = torch.Generator(device=device).manual_seed(99)
+    sweep = []
+    nblocks = N_OUT * K_IN // 64
+    for m in (1, 16, 64, 256, 1024, 4096, 16384):
+        x = torch.randn(m, K_IN, device=device, generator=gen).bfloat16()
+        ms = event_time_ms(lambda: linear_forward(desc, x, lora_a, lora_b, SCALING, False), iters=10, warmup=3)
+        flops = linear_flops(m, backward=False)
+        bytes_alg = N_OUT * K_IN // 2 + nblocks + nblocks // 256 * 4 + m * K_IN * 2 + m * N_OUT * 2 + RANK * (K_IN + N_OUT) * 4
+        sweep.append({"m": m, "ms": ms, "tflops": flops / ms / 1e9, "frac_bf16_peak": flops / ms / 1e9 / peaks["bf16_tflops"],
+                      "gbs": bytes_alg / ms / 1e6, "frac_hbm": bytes_alg / ms / 1e6 / peaks["hbm_gbs"]})
+    out["forward_sweep_config2"] = sweep
+
+    rows, inter, hidden = 8192, 8960, 1536
+    g = torch.randn(rows, inter, device=device, generator=gen).bfloat16()
+    u = torch.randn(rows, inter, device=device, generator=gen).bfloat16()
+    d = torch.randn(rows, inter, device=device, generator=gen).bfloat16()
+    count = rows * inter
+    fwd_ms = event_time_ms(lambda: swiglu_forward(g, u), iters=10, warmup=3)
+    bwd_ms = event_time_ms(lambda: swiglu_backward(d, g, u), iters=10, warmup=3)
+    out["swiglu_config3"] = {
+        "elements": count,
+        "fwd": {"ms": fwd_ms, "gbs": 6 * count / fwd_ms / 1e6, "frac_hbm": 6 * count / fwd_ms / 1e6 / peaks["hbm_gbs"]},
+        "bwd": {"ms": bwd_ms, "gbs": 10 * count / bwd_ms / 1e6, "frac_hbm": 10 * count / bwd_ms / 1e6 / peaks["hbm_gbs"]},
+    }
+    del g, u, d
+
+    def proj(n, k):
+        w = torch.randn(n, k, device=device, generator=gen) * 0.02
+        lin = NF4LoRALinear.from_dense(w, RANK, ALPHA, nibble_order="low-first")
+        with torch.no_grad():
+            lin.lora_B["default"].weight.normal_(0, 0.01, generator=gen)
+        return lin
+
+    mlp = GatedMLP(proj(inter, hidden), proj(inter, hidden), proj(hidden, inter))
+    x = torch.randn(rows, hidden, device=device, generator=gen).bfloat16()
+    dy = torch.randn(rows, hidden, device=device, generator=gen).bfloat16()
+
+    def block_step():
+        xin = x.detach().requires_grad_()
+        mlp.fused(xin, rematerialize_up=True).backward(dy)
+
+    ms = event_time_ms(block_step, iters=5, warmup=2)
+    flops = 3 * linear_flops(rows, inter, hidden)
+    out["mlp_block_config3"] = {"ms": ms, "tflops_algorithmic": flops / ms / 1e9,
+                                "frac_bf16_peak": flops / ms / 1e9 / peaks["bf16_tflops"], "replay_up": True}
+    return out
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
+    args = parser.parse_args()
+    if args.steps < 1:
+        parser.error("--steps must be positive")
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
