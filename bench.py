@@ -195,6 +195,28 @@ def event_time_ms(fn, iters: int, warmup: int = 0) -> float:
     return start.elapsed_time(stop) / iters
 
 
+def graph_time_ms(calls, replays: int = 20) -> float:
+    """Device time per call for short kernels: the calls (one per rotating buffer set) are captured into a
+    CUDA graph so that host launch overhead is not what is measured; returns ms per call."""
+    for fn in calls:
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for fn in calls:
+            fn()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / (replays * len(calls))
+
+
 def run_ours(args) -> int:
     import torch.distributed as dist
 
@@ -253,6 +275,9 @@ def run_ours(args) -> int:
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.profile:
+        return profile_case(args.profile, lib, device, desc, packed, state, lora_a, lora_b, x, dy, y, dx, ws, ws_bytes)
 
     # ---- timed region: device-resident inputs -------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
@@ -355,24 +380,77 @@ def run_ours(args) -> int:
     return 0
 
 
+def profile_case(which, lib, device, desc, packed, state, lora_a, lora_b, x, dy, y, dx, ws, ws_bytes) -> int:
+    """Runs one kernel family a few times and exits: the small case an ncu capture is pointed at."""
+    from molt_b200 import _native
+    from molt_b200.kernels.gated_activation import swiglu_backward, swiglu_forward
+    from molt_b200.methods import QuantState, resolved_nf4_scales
+    from molt_b200.methods._linear import weight_desc
+
+    stream = _native.stream_handle(device)
+    m = x.shape[0]
+    plain = QuantState(absmax=resolved_nf4_scales(state), shape=(N_OUT, K_IN), nibble_order=state.nibble_order)
+    plain_desc = weight_desc(packed, plain)
+    for _ in range(4):
+        if which == "gemm_bwd":
+            _native.check(lib.molt_nf4_dx(ctypes.byref(plain_desc), dy.data_ptr(), None, None, 0, 0.0, 0, dx.data_ptr(), m,
+                                          ws.data_ptr(), ws_bytes, _native.PATH_TCGEN05, stream))
+        elif which == "linear_fwd":
+            _native.check(lib.molt_nf4_lora_fwd(ctypes.byref(plain_desc), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
+                                                SCALING, RANK, y.data_ptr(), m, None, ws.data_ptr(), ws_bytes,
+                                                _native.PATH_TCGEN05, stream))
+        elif which == "gemv":
+            _native.check(lib.molt_nf4_gemv(ctypes.byref(desc), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(), SCALING,
+                                            RANK, y.data_ptr(), 16, ws.data_ptr(), ws_bytes, stream))
+        elif which == "swiglu":
+            swiglu_forward(dy, dy)
+            swiglu_backward(dy, dy, dy)
+        else:
+            raise SystemExit(f"unknown profile case {which}")
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": which, "status": _native.read_status(device)}))
+    return 0
+
+
 def extras(lib, device, desc, packed, state, lora_a, lora_b, peaks):
     """Secondary measurements: BASELINE config 2's forward M-sweep, SwiGLU bandwidth, config 3's MLP block."""
     from molt_b200 import _native
     from molt_b200.kernels.gated_activation import swiglu_backward, swiglu_forward
-    from molt_b200.methods._linear import linear_forward
+    from molt_b200.methods import QuantState
+    from molt_b200.methods._linear import weight_desc
     from molt_b200.modules import GatedMLP, NF4LoRALinear
 
     out = {}
     gen = torch.Generator(device=device).manual_seed(99)
     sweep = []
     nblocks = N_OUT * K_IN // 64
+    # Rotate over copies of the packed weight so that consecutive calls do not find it in the 126 MB L2.
+    copies = []
+    for _ in range(6):
+        st = QuantState(absmax=state.absmax.clone(), shape=state.shape, nested=True, nibble_order=state.nibble_order,
+                        state2=state.state2, offset=state.offset)
+        pk = packed.clone()
+        copies.append((pk, st, weight_desc(pk, st)))
     for m in (1, 16, 64, 256, 1024, 4096, 16384):
         x = torch.randn(m, K_IN, device=device, generator=gen).bfloat16()
-        ms = event_time_ms(lambda: linear_forward(desc, x, lora_a, lora_b, SCALING, False), iters=10, warmup=3)
+        y = torch.empty(m, N_OUT, device=device, dtype=torch.bfloat16)
+        ws_bytes = lib.molt_workspace_bytes(_native.OP_LORA_FWD, m, N_OUT, K_IN, RANK)
+        ws = torch.empty(ws_bytes, device=device, dtype=torch.uint8)
+
+        def call(d):
+            def fn():
+                _native.check(lib.molt_nf4_lora_fwd(ctypes.byref(d), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
+                                                    SCALING, RANK, y.data_ptr(), m, None, ws.data_ptr(), ws_bytes,
+                                                    _native.PATH_AUTO, _native.stream_handle(device)))
+            return fn
+
+        ms = graph_time_ms([call(c[2]) for c in copies], replays=20 if m <= 1024 else 3)
         flops = linear_flops(m, backward=False)
         bytes_alg = N_OUT * K_IN // 2 + nblocks + nblocks // 256 * 4 + m * K_IN * 2 + m * N_OUT * 2 + RANK * (K_IN + N_OUT) * 4
-        sweep.append({"m": m, "ms": ms, "tflops": flops / ms / 1e9, "frac_bf16_peak": flops / ms / 1e9 / peaks["bf16_tflops"],
+        sweep.append({"m": m, "ms": ms, "path": "gemv" if m <= 16 else "tcgen05", "tflops": flops / ms / 1e9,
+                      "frac_bf16_peak": flops / ms / 1e9 / peaks["bf16_tflops"],
                       "gbs": bytes_alg / ms / 1e6, "frac_hbm": bytes_alg / ms / 1e6 / peaks["hbm_gbs"]})
+    del copies
     out["forward_sweep_config2"] = sweep
 
     rows, inter, hidden = 8192, 8960, 1536
@@ -418,6 +496,8 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
+    parser.add_argument("--profile", choices=("gemm_bwd", "linear_fwd", "gemv", "swiglu"), default=None,
+                        help="run one kernel family four times and exit (target of an ncu capture)")
     args = parser.parse_args()
     if args.steps < 1:
         parser.error("--steps must be positive")

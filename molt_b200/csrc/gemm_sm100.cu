@@ -17,8 +17,10 @@
 // kernel returns.
 #include <cuda.h>
 #include <cudaTypedefs.h>
+#include <stdlib.h>
 
 #include "internal.h"
+#include "sm100_ptx.cuh"
 
 namespace molt {
 
@@ -41,8 +43,6 @@ constexpr uint32_t kStoreBytes = BM * 64 * 2;       // one TMA-store box: 128 ro
 constexpr uint32_t kLutBytes = 16 * 32 * 4;
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + 2 * kStoreBytes + kLutBytes + 256 /*barriers*/ + 1024 /*align*/;
 
-constexpr int kStatusTimeout = 1;
-
 struct GemmParams {
   const float* absmax;   // fp32 [n * k / 64]
   int32_t* status;
@@ -53,113 +53,6 @@ struct GemmParams {
   int nibble_high_first;
   float codebook[16];
 };
-
-// ---- PTX wrappers ------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-
-// Bounded wait.  Returns false when the wait expired or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int where) {
-  if (mbar_try(bar, parity)) return true;
-  const long long start = clock64();
-  for (uint32_t spin = 0;; ++spin) {
-    if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if ((spin & 63u) == 63u && clock64() - start > 2000000000LL) {  // about one second
-      *abort_flag = 1;
-      atomicCAS(status, 0, (kStatusTimeout << 24) | (where << 16) | (int)(blockIdx.x & 0xffff));
-      return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
-               "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-      "%29,%30,%31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
-//   K-major  (forward operands, activations): 8-row groups 1024 bytes apart  -> SBO = 1024, LBO unused (1)
-//   MN-major (backward weight operand): 64-column atoms 8192 bytes apart     -> LBO = 8192; 8 contraction rows
-//                                        are 1024 bytes apart                -> SBO = 1024
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= (uint64_t)1 << 46;   // version
-  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor for kind::f16: bf16 x bf16 -> fp32, A K-major, B K-major or MN-major.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
-}
 
 // Static tile schedule: bands of 16 token tiles; inside a band the column tile is the slow index, so the
 // CTAs running at one time share a few weight column tiles and one band of activations through L2.
@@ -458,8 +351,8 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-static int make_map(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* ptr, uint64_t inner,
-                    uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128,
+int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* ptr, uint64_t inner, uint64_t outer,
+                    uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
                     const char* what) {
   auto fn = encode_fn();
   if (fn == nullptr) return fail(MOLT_E_RUNTIME, "cuTensorMapEncodeTiled is not available from the driver");
@@ -467,21 +360,46 @@ static int make_map(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes,
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  (void)elem_bytes;
   CUresult rc = fn(map, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return fail(MOLT_E_RUNTIME, "cuTensorMapEncodeTiled(%s) failed with code %d", what, (int)rc);
   return MOLT_OK;
+}
+
+static int make_map(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* ptr, uint64_t inner,
+                    uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128,
+                    const char* what) {
+  (void)elem_bytes;
+  return make_tensor_map(map, dtype, ptr, inner, outer, row_stride_bytes, box_inner, box_outer,
+                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, what);
 }
 
 bool sm100_gemm_supported(const WeightView& w, int rank) {
   return w.blocksize == 64 && w.k % 64 == 0 && w.n % 64 == 0 && rank <= 64;
 }
 
+int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
+                    const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
+                    cudaStream_t s);
+
+// 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel (MOLT_B200_GEMM_VARIANT, read once; for testing)
+static int forced_variant() {
+  static int value = -1;
+  if (value < 0) {
+    const char* env = getenv("MOLT_B200_GEMM_VARIANT");
+    value = env != nullptr ? atoi(env) : 0;
+    if (value < 0 || value > 2) value = 0;
+  }
+  return value;
+}
+
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
                cudaStream_t s) {
+  // The CTA pair works on 256 token rows at a time; up to 128 tokens the single-CTA kernel wastes nothing.
+  const int variant = forced_variant();
+  if (variant == 2 || (variant == 0 && m > 128))
+    return sm100_gemm_pair(backward, w, absmax_f32, in, low, ext, rp, out, m, s);
   if (!sm100_gemm_supported(w, rp)) return fail(MOLT_E_CAPABILITY, "tcgen05 GEMM: unsupported shape");
   const long long contraction = backward ? w.n : w.k;
   const long long out_cols = backward ? w.k : w.n;

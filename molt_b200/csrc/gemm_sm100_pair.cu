@@ -1,0 +1,554 @@
+// CTA-pair (cta_group::2) tcgen05 GEMM with the NF4 decode fused in front of the tensor core.
+//
+//   forward : out[m, n] = in[m, k] . deq(W)[n, k]^T + low[m, r] . ext[n, r]^T        contraction over k
+//   backward: out[m, k] = in[m, n] . deq(W)[n, k]   + low[m, r] . ext[r, k]          contraction over n
+//
+// Two CTAs on neighbouring SMs form a cluster and share one UMMA of shape 256 x 256 x 16: each CTA owns 128 token
+// rows (its A operand and its 128 x 256 fp32 accumulator in TMEM) and supplies one half of the B operand, i.e. it
+// decodes only 128 weight segments per 64-wide contraction block while the tensor cores of both SMs consume the
+// whole 256-wide tile.  Compared with a single-CTA tile this halves the decode work and the shared-memory operand
+// traffic per FLOP.
+//
+// Per CTA: a TMA ring (activation tile + 4 KB of packed codes per stage) runs several blocks ahead of a
+// separate ring of decoded B half-tiles, so the global-memory latency is not serialised with the decode.
+// Decode: one 8-byte shared-memory lookup per packed byte returns both fp32 codebook values (table replicated
+// per bank pair, conflict free), multiplied by the fp32 absmax and rounded once to bf16 -- the bits of the
+// standalone dequantiser.  The leader CTA's MMA warp issues the pair MMA and signals both CTAs with
+// tcgen05.commit; decoders and epilogue warps of the second CTA signal the leader with remote mbarrier arrives.
+// All waits are bounded (status word + clean exit), and TMEM is released after a cluster barrier.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <stdlib.h>
+
+#include "internal.h"
+#include "sm100_ptx.cuh"
+
+namespace molt {
+namespace pair {
+
+constexpr int BM = 128;            // token rows per CTA (256 per pair)
+constexpr int BN = 256;            // output columns per pair tile
+constexpr int BNH = 128;           // B rows decoded per CTA
+constexpr int BK = 64;
+constexpr int kEpilogueWarps = 4;
+constexpr int kDecodeWarps = 8;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kFirstDecodeWarp = 6;
+constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;  // 448
+
+constexpr uint32_t kTileABytes = BM * BK * 2;          // 16384
+constexpr uint32_t kPackedBytes = BNH * BK / 2;        // 4096
+constexpr uint32_t kLoadStageBytes = kTileABytes + kPackedBytes;  // 20480
+constexpr uint32_t kTileBBytes = BNH * BK * 2;         // 16384
+constexpr uint32_t kStoreBytes = BM * 64 * 2;          // 16384
+constexpr uint32_t kLutBytes = 256 * 16 * 8;           // 32768: [byte][16 copies] of float2
+constexpr uint32_t smem_bytes(int load_stages, int b_stages, int store_bufs) {
+  return load_stages * kLoadStageBytes + b_stages * kTileBBytes + store_bufs * kStoreBytes + kLutBytes +
+         256 /*barriers*/ + 1024 /*alignment*/;
+}
+
+struct Params {
+  const float* absmax;   // fp32 [n * k / 64]
+  int32_t* status;
+  long long m, n, k;
+  int num_kb;
+  int ext_steps;         // rp / 16, 0 = no low-rank block
+  int tiles_m, tiles_n;  // pair tiles: 256 tokens x 256 columns
+  int nibble_high_first;
+  int debug;             // timing experiments only: 1 = skip decode, 2 = skip MMA issue, 4 = skip epilogue stores
+  float codebook[16];
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(local_smem_addr), "r"(rank));
+  return out;
+}
+// Remote arrive with the default (CTA-scope release) semantics.  A cluster-scope release here was measured to
+// cost several hundred nanoseconds per arrive; the data handed over is made visible to its only reader, the
+// tensor core, by the fence.proxy.async each writer executes before arriving.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Barriers completed from the other CTA (remote arrives, tcgen05.commit of the leader) are waited on with the
+// ordinary CTA-scope try_wait.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  int32_t* status, int where) {
+  return mbar_wait(bar, parity, abort_flag, status, where);
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on one mbarrier (given by its shared::cluster address) when all MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar_addr)
+               : "memory");
+}
+// One commit that arrives on the barrier at the same shared-memory offset in both CTAs of the pair (a
+// tcgen05.commit multicast: it signals barriers only, it does not move data).
+__device__ __forceinline__ void umma_commit_both(uint32_t local_bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(local_bar_addr), "h"((unsigned short)3)
+               : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int kBand = 8;  // 8 pair tiles = 2048 tokens share the L2 while the weight columns stream by
+  const int band_tiles = kBand * tiles_n;
+  const int band = tile / band_tiles;
+  const int first_m = band * kBand;
+  int rows = tiles_m - first_m;
+  if (rows > kBand) rows = kBand;
+  const int inside = tile - band * band_tiles;
+  tn = inside / rows;
+  tm = first_m + inside % rows;
+}
+
+template <bool BACKWARD, int kLoadStages, int kBStages, int kStoreBufs>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_packed,
+                           const __grid_constant__ CUtensorMap map_low, const __grid_constant__ CUtensorMap map_ext,
+                           const __grid_constant__ CUtensorMap map_out, const __grid_constant__ Params p) {
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag_s;
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+  const uint32_t load0 = base;
+  const uint32_t btile0 = load0 + kLoadStages * kLoadStageBytes;
+  const uint32_t store0 = btile0 + kBStages * kTileBBytes;
+  const uint32_t lut0 = store0 + kStoreBufs * kStoreBytes;
+  const uint32_t bar0 = lut0 + kLutBytes;
+  float2* lut_ptr = reinterpret_cast<float2*>(base_ptr + (lut0 - base));
+  auto bar_ldfull = [&](int s) { return bar0 + 8u * s; };
+  // consumed[g % 8] completes when the MMAs of contraction block number g (counted per CTA across tiles) have
+  // finished reading their operands; ONE commit per block releases both the load stage and the B stage, in both
+  // CTAs.  Eight slots exceed either ring depth, so a waiter can never be lapped.
+  constexpr int kConsumedSlots = 8;
+  static_assert(kLoadStages < kConsumedSlots && kBStages < kConsumedSlots, "ring deeper than the consumed slots");
+  auto bar_consumed = [&](int g) { return bar0 + 8u * (kLoadStages + (g & (kConsumedSlots - 1))); };
+  auto bar_bfull = [&](int s) { return bar0 + 8u * (kLoadStages + kConsumedSlots + s); };          // used in the leader
+  auto bar_accfull = [&](int b) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + b); };
+  auto bar_accempty = [&](int b) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + 2 + b); };  // leader
+  const uint32_t bar_ext = bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + 4);
+  auto consumed_parity = [&](int g) { return (uint32_t)((g / kConsumedSlots) & 1); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  volatile int* abort_flag = &abort_flag_s;
+
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    for (int s = 0; s < kLoadStages; ++s) mbar_init(bar_ldfull(s), 1);
+    for (int g = 0; g < kConsumedSlots; ++g) mbar_init(bar_consumed(g), 1);
+    for (int s = 0; s < kBStages; ++s) mbar_init(bar_bfull(s), 2 * kDecodeWarps);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_accfull(b), 1);
+      mbar_init(bar_accempty(b), 2 * kEpilogueWarps);
+    }
+    mbar_init(bar_ext, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // byte -> (first element, second element) fp32 codebook values; 16 copies so that lane l reads bank pair l % 16
+  for (int i = threadIdx.x; i < 256 * 16; i += kThreads) {
+    const int byte = i >> 4;
+    const int lo = byte & 15, hi = byte >> 4;
+    lut_ptr[i] = p.nibble_high_first ? make_float2(p.codebook[hi], p.codebook[lo])
+                                     : make_float2(p.codebook[lo], p.codebook[hi]);
+  }
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_pairs = gridDim.x >> 1;
+  const int pair_id = blockIdx.x >> 1;
+  const int blocks_per_tile = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
+
+  if (warp == kProducerWarp) {
+    // ================= TMA producer (each CTA loads its own token rows and its own half of the codes) ==========
+    int s = 0;
+    int g = 0;   // running block number
+    bool ok = true;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int row0 = tm * 2 * BM + (int)rank * BM;
+      for (int kb = 0; kb < blocks_per_tile; ++kb, ++g) {
+        if (g >= kLoadStages)   // the block that used this load stage must have been consumed
+          ok = mbar_wait_cluster(bar_consumed(g - kLoadStages), consumed_parity(g - kLoadStages), abort_flag, p.status, 1);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t a_dst = load0 + s * kLoadStageBytes;
+          const uint32_t pk_dst = a_dst + kTileABytes;
+          if (kb < p.num_kb) {
+            const bool skip_pk = p.debug & 256, skip_a = p.debug & 512;
+            mbar_expect_tx(bar_ldfull(s), (skip_a ? 0u : kTileABytes) + (skip_pk ? 0u : kPackedBytes));
+            if (!skip_a) tma_load_2d(a_dst, &map_in, kb * BK, row0, bar_ldfull(s));
+            if (skip_pk) {
+            } else if (!BACKWARD) tma_load_2d(pk_dst, &map_packed, kb * (BK / 2), tn * BN + (int)rank * BNH, bar_ldfull(s));
+            else tma_load_2d(pk_dst, &map_packed, (tn * BN + (int)rank * BNH) / 2, kb * BK, bar_ldfull(s));
+          } else {
+            mbar_expect_tx(bar_ldfull(s), kTileABytes);
+            tma_load_2d(a_dst, &map_low, 0, row0, bar_ldfull(s));
+          }
+        }
+        __syncwarp();
+        if (++s == kLoadStages) s = 0;
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ================= MMA issuer (leader CTA only) =================
+    if (leader) {
+      constexpr uint32_t idesc = make_idesc(2 * BM, BN, BACKWARD ? 1 : 0);
+      int ls = 0, bs = 0, acc = 0, g = 0;
+      uint32_t lphase = 0, bphase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        ok = mbar_wait_cluster(bar_accempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < blocks_per_tile; ++kb) {
+          ok = mbar_wait(bar_ldfull(ls), lphase, abort_flag, p.status, 3) &&
+               mbar_wait_cluster(bar_bfull(bs), bphase, abort_flag, p.status, 4);
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_addr = load0 + ls * kLoadStageBytes;
+            const uint32_t b_addr = btile0 + bs * kTileBBytes;
+            const uint64_t a_desc = make_desc(a_addr, 16, 1024);
+            const uint64_t b_desc = BACKWARD ? make_desc(b_addr, 8192, 1024) : make_desc(b_addr, 16, 1024);
+            const int steps = kb < p.num_kb ? BK / 16 : p.ext_steps;
+            for (int ks = 0; ks < steps && !(p.debug & 2); ++ks) {
+              const uint64_t a_k = a_desc + (uint64_t)(ks * 2);
+              const uint64_t b_k = b_desc + (uint64_t)(BACKWARD ? ks * 128 : ks * 2);
+              umma_bf16_pair(d_tmem, a_k, b_k, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            }
+            // one commit releases this block's load stage and B stage in both CTAs once the MMAs have read them
+            umma_commit_both(bar_consumed(g));
+            if (kb == blocks_per_tile - 1) umma_commit_both(bar_accfull(acc));
+          }
+          ++g;
+          __syncwarp();
+          if (++ls == kLoadStages) { ls = 0; lphase ^= 1u; }
+          if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp >= kFirstDecodeWarp) {
+    // ================= NF4 decoders: 256 threads, half a 64-element segment each =================
+    const int dt = threadIdx.x - kFirstDecodeWarp * 32;
+    const uint32_t lut_lane = lut0 + (uint32_t)(lane & 15) * 8u;
+    const long long kblocks_per_row = p.k / 64;
+    const uint32_t bfull_remote_base = map_to_cta(bar_bfull(0), 0);
+    int ls = 0, bs = 0, g = 0;
+    uint32_t lphase = 0, ext_phase = 0;
+    bool ok = true;
+    // Segment geometry of this thread (the same for every contraction block).
+    const int h = dt & 1;
+    const int seg_i = dt >> 1;                       // forward: B row inside the CTA's half tile
+    const int seg_j = (dt >> 1) & 63, seg_a = dt >> 7;   // backward: contraction row, 64-column atom
+    const uint32_t src_off = !BACKWARD ? (uint32_t)seg_i * 32u + (uint32_t)h * 16u
+                                       : (uint32_t)seg_j * 64u +
+                                             ((((uint32_t)(2 * seg_a + h)) ^ (((uint32_t)seg_j >> 1) & 3u)) << 4);
+    const uint32_t dst_off = !BACKWARD ? (uint32_t)seg_i * 128u : (uint32_t)seg_a * 8192u + (uint32_t)seg_j * 128u;
+    const uint32_t swz = (dst_off >> 7) & 7u;
+    constexpr int kPrefetch = 4;   // absmax values are fetched this many blocks ahead of their use
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int col0 = tn * BN + (int)rank * BNH;   // first B row (forward: weight row; backward: weight column)
+      // forward : absmax[(col0 + i) * kpr + kb]            backward: absmax[(kb * 64 + j) * kpr + col0 / 64 + a]
+      const float* scale_ptr;
+      long long scale_step;
+      bool scale_ok;
+      if (!BACKWARD) {
+        const long long row = (long long)col0 + seg_i;
+        scale_ok = row < p.n;
+        scale_ptr = p.absmax + (scale_ok ? row : 0) * kblocks_per_row;
+        scale_step = 1;
+      } else {
+        const long long colblk = (long long)(col0 >> 6) + seg_a;
+        scale_ok = colblk < kblocks_per_row;
+        scale_ptr = p.absmax + (long long)seg_j * kblocks_per_row + (scale_ok ? colblk : 0);
+        scale_step = (long long)BK * kblocks_per_row;
+      }
+      auto load_scale = [&](int kb) -> float {
+        return (kb < p.num_kb && scale_ok) ? __ldg(scale_ptr + (long long)kb * scale_step) : 0.f;
+      };
+      float cur[kPrefetch];
+#pragma unroll
+      for (int u = 0; u < kPrefetch; ++u) cur[u] = load_scale(u);
+      for (int kb0 = 0; kb0 < blocks_per_tile && ok; kb0 += kPrefetch) {
+        float nxt[kPrefetch];
+#pragma unroll
+        for (int u = 0; u < kPrefetch; ++u) nxt[u] = load_scale(kb0 + kPrefetch + u);
+#pragma unroll
+        for (int u = 0; u < kPrefetch; ++u) {
+          const int kb = kb0 + u;
+          if (kb >= blocks_per_tile || !ok) continue;
+          const float scale = cur[u];
+          ok = mbar_wait(bar_ldfull(ls), lphase, abort_flag, p.status, 5);
+          if (ok && g >= kBStages)   // the block that used this B stage must have been consumed
+            ok = mbar_wait_cluster(bar_consumed(g - kBStages), consumed_parity(g - kBStages), abort_flag, p.status, 6);
+          if (!ok) continue;
+          const uint32_t bt = btile0 + bs * kTileBBytes;
+          if (kb < p.num_kb && (p.debug & 1)) {
+          } else if (kb < p.num_kb) {
+            const uint32_t pk = load0 + ls * kLoadStageBytes + kTileABytes + src_off;
+            uint32_t words[4];
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3]) : "r"(pk));
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t out[4];
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const uint32_t byte = __byte_perm(words[c], 0u, 0x4440u + (uint32_t)b);
+                float2 codes;
+                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(codes.x), "=f"(codes.y) : "r"(lut_lane + byte * 128u));
+                out[b] = pack_bf16x2(__fmul_rn(codes.x, scale), __fmul_rn(codes.y, scale));
+              }
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + dst_off + ((((uint32_t)(4 * h + c)) ^ swz) << 4)),
+                           "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3])
+                           : "memory");
+            }
+            fence_proxy_async();
+          } else {
+            // low-rank block: this CTA's half of the ready-made B operand comes by TMA into the B stage
+            if (dt == 0) {
+              if (!BACKWARD) {
+                mbar_expect_tx(bar_ext, kTileBBytes);
+                tma_load_2d(bt, &map_ext, 0, col0, bar_ext);
+              } else {
+                mbar_expect_tx(bar_ext, 2u * (uint32_t)p.ext_steps * 16u * 128u);
+                tma_load_2d(bt, &map_ext, col0, 0, bar_ext);
+                tma_load_2d(bt + 8192u, &map_ext, col0 + 64, 0, bar_ext);
+              }
+            }
+            ok = mbar_wait(bar_ext, ext_phase, abort_flag, p.status, 7);
+            ext_phase ^= 1u;
+            if (!ok) continue;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive_remote(bfull_remote_base + 8u * (uint32_t)bs);
+          ++g;
+          if (++ls == kLoadStages) { ls = 0; lphase ^= 1u; }
+          if (++bs == kBStages) bs = 0;
+        }
+#pragma unroll
+        for (int u = 0; u < kPrefetch; ++u) cur[u] = nxt[u];
+      }
+    }
+  } else {
+    // ================= epilogue: TMEM -> bf16 -> shared -> TMA store (own 128 token rows) =================
+    const int row = warp * 32 + lane;
+    const uint32_t accempty_remote_base = map_to_cta(bar_accempty(0), 0);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int store_buf = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int row0 = tm * 2 * BM + (int)rank * BM;
+      ok = mbar_wait_cluster(bar_accfull(acc), acc_phase, abort_flag, p.status, 8);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)acc * BN;
+      for (int cg = 0; cg < BN / 64 && !(p.debug & 4); ++cg) {
+        const uint32_t stage_addr = store0 + (uint32_t)store_buf * kStoreBytes;
+        // the store that last read this staging buffer must have finished reading it
+        if (threadIdx.x == 0) {
+          if (kStoreBufs == 2) tma_store_wait_read<1>();
+          else tma_store_wait_read<0>();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint32_t v0[32], v1[32];
+        tmem_ld32(t_row + (uint32_t)cg * 64u, v0);
+        tmem_ld32(t_row + (uint32_t)cg * 64u + 32u, v1);
+        tmem_ld_wait();
+        const uint32_t dst_row = stage_addr + (uint32_t)row * 128u;
+        const uint32_t swz = (uint32_t)row & 7u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t o0 = pack_bf16x2(__uint_as_float(v0[c * 8 + 0]), __uint_as_float(v0[c * 8 + 1]));
+          const uint32_t o1 = pack_bf16x2(__uint_as_float(v0[c * 8 + 2]), __uint_as_float(v0[c * 8 + 3]));
+          const uint32_t o2 = pack_bf16x2(__uint_as_float(v0[c * 8 + 4]), __uint_as_float(v0[c * 8 + 5]));
+          const uint32_t o3 = pack_bf16x2(__uint_as_float(v0[c * 8 + 6]), __uint_as_float(v0[c * 8 + 7]));
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + (((uint32_t)c ^ swz) << 4)), "r"(o0),
+                       "r"(o1), "r"(o2), "r"(o3)
+                       : "memory");
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t o0 = pack_bf16x2(__uint_as_float(v1[c * 8 + 0]), __uint_as_float(v1[c * 8 + 1]));
+          const uint32_t o1 = pack_bf16x2(__uint_as_float(v1[c * 8 + 2]), __uint_as_float(v1[c * 8 + 3]));
+          const uint32_t o2 = pack_bf16x2(__uint_as_float(v1[c * 8 + 4]), __uint_as_float(v1[c * 8 + 5]));
+          const uint32_t o3 = pack_bf16x2(__uint_as_float(v1[c * 8 + 6]), __uint_as_float(v1[c * 8 + 7]));
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst_row + (((uint32_t)(c + 4) ^ swz) << 4)),
+                       "r"(o0), "r"(o1), "r"(o2), "r"(o3)
+                       : "memory");
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 0) {
+          if (row0 < p.m) tma_store_2d(&map_out, stage_addr, tn * BN + cg * 64, row0);
+          tma_store_commit();
+        }
+        if (kStoreBufs == 2) store_buf ^= 1;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(accempty_remote_base + 8u * (uint32_t)acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (threadIdx.x == 0) tma_store_wait_all();
+  }
+
+  // ---- teardown ----
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA releases TMEM or exits while the other may still signal it or use its operands
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+}  // namespace pair
+
+// ---- host side -----------------------------------------------------------------------------------------
+int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* ptr, uint64_t inner, uint64_t outer,
+                    uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
+                    const char* what);
+
+int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
+                    const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
+                    cudaStream_t s) {
+  using namespace pair;
+  if (!sm100_gemm_supported(w, rp)) return fail(MOLT_E_CAPABILITY, "tcgen05 GEMM: unsupported shape");
+  const long long contraction = backward ? w.n : w.k;
+  const long long out_cols = backward ? w.k : w.n;
+  CUtensorMap map_in, map_packed, map_low, map_ext, map_out;
+  if (int rc = make_tensor_map(&map_in, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, in, contraction, m, contraction * 2, BK, BM,
+                               CU_TENSOR_MAP_SWIZZLE_128B, "activations"))
+    return rc;
+  if (!backward) {
+    if (int rc = make_tensor_map(&map_packed, CU_TENSOR_MAP_DATA_TYPE_UINT8, w.packed, w.k / 2, w.n, w.k / 2, BK / 2,
+                                 BNH, CU_TENSOR_MAP_SWIZZLE_NONE, "packed weight"))
+      return rc;
+  } else {
+    if (int rc = make_tensor_map(&map_packed, CU_TENSOR_MAP_DATA_TYPE_UINT8, w.packed, w.k / 2, w.n, w.k / 2, BNH / 2,
+                                 BK, CU_TENSOR_MAP_SWIZZLE_64B, "packed weight"))
+      return rc;
+  }
+  const bool has_low = low != nullptr && ext != nullptr && rp > 0;
+  if (has_low) {
+    if (int rc = make_tensor_map(&map_low, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, low, 64, m, 128, 64, BM,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, "low-rank input"))
+      return rc;
+    if (!backward) {
+      if (int rc = make_tensor_map(&map_ext, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ext, 64, w.n, 128, 64, BNH,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, "scaled LoRA B"))
+        return rc;
+    } else {
+      if (int rc = make_tensor_map(&map_ext, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ext, w.k, rp, w.k * 2, 64, rp,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, "LoRA A"))
+        return rc;
+    }
+  } else {
+    map_low = map_in;
+    map_ext = map_in;
+  }
+  if (int rc = make_tensor_map(&map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, out_cols, m, out_cols * 2, 64, BM,
+                               CU_TENSOR_MAP_SWIZZLE_128B, "output"))
+    return rc;
+
+  Params p;
+  p.absmax = absmax_f32;
+  p.status = device_status_word();
+  if (p.status == nullptr) return fail(MOLT_E_RUNTIME, "tcgen05 GEMM: no device status word");
+  p.m = m;
+  p.n = w.n;
+  p.k = w.k;
+  p.num_kb = (int)(contraction / BK);
+  p.ext_steps = has_low ? rp / 16 : 0;
+  p.tiles_m = (int)((m + 2 * BM - 1) / (2 * BM));
+  p.tiles_n = (int)((out_cols + BN - 1) / BN);
+  p.nibble_high_first = w.nibble_order == MOLT_NIBBLE_HIGH_FIRST ? 1 : 0;
+  {
+    const char* dbg = getenv("MOLT_B200_DEBUG");
+    p.debug = dbg != nullptr ? atoi(dbg) : 0;
+  }
+  for (int i = 0; i < 16; ++i) p.codebook[i] = w.codebook[i];
+
+  int variant = 0;
+  {
+    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = load/B stages (4,4), 1 = (4,6), 2 = (5,4), 3 = (3,7)
+    variant = env != nullptr ? atoi(env) : 0;
+    if (variant < 0 || variant > 3) variant = 0;
+  }
+  const long long tiles = (long long)p.tiles_m * p.tiles_n;
+  long long pairs = sm_count() / 2;
+  if (tiles < pairs) pairs = tiles;
+  const int grid = (int)pairs * 2;
+  static thread_local bool configured[64][2][4] = {};
+  int dev = 0;
+  MOLT_CUDA(cudaGetDevice(&dev));
+  const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0][variant];
+#define MOLT_PAIR_LAUNCH(BWD, LS, BS, SB)                                                                  \
+  do {                                                                                                     \
+    if (need_config)                                                                                       \
+      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB>,                          \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,                          \
+                                     (int)smem_bytes(LS, BS, SB)));                                        \
+    nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB><<<grid, kThreads, smem_bytes(LS, BS, SB), s>>>(            \
+        map_in, map_packed, map_low, map_ext, map_out, p);                                                 \
+  } while (0)
+#define MOLT_PAIR_DISPATCH(BWD)                             \
+  do {                                                      \
+    if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 4, 6, 1);       \
+    else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 5, 4, 1);  \
+    else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 3, 7, 1);  \
+    else MOLT_PAIR_LAUNCH(BWD, 4, 4, 2);                    \
+  } while (0)
+  if (backward) MOLT_PAIR_DISPATCH(true);
+  else MOLT_PAIR_DISPATCH(false);
+#undef MOLT_PAIR_DISPATCH
+#undef MOLT_PAIR_LAUNCH
+  if (need_config) configured[dev][backward ? 1 : 0][variant] = true;
+  return launch_status("nf4_gemm_sm100_pair_kernel");
+}
+
+}  // namespace molt
