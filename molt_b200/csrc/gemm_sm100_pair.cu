@@ -56,9 +56,22 @@ struct Params {
   int ext_steps;         // rp / 16, 0 = no low-rank block
   int tiles_m, tiles_n;  // pair tiles: 256 tokens x 256 columns
   int nibble_high_first;
+  unsigned long long* trace;   // optional [2 CTAs][4 roles][256 events] timestamps (ns) for pipeline analysis
   int debug;             // timing experiments only: 1 = skip decode, 2 = skip MMA issue, 4 = skip epilogue stores
   float codebook[16];
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// role: 0 producer (TMA issued), 1 MMA (issued), 2 decoder warp 0 (waits done), 3 decoder warp 0 (arrived)
+#define MOLT_TRACE(role, index)                                                                       \
+  do {                                                                                                \
+    if (p.trace != nullptr && blockIdx.x < 2 && (index) < 256)                                        \
+      p.trace[(blockIdx.x * 4 + (role)) * 256 + (index)] = global_ns();                               \
+  } while (0)
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -81,6 +94,11 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   int32_t* status, int where) {
   return mbar_wait(bar, parity, abort_flag, status, where);
+}
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
 }
 __device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                uint32_t accumulate) {
@@ -217,6 +235,9 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
             mbar_expect_tx(bar_ldfull(s), kTileABytes);
             tma_load_2d(a_dst, &map_low, 0, row0, bar_ldfull(s));
           }
+#ifdef MOLT_PAIR_TRACE
+          MOLT_TRACE(0, g);
+#endif
         }
         __syncwarp();
         if (++s == kLoadStages) s = 0;
@@ -226,6 +247,12 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     // ================= MMA issuer (leader CTA only) =================
     if (leader) {
       constexpr uint32_t idesc = make_idesc(2 * BM, BN, BACKWARD ? 1 : 0);
+      // low descriptor words of stage 0: start address and leading byte offset (K-major: unused, 16; MN-major: 8192)
+      const uint32_t a_lo0 = ((load0 >> 4) & 0x3fffu) | (1u << 16);
+      const uint32_t b_lo0 = ((btile0 >> 4) & 0x3fffu) | ((BACKWARD ? (8192u >> 4) : 1u) << 16);
+      // high word: stride byte offset 1024, descriptor version 1, 128-byte swizzle
+      constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kBStep = BACKWARD ? 128u : 2u;   // 16 contraction elements: 2048 bytes MN-major, 32 bytes K-major
       int ls = 0, bs = 0, acc = 0, g = 0;
       uint32_t lphase = 0, bphase = 0, acc_phase = 0;
       bool ok = true;
@@ -234,25 +261,35 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+        // This loop is the serial heart of the kernel (one thread feeds the tensor cores of two SMs), so it is
+        // kept as short as possible: descriptors are a constant high word plus a low word that advances with
+        // the stage and the 16-element step.
         for (int kb = 0; kb < blocks_per_tile; ++kb) {
           ok = mbar_wait(bar_ldfull(ls), lphase, abort_flag, p.status, 3) &&
                mbar_wait_cluster(bar_bfull(bs), bphase, abort_flag, p.status, 4);
           if (!ok) break;
           tc_fence_after();
           if (lane == 0) {
-            const uint32_t a_addr = load0 + ls * kLoadStageBytes;
-            const uint32_t b_addr = btile0 + bs * kTileBBytes;
-            const uint64_t a_desc = make_desc(a_addr, 16, 1024);
-            const uint64_t b_desc = BACKWARD ? make_desc(b_addr, 8192, 1024) : make_desc(b_addr, 16, 1024);
-            const int steps = kb < p.num_kb ? BK / 16 : p.ext_steps;
-            for (int ks = 0; ks < steps && !(p.debug & 2); ++ks) {
-              const uint64_t a_k = a_desc + (uint64_t)(ks * 2);
-              const uint64_t b_k = b_desc + (uint64_t)(BACKWARD ? ks * 128 : ks * 2);
-              umma_bf16_pair(d_tmem, a_k, b_k, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            const uint32_t a_lo = a_lo0 + (uint32_t)ls * (kLoadStageBytes >> 4);
+            const uint32_t b_lo = b_lo0 + (uint32_t)bs * (kTileBBytes >> 4);
+            if (kb < p.num_kb) {
+              if (!(p.debug & 2)) {
+                umma_bf16_pair(d_tmem, desc64(a_lo, desc_hi), desc64(b_lo, desc_hi), idesc, kb > 0 ? 1u : 0u);
+#pragma unroll
+                for (int ks = 1; ks < BK / 16; ++ks)
+                  umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc, 1u);
+              }
+            } else {
+              for (int ks = 0; ks < p.ext_steps; ++ks)
+                umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc,
+                               (kb > 0 || ks > 0) ? 1u : 0u);
             }
             // one commit releases this block's load stage and B stage in both CTAs once the MMAs have read them
             umma_commit_both(bar_consumed(g));
             if (kb == blocks_per_tile - 1) umma_commit_both(bar_accfull(acc));
+#ifdef MOLT_PAIR_TRACE
+            MOLT_TRACE(1, g);
+#endif
           }
           ++g;
           __syncwarp();
@@ -319,23 +356,32 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           if (ok && g >= kBStages)   // the block that used this B stage must have been consumed
             ok = mbar_wait_cluster(bar_consumed(g - kBStages), consumed_parity(g - kBStages), abort_flag, p.status, 6);
           if (!ok) continue;
+#ifdef MOLT_PAIR_TRACE
+          if (dt == 0) MOLT_TRACE(2, g);
+#endif
           const uint32_t bt = btile0 + bs * kTileBBytes;
           if (kb < p.num_kb && (p.debug & 1)) {
           } else if (kb < p.num_kb) {
             const uint32_t pk = load0 + ls * kLoadStageBytes + kTileABytes + src_off;
             uint32_t words[4];
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3]) : "r"(pk));
+                         : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3]) : "r"(pk) : "memory");
+            // 16 table lookups (independent, issued back to back), then 32 multiplies, 16 roundings, 4 stores
+            float2 codes[16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const uint32_t byte = __byte_perm(words[c], 0u, 0x4440u + (uint32_t)b);
+                asm("ld.shared.v2.f32 {%0,%1}, [%2];"
+                    : "=f"(codes[c * 4 + b].x), "=f"(codes[c * 4 + b].y) : "r"(lut_lane + byte * 128u));
+              }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
               uint32_t out[4];
 #pragma unroll
-              for (int b = 0; b < 4; ++b) {
-                const uint32_t byte = __byte_perm(words[c], 0u, 0x4440u + (uint32_t)b);
-                float2 codes;
-                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(codes.x), "=f"(codes.y) : "r"(lut_lane + byte * 128u));
-                out[b] = pack_bf16x2(__fmul_rn(codes.x, scale), __fmul_rn(codes.y, scale));
-              }
+              for (int b = 0; b < 4; ++b)
+                out[b] = pack_bf16x2(__fmul_rn(codes[c * 4 + b].x, scale), __fmul_rn(codes[c * 4 + b].y, scale));
               asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + dst_off + ((((uint32_t)(4 * h + c)) ^ swz) << 4)),
                            "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3])
                            : "memory");
@@ -359,6 +405,9 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           }
           __syncwarp();
           if (lane == 0) mbar_arrive_remote(bfull_remote_base + 8u * (uint32_t)bs);
+#ifdef MOLT_PAIR_TRACE
+          if (dt == 0) MOLT_TRACE(3, g);
+#endif
           ++g;
           if (++ls == kLoadStages) { ls = 0; lphase ^= 1u; }
           if (++bs == kBStages) bs = 0;
@@ -510,6 +559,8 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
   {
     const char* dbg = getenv("MOLT_B200_DEBUG");
     p.debug = dbg != nullptr ? atoi(dbg) : 0;
+    const char* tr = getenv("MOLT_B200_TRACE_PTR");   // device pointer (decimal) of a 16 KB trace buffer
+    p.trace = tr != nullptr ? reinterpret_cast<unsigned long long*>(strtoull(tr, nullptr, 10)) : nullptr;
   }
   for (int i = 0; i < 16; ++i) p.codebook[i] = w.codebook[i];
 

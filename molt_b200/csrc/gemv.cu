@@ -7,9 +7,10 @@
 // is replicated once per lane (bank = lane, so lookups never conflict) and fed to mma.sync m16n8k16
 // with the tokens as the M dimension.  The MMA runs on the unscaled code values; each absmax block's
 // partial sum is multiplied by its fp32 absmax afterwards, so no per-element multiply is needed.
+// Packed codes are fetched two chunks ahead and the absmax data one chunk ahead of their use.
 // K-slices are summed in warp order through shared memory (deterministic).  When K needs more warps
-// than a CTA holds, CTAs of different K-groups exchange fp32 partials through the workspace and the
-// last CTA to arrive at a chunk finishes it (an atomic ticket, nobody waits).
+// than a CTA holds, CTAs of different K-groups write fp32 partials to the workspace and a small second
+// kernel adds them, adds the low-rank term and rounds to bf16.
 #include "common.cuh"
 
 namespace molt {
@@ -31,7 +32,6 @@ struct GemvParams {
   int kgroups;
   int warps_per_cta;
   float* partial;           // [kgroups][16][n] fp32 (kgroups > 1)
-  unsigned* tickets;        // [n / 16] zero-initialised (kgroups > 1)
   __nv_bfloat16* y;         // [m, n]
 };
 
@@ -42,15 +42,48 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ float resolve_absmax(const GemvParams& p, long long blk) { return load_absmax(p.w, blk); }
+// Raw absmax data of one weight row for this warp's two blocks, fetched ahead of use.
+template <bool NESTED>
+struct RowScales;
+template <>
+struct RowScales<false> {
+  float2 v;
+  __device__ __forceinline__ void load(const GemvParams& p, long long row, int blk0, int nb) {
+    const long long blk = row * p.nblk + blk0;
+    const float* src = reinterpret_cast<const float*>(p.w.absmax) + blk;
+    if (nb == 2 && (blk & 1) == 0) v = __ldg(reinterpret_cast<const float2*>(src));
+    else v = make_float2(nb >= 1 ? __ldg(src) : 0.f, nb == 2 ? __ldg(src + 1) : 0.f);
+  }
+  __device__ __forceinline__ float get(const GemvParams&, const float*, int b) const { return b == 0 ? v.x : v.y; }
+};
+template <>
+struct RowScales<true> {
+  unsigned codes;   // two uint8 codes
+  float2 second;    // absmax2 of the two blocks
+  __device__ __forceinline__ void load(const GemvParams& p, long long row, int blk0, int nb) {
+    const long long blk = row * p.nblk + blk0;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.w.absmax) + blk;
+    if (nb == 2 && (blk & 1) == 0) codes = (unsigned)__ldg(reinterpret_cast<const unsigned short*>(src));
+    else codes = (nb >= 1 ? (unsigned)__ldg(src) : 0u) | (nb == 2 ? (unsigned)__ldg(src + 1) << 8 : 0u);
+    second.x = nb >= 1 ? __ldg(p.w.absmax2 + blk / p.w.block2) : 0.f;
+    second.y = nb == 2 ? __ldg(p.w.absmax2 + (blk + 1) / p.w.block2) : 0.f;
+  }
+  // code2[u8] * absmax2 + offset with separate multiply and add: the bits the dequantiser produces
+  __device__ __forceinline__ float get(const GemvParams& p, const float* code2_s, int b) const {
+    const unsigned c = b == 0 ? (codes & 0xffu) : (codes >> 8);
+    return __fadd_rn(__fmul_rn(code2_s[c], b == 0 ? second.x : second.y), p.w.offset);
+  }
+};
 
-__global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) nf4_gemv_kernel(GemvParams p) {
+template <bool NESTED>
+__global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  // [256 entries][32 lanes] bf16x2 pair table, then [2 buffers][warps][2 ntiles][32 lanes][4] partials, then T
+  // [256 entries][32 lanes] bf16x2 pair table, [2 buffers][warps][2 ntiles][32 lanes][4] partials, T, code2
   uint32_t* pair_lut = reinterpret_cast<uint32_t*>(smem_raw);
   float* red = reinterpret_cast<float*>(smem_raw + 256 * 32 * 4);
   const int warps = p.warps_per_cta;
   float* t_s = red + 2 * warps * 256;  // [16][64]
+  float* code2_s = t_s + 16 * 64;      // [256]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int kgroup = blockIdx.y;
@@ -63,11 +96,13 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) nf4_gemv_kernel(GemvPar
     pair_lut[i] = pack_bf16x2(p.w.codebook[first], p.w.codebook[second]);
   }
   for (int i = threadIdx.x; i < 16 * 64; i += blockDim.x) t_s[i] = p.t != nullptr ? p.t[i] : 0.f;
+  if (NESTED)
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) code2_s[i] = p.w.code2[i];
 
   // ---- this warp's K-slice and its X fragments ----
-  const int slice = kgroup * warps + warp;             // global warp-slice index
+  const int slice = kgroup * warps + warp;
   const int blk0 = slice * kGemvBlocksPerWarp;
-  int nb = p.nblk - blk0;                              // blocks owned by this warp (0, 1 or 2)
+  int nb = p.nblk - blk0;
   if (slice >= p.warps_needed || nb < 0) nb = 0;
   if (nb > kGemvBlocksPerWarp) nb = kGemvBlocksPerWarp;
   uint32_t xa[kGemvBlocksPerWarp][4][4];
@@ -90,35 +125,52 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) nf4_gemv_kernel(GemvPar
   const int chunks = (int)(p.w.n / kGemvChunkRows);
   const uint8_t* wbase = p.w.packed + (long long)blk0 * 32 + t * 8;
 
-  auto load_chunk = [&](int chunk, uint2 (&dst)[2][kGemvBlocksPerWarp]) {
+  struct Chunk {
+    uint2 wq[2][kGemvBlocksPerWarp];   // packed codes: [n-tile][block]
+  };
+  auto load_codes = [&](int chunk, Chunk& dst) {
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       const long long row = (long long)chunk * kGemvChunkRows + nt * 8 + g;
 #pragma unroll
       for (int b = 0; b < kGemvBlocksPerWarp; ++b)
-        dst[nt][b] = (b < nb) ? __ldcs(reinterpret_cast<const uint2*>(wbase + row * row_bytes + b * 32))
-                              : make_uint2(0, 0);
+        dst.wq[nt][b] = (b < nb && chunk < chunks)
+                            ? __ldcs(reinterpret_cast<const uint2*>(wbase + row * row_bytes + b * 32))
+                            : make_uint2(0, 0);
     }
   };
+  auto load_scales = [&](int chunk, RowScales<NESTED> (&dst)[2][2]) {
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const long long row = (long long)chunk * kGemvChunkRows + nt * 8 + 2 * t + r;
+        dst[nt][r].load(p, chunk < chunks ? row : 0, blk0, chunk < chunks ? nb : 0);
+      }
+  };
 
-  uint2 cur[2][kGemvBlocksPerWarp], nxt[2][kGemvBlocksPerWarp];
+  // software pipeline: codes two chunks ahead, scales one chunk ahead
+  Chunk c0, c1, c2;
+  RowScales<NESTED> s0[2][2], s1[2][2];
   int chunk = blockIdx.x;
-  if (chunk < chunks) load_chunk(chunk, cur);
+  const int stride = gridDim.x;
+  load_codes(chunk, c0);
+  load_codes(chunk + stride, c1);
+  load_scales(chunk, s0);
   int buf = 0;
-  for (; chunk < chunks; chunk += gridDim.x) {
-    const int next = chunk + gridDim.x;
-    if (next < chunks) load_chunk(next, nxt);
+  for (; chunk < chunks; chunk += stride) {
+    load_codes(chunk + 2 * stride, c2);
+    load_scales(chunk + stride, s1);
     float acc[2][4];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
-      const long long n_lo = (long long)chunk * kGemvChunkRows + nt * 8 + 2 * t;  // rows of c0/c2 ; +1 for c1/c3
 #pragma unroll
       for (int b = 0; b < kGemvBlocksPerWarp; ++b) {
         if (b < nb) {
           float part[4] = {0.f, 0.f, 0.f, 0.f};
-          const uint32_t words[2] = {cur[nt][b].x, cur[nt][b].y};
+          const uint32_t words[2] = {c0.wq[nt][b].x, c0.wq[nt][b].y};
 #pragma unroll
           for (int wi = 0; wi < 2; ++wi) {
             const uint32_t wd = words[wi];
@@ -129,16 +181,16 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) nf4_gemv_kernel(GemvPar
             mma_16816(part, xa[b][wi * 2], p0, p1);
             mma_16816(part, xa[b][wi * 2 + 1], p2, p3);
           }
-          const float s0 = resolve_absmax(p, n_lo * p.nblk + blk0 + b);
-          const float s1 = resolve_absmax(p, (n_lo + 1) * p.nblk + blk0 + b);
-          acc[nt][0] = fmaf(part[0], s0, acc[nt][0]);
-          acc[nt][1] = fmaf(part[1], s1, acc[nt][1]);
-          acc[nt][2] = fmaf(part[2], s0, acc[nt][2]);
-          acc[nt][3] = fmaf(part[3], s1, acc[nt][3]);
+          const float sc0 = s0[nt][0].get(p, code2_s, b);   // row 2t   : accumulator columns c0, c2
+          const float sc1 = s0[nt][1].get(p, code2_s, b);   // row 2t+1 : accumulator columns c1, c3
+          acc[nt][0] = fmaf(part[0], sc0, acc[nt][0]);
+          acc[nt][1] = fmaf(part[1], sc1, acc[nt][1]);
+          acc[nt][2] = fmaf(part[2], sc0, acc[nt][2]);
+          acc[nt][3] = fmaf(part[3], sc1, acc[nt][3]);
         }
       }
     }
-    // ---- sum the K-slices of this CTA (warp order) ----
+    // ---- sum the K-slices of this CTA in warp order (double-buffered, one barrier per chunk) ----
     float* my_red = red + (buf * warps + warp) * 256;
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
@@ -146,37 +198,16 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) nf4_gemv_kernel(GemvPar
           make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
     __syncthreads();
     if (threadIdx.x < 256) {
-      // output element: row r (0..15) of the chunk, token tok (0..15)
-      const int r = threadIdx.x & 15, tok = threadIdx.x >> 4;
+      const int r = threadIdx.x & 15, tok = threadIdx.x >> 4;   // row inside the chunk, token
       const int nt = r >> 3, rr = r & 7;
       const int src_lane = (tok & 7) * 4 + (rr >> 1);
       const int src_c = (rr & 1) + (tok >> 3) * 2;
       float sum = 0.f;
       for (int wv = 0; wv < warps; ++wv) sum += red[((buf * warps + wv) * 64 + nt * 32 + src_lane) * 4 + src_c];
       const long long n = (long long)chunk * kGemvChunkRows + r;
-      bool finish = true;
       if (p.kgroups > 1) {
         p.partial[((long long)kgroup * 16 + tok) * p.w.n + n] = sum;
-        __threadfence();
-        __shared__ unsigned last_flag[2];
-        __syncwarp();
-        // 256 finishing threads = 8 full warps; one ticket per chunk taken by thread 0 after a CTA-local barrier
-        asm volatile("bar.sync 1, 256;\n" ::);
-        if (threadIdx.x == 0) {
-          const unsigned old = atomicAdd(p.tickets + chunk, 1u);
-          last_flag[buf] = (old == (unsigned)(p.kgroups - 1));
-          if (old == (unsigned)(p.kgroups - 1)) p.tickets[chunk] = 0;  // leave the tickets clean for the next call
-        }
-        asm volatile("bar.sync 1, 256;\n" ::);
-        finish = last_flag[buf] != 0;
-        if (finish) {
-          __threadfence();
-          sum = 0.f;
-          for (int kg = 0; kg < p.kgroups; ++kg)
-            sum += __ldcg(p.partial + ((long long)kg * 16 + tok) * p.w.n + n);
-        }
-      }
-      if (finish && tok < p.m) {
+      } else if (tok < p.m) {
         float lora = 0.f;
         for (int rk = 0; rk < p.rank; ++rk)
           lora += t_s[tok * 64 + rk] * __bfloat162float(__float2bfloat16_rn(p.scaling * p.lora_b[n * p.rank + rk]));
@@ -184,20 +215,37 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) nf4_gemv_kernel(GemvPar
       }
     }
     buf ^= 1;
+    c0 = c1;
+    c1 = c2;
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int b = 0; b < kGemvBlocksPerWarp; ++b) cur[nt][b] = nxt[nt][b];
+      for (int r = 0; r < 2; ++r) s0[nt][r] = s1[nt][r];
   }
 }
 
+// y[tok, n] = bf16(sum over K-groups of partial + low-rank term); only launched when K needed several CTAs.
+__global__ void gemv_finish_kernel(const float* __restrict__ partial, int kgroups, const float* __restrict__ t,
+                                   const float* __restrict__ lora_b, float scaling, int rank, int m, long long n,
+                                   __nv_bfloat16* __restrict__ y) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= (long long)m * n) return;
+  const int tok = (int)(idx / n);
+  const long long col = idx % n;
+  float sum = 0.f;
+  for (int kg = 0; kg < kgroups; ++kg) sum += partial[((long long)kg * 16 + tok) * n + col];
+  float lora = 0.f;
+  for (int rk = 0; rk < rank; ++rk)
+    lora += t[tok * 64 + rk] * __bfloat162float(__float2bfloat16_rn(scaling * lora_b[col * rank + rk]));
+  y[idx] = __float2bfloat16_rn(sum + lora);
+}
+
 // t[tok, r] = bf16(sum_k x[tok, k] * bf16(A[r, k])) as fp32, zero elsewhere in the [16, 64] tile.
-// One warp per (token, r).  Also clears the chunk tickets.
+// One warp per (token, r).
 __global__ void gemv_lowrank_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ a, int m, int rank,
-                                    long long k, float* __restrict__ t, unsigned* tickets, int ticket_count) {
+                                    long long k, float* __restrict__ t) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ticket_count; i += gridDim.x * blockDim.x) tickets[i] = 0;
   if (warp >= 16 * 64) return;
   const int tok = warp >> 6, r = warp & 63;
   float sum = 0.f;
@@ -215,11 +263,9 @@ size_t gemv_workspace_bytes(long long n, long long k) {
   const int nblk = (int)(k / 64);
   const int warps_needed = (nblk + kGemvBlocksPerWarp - 1) / kGemvBlocksPerWarp;
   const int kgroups = (warps_needed + kGemvMaxWarps - 1) / kGemvMaxWarps;
-  size_t bytes = 16 * 64 * sizeof(float);                         // T
-  bytes += (size_t)(n / kGemvChunkRows + 1) * sizeof(unsigned);   // tickets
-  bytes = (bytes + 255) & ~size_t(255);
+  size_t bytes = 16 * 64 * sizeof(float);  // T
   if (kgroups > 1) bytes += (size_t)kgroups * 16 * n * sizeof(float);
-  return bytes;
+  return bytes + 256;
 }
 
 int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_a, const float* lora_b, float scaling,
@@ -238,33 +284,40 @@ int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_
   p.warps_needed = (p.nblk + kGemvBlocksPerWarp - 1) / kGemvBlocksPerWarp;
   p.kgroups = (p.warps_needed + kGemvMaxWarps - 1) / kGemvMaxWarps;
   p.warps_per_cta = (p.warps_needed + p.kgroups - 1) / p.kgroups;
-  if (p.warps_per_cta < 8) p.warps_per_cta = 8;  // the finishing step uses 256 threads
+  if (p.warps_per_cta < 8) p.warps_per_cta = 8;  // the chunk reduction uses 256 threads
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   float* t = reinterpret_cast<float*>(ws);
-  unsigned* tickets = reinterpret_cast<unsigned*>(ws + 16 * 64 * sizeof(float));
-  const int ticket_count = (int)(w.n / kGemvChunkRows);
-  size_t head = 16 * 64 * sizeof(float) + (size_t)(ticket_count + 1) * sizeof(unsigned);
-  head = (head + 255) & ~size_t(255);
   p.t = t;
-  p.tickets = tickets;
-  p.partial = reinterpret_cast<float*>(ws + head);
+  p.partial = reinterpret_cast<float*>(ws + 16 * 64 * sizeof(float) + 256 - (16 * 64 * sizeof(float)) % 256);
   p.y = y;
-  gemv_lowrank_kernel<<<(16 * 64 * 32 + 255) / 256, 256, 0, s>>>(x, lora_a, m, rank, w.k, t, tickets, ticket_count);
+  gemv_lowrank_kernel<<<(16 * 64 * 32 + 255) / 256, 256, 0, s>>>(x, lora_a, m, rank, w.k, t);
   if (int rc = launch_status("gemv_lowrank_kernel")) return rc;
 
-  const size_t smem = 256 * 32 * 4 + (size_t)2 * p.warps_per_cta * 256 * 4 + 16 * 64 * 4;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(nf4_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    if (err != cudaSuccess) return fail(MOLT_E_RUNTIME, "cudaFuncSetAttribute(gemv): %s", cudaGetErrorString(err));
-    configured = true;
+  const size_t smem = 256 * 32 * 4 + (size_t)2 * p.warps_per_cta * 256 * 4 + 16 * 64 * 4 + 256 * 4;
+  const bool nested = w.absmax_kind == MOLT_ABSMAX_NESTED;
+  static thread_local bool configured[64][2] = {};
+  int dev = 0;
+  MOLT_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev][nested ? 1 : 0]) {
+    if (nested) MOLT_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    else MOLT_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    configured[dev][nested ? 1 : 0] = true;
   }
+  const int chunks = (int)(w.n / kGemvChunkRows);
   int gx = sm_count() / p.kgroups;
   if (gx < 1) gx = 1;
-  if (gx > ticket_count) gx = ticket_count;
+  if (gx > chunks) gx = chunks;
   dim3 grid((unsigned)gx, (unsigned)p.kgroups);
-  nf4_gemv_kernel<<<grid, p.warps_per_cta * 32, smem, s>>>(p);
-  return launch_status("nf4_gemv_kernel");
+  if (nested) nf4_gemv_kernel<true><<<grid, p.warps_per_cta * 32, smem, s>>>(p);
+  else nf4_gemv_kernel<false><<<grid, p.warps_per_cta * 32, smem, s>>>(p);
+  if (int rc = launch_status("nf4_gemv_kernel")) return rc;
+  if (p.kgroups > 1) {
+    const long long total = (long long)m * w.n;
+    gemv_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(p.partial, p.kgroups, t, lora_b, scaling, rank, m,
+                                                                       w.n, y);
+    return launch_status("gemv_finish_kernel");
+  }
+  return MOLT_OK;
 }
 
 }  // namespace molt
