@@ -43,6 +43,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     common = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS, "-Xcompiler", "-fPIC,-O3", "--expt-relaxed-constexpr"]
     if verbose:
         common += ["-Xptxas", "-v"]
+    common += os.environ.get("MOLT_B200_NVCC_FLAGS", "").split()  # e.g. -DMOLT_PAIR_TRACE for pipeline timelines
     jobs = []
     objects = []
     for name in SOURCES:

@@ -31,11 +31,12 @@ constexpr int BN = 256;            // output columns per pair tile
 constexpr int BNH = 128;           // B rows decoded per CTA
 constexpr int BK = 64;
 constexpr int kEpilogueWarps = 4;
-constexpr int kDecodeWarps = 8;
+constexpr int kDecodeGroups = 3;   // groups of four warps that take the contraction blocks in turn
+constexpr int kDecodeWarps = 4 * kDecodeGroups;
 constexpr int kProducerWarp = 4;
 constexpr int kMmaWarp = 5;
 constexpr int kFirstDecodeWarp = 6;
-constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;  // 448
+constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;
 
 constexpr uint32_t kTileABytes = BM * BK * 2;          // 16384
 constexpr uint32_t kPackedBytes = BNH * BK / 2;        // 4096
@@ -49,6 +50,7 @@ constexpr uint32_t smem_bytes(int load_stages, int b_stages, int store_bufs) {
 }
 
 struct Params {
+  const uint8_t* packed; // [n, k / 2] packed codes
   const float* absmax;   // fp32 [n * k / 64]
   int32_t* status;
   long long m, n, k;
@@ -176,7 +178,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     abort_flag_s = 0;
     for (int s = 0; s < kLoadStages; ++s) mbar_init(bar_ldfull(s), 1);
     for (int g = 0; g < kConsumedSlots; ++g) mbar_init(bar_consumed(g), 1);
-    for (int s = 0; s < kBStages; ++s) mbar_init(bar_bfull(s), 2 * kDecodeWarps);
+    for (int s = 0; s < kBStages; ++s) mbar_init(bar_bfull(s), 8);   // 4 warps of one group x 2 CTAs
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_accfull(b), 1);
       mbar_init(bar_accempty(b), 2 * kEpilogueWarps);
@@ -223,13 +225,11 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         if (!ok) break;
         if (lane == 0) {
           const uint32_t a_dst = load0 + s * kLoadStageBytes;
-          const uint32_t pk_dst = a_dst + kTileABytes;
           if (kb < p.num_kb) {
-            const bool skip_pk = p.debug & 256, skip_a = p.debug & 512;
-            mbar_expect_tx(bar_ldfull(s), (skip_a ? 0u : kTileABytes) + (skip_pk ? 0u : kPackedBytes));
-            if (!skip_a) tma_load_2d(a_dst, &map_in, kb * BK, row0, bar_ldfull(s));
-            if (skip_pk) {
-            } else if (!BACKWARD) tma_load_2d(pk_dst, &map_packed, kb * (BK / 2), tn * BN + (int)rank * BNH, bar_ldfull(s));
+            const uint32_t pk_dst = a_dst + kTileABytes;
+            mbar_expect_tx(bar_ldfull(s), kTileABytes + kPackedBytes);
+            tma_load_2d(a_dst, &map_in, kb * BK, row0, bar_ldfull(s));
+            if (!BACKWARD) tma_load_2d(pk_dst, &map_packed, kb * (BK / 2), tn * BN + (int)rank * BNH, bar_ldfull(s));
             else tma_load_2d(pk_dst, &map_packed, (tn * BN + (int)rank * BNH) / 2, kb * BK, bar_ldfull(s));
           } else {
             mbar_expect_tx(bar_ldfull(s), kTileABytes);
@@ -253,72 +253,91 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       // high word: stride byte offset 1024, descriptor version 1, 128-byte swizzle
       constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
       constexpr uint32_t kBStep = BACKWARD ? 128u : 2u;   // 16 contraction elements: 2048 bytes MN-major, 32 bytes K-major
-      int ls = 0, bs = 0, acc = 0, g = 0;
-      uint32_t lphase = 0, bphase = 0, acc_phase = 0;
-      bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        ok = mbar_wait_cluster(bar_accempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
-        // This loop is the serial heart of the kernel (one thread feeds the tensor cores of two SMs), so it is
-        // kept as short as possible: descriptors are a constant high word plus a low word that advances with
-        // the stage and the 16-element step.
-        for (int kb = 0; kb < blocks_per_tile; ++kb) {
-          ok = mbar_wait(bar_ldfull(ls), lphase, abort_flag, p.status, 3) &&
-               mbar_wait_cluster(bar_bfull(bs), bphase, abort_flag, p.status, 4);
+      // One thread runs this loop: it is the serial heart of the kernel (it feeds the tensor cores of two SMs),
+      // so it holds nothing but the wait, the four MMAs and the commit.
+      if (lane == 0) {
+        int ls = 0, bs = 0, acc = 0, g = 0;
+        uint32_t bphase = 0, acc_phase = 0;
+        bool ok = true;
+        for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+          ok = mbar_wait_cluster(bar_accempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2);
           if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
+          const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+          uint32_t accumulate = 0u;
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            // The decoders of both CTAs arrive on b_full only after their own activation tile has landed, so
+            // this one wait covers both operands in both CTAs.
+            ok = mbar_wait_cluster(bar_bfull(bs), bphase, abort_flag, p.status, 4);
+            if (!ok) break;
+            tc_fence_after();
             const uint32_t a_lo = a_lo0 + (uint32_t)ls * (kLoadStageBytes >> 4);
             const uint32_t b_lo = b_lo0 + (uint32_t)bs * (kTileBBytes >> 4);
-            if (kb < p.num_kb) {
-              if (!(p.debug & 2)) {
-                umma_bf16_pair(d_tmem, desc64(a_lo, desc_hi), desc64(b_lo, desc_hi), idesc, kb > 0 ? 1u : 0u);
+            umma_bf16_pair(d_tmem, desc64(a_lo, desc_hi), desc64(b_lo, desc_hi), idesc, accumulate);
 #pragma unroll
-                for (int ks = 1; ks < BK / 16; ++ks)
-                  umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc, 1u);
-              }
-            } else {
-              for (int ks = 0; ks < p.ext_steps; ++ks)
-                umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc,
-                               (kb > 0 || ks > 0) ? 1u : 0u);
-            }
+            for (int ks = 1; ks < BK / 16; ++ks)
+              umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc, 1u);
+            accumulate = 1u;
             // one commit releases this block's load stage and B stage in both CTAs once the MMAs have read them
             umma_commit_both(bar_consumed(g));
             if (kb == blocks_per_tile - 1) umma_commit_both(bar_accfull(acc));
 #ifdef MOLT_PAIR_TRACE
             MOLT_TRACE(1, g);
 #endif
+            ++g;
+            if (++ls == kLoadStages) ls = 0;
+            if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
           }
-          ++g;
-          __syncwarp();
-          if (++ls == kLoadStages) { ls = 0; lphase ^= 1u; }
-          if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
+          if (ok && p.ext_steps > 0) {   // the low-rank block
+            ok = mbar_wait_cluster(bar_bfull(bs), bphase, abort_flag, p.status, 4);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_lo = a_lo0 + (uint32_t)ls * (kLoadStageBytes >> 4);
+            const uint32_t b_lo = b_lo0 + (uint32_t)bs * (kTileBBytes >> 4);
+            for (int ks = 0; ks < p.ext_steps; ++ks)
+              umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc,
+                             (accumulate | (uint32_t)(ks > 0)));
+            umma_commit_both(bar_consumed(g));
+            umma_commit_both(bar_accfull(acc));
+            ++g;
+            if (++ls == kLoadStages) ls = 0;
+            if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
+          }
+          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
+      __syncwarp();
     }
   } else if (warp >= kFirstDecodeWarp) {
-    // ================= NF4 decoders: 256 threads, half a 64-element segment each =================
+    // ================= NF4 decoders =================
+    // Groups of four warps take the contraction blocks in turn (running block number modulo the group count),
+    // so the decode latency of one block overlaps the following blocks'.  Inside a group every thread expands one whole
+    // 64-element segment (one absmax) per block.
     const int dt = threadIdx.x - kFirstDecodeWarp * 32;
+    const int dwarp = dt >> 5;
+    const int grp = dwarp % kDecodeGroups;
+    const int u = (dwarp / kDecodeGroups) * 32 + lane;   // 0..127 inside the group
     const uint32_t lut_lane = lut0 + (uint32_t)(lane & 15) * 8u;
     const long long kblocks_per_row = p.k / 64;
     const uint32_t bfull_remote_base = map_to_cta(bar_bfull(0), 0);
-    int ls = 0, bs = 0, g = 0;
-    uint32_t lphase = 0, ext_phase = 0;
+    uint32_t ext_phase = 0;
     bool ok = true;
     // Segment geometry of this thread (the same for every contraction block).
-    const int h = dt & 1;
-    const int seg_i = dt >> 1;                       // forward: B row inside the CTA's half tile
-    const int seg_j = (dt >> 1) & 63, seg_a = dt >> 7;   // backward: contraction row, 64-column atom
-    const uint32_t src_off = !BACKWARD ? (uint32_t)seg_i * 32u + (uint32_t)h * 16u
-                                       : (uint32_t)seg_j * 64u +
-                                             ((((uint32_t)(2 * seg_a + h)) ^ (((uint32_t)seg_j >> 1) & 3u)) << 4);
-    const uint32_t dst_off = !BACKWARD ? (uint32_t)seg_i * 128u : (uint32_t)seg_a * 8192u + (uint32_t)seg_j * 128u;
+    const int seg_j = u & 63, seg_a = u >> 6;        // backward: contraction row, 64-column atom
+    uint32_t src_off0, src_off1;                     // the two 16-byte halves of the segment's packed codes
+    if (!BACKWARD) {
+      src_off0 = (uint32_t)u * 32u;
+      src_off1 = src_off0 + 16u;
+    } else {
+      const uint32_t x = ((uint32_t)seg_j >> 1) & 3u;   // 64-byte swizzle of the packed tile
+      src_off0 = (uint32_t)seg_j * 64u + ((((uint32_t)(2 * seg_a)) ^ x) << 4);
+      src_off1 = (uint32_t)seg_j * 64u + ((((uint32_t)(2 * seg_a + 1)) ^ x) << 4);
+    }
+    const uint32_t dst_off = !BACKWARD ? (uint32_t)u * 128u : (uint32_t)seg_a * 8192u + (uint32_t)seg_j * 128u;
     const uint32_t swz = (dst_off >> 7) & 7u;
-    constexpr int kPrefetch = 4;   // absmax values are fetched this many blocks ahead of their use
-    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+    constexpr int kPrefetch = 4;   // absmax values are fetched this many of the group's blocks ahead of their use
+    int g_tile = 0;                // running block number of the tile's first block
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, g_tile += blocks_per_tile) {
       int tm, tn;
       pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       const int col0 = tn * BN + (int)rank * BNH;   // first B row (forward: weight row; backward: weight column)
@@ -327,7 +346,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       long long scale_step;
       bool scale_ok;
       if (!BACKWARD) {
-        const long long row = (long long)col0 + seg_i;
+        const long long row = (long long)col0 + u;
         scale_ok = row < p.n;
         scale_ptr = p.absmax + (scale_ok ? row : 0) * kblocks_per_row;
         scale_step = 1;
@@ -340,56 +359,64 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       auto load_scale = [&](int kb) -> float {
         return (kb < p.num_kb && scale_ok) ? __ldg(scale_ptr + (long long)kb * scale_step) : 0.f;
       };
+      const int kb_first = ((grp - g_tile) % kDecodeGroups + kDecodeGroups) % kDecodeGroups;   // group's first block
       float cur[kPrefetch];
 #pragma unroll
-      for (int u = 0; u < kPrefetch; ++u) cur[u] = load_scale(u);
-      for (int kb0 = 0; kb0 < blocks_per_tile && ok; kb0 += kPrefetch) {
+      for (int q = 0; q < kPrefetch; ++q) cur[q] = load_scale(kb_first + kDecodeGroups * q);
+      for (int kb0 = kb_first; kb0 < blocks_per_tile && ok; kb0 += kDecodeGroups * kPrefetch) {
         float nxt[kPrefetch];
 #pragma unroll
-        for (int u = 0; u < kPrefetch; ++u) nxt[u] = load_scale(kb0 + kPrefetch + u);
+        for (int q = 0; q < kPrefetch; ++q) nxt[q] = load_scale(kb0 + kDecodeGroups * (kPrefetch + q));
 #pragma unroll
-        for (int u = 0; u < kPrefetch; ++u) {
-          const int kb = kb0 + u;
+        for (int q = 0; q < kPrefetch; ++q) {
+          const int kb = kb0 + kDecodeGroups * q;
           if (kb >= blocks_per_tile || !ok) continue;
-          const float scale = cur[u];
-          ok = mbar_wait(bar_ldfull(ls), lphase, abort_flag, p.status, 5);
+          const float scale = cur[q];
+          const int g = g_tile + kb;
+          const int ls = g % kLoadStages, bs = g % kBStages;
+          ok = mbar_wait(bar_ldfull(ls), (uint32_t)((g / kLoadStages) & 1), abort_flag, p.status, 5);
           if (ok && g >= kBStages)   // the block that used this B stage must have been consumed
             ok = mbar_wait_cluster(bar_consumed(g - kBStages), consumed_parity(g - kBStages), abort_flag, p.status, 6);
           if (!ok) continue;
 #ifdef MOLT_PAIR_TRACE
-          if (dt == 0) MOLT_TRACE(2, g);
+          if (dt == 0 && !(p.debug & 64)) MOLT_TRACE(2, g);
 #endif
           const uint32_t bt = btile0 + bs * kTileBBytes;
           if (kb < p.num_kb && (p.debug & 1)) {
           } else if (kb < p.num_kb) {
-            const uint32_t pk = load0 + ls * kLoadStageBytes + kTileABytes + src_off;
-            uint32_t words[4];
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3]) : "r"(pk) : "memory");
-            // 16 table lookups (independent, issued back to back), then 32 multiplies, 16 roundings, 4 stores
-            float2 codes[16];
+            const uint32_t pk = load0 + ls * kLoadStageBytes + kTileABytes;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-              for (int b = 0; b < 4; ++b) {
-                const uint32_t byte = __byte_perm(words[c], 0u, 0x4440u + (uint32_t)b);
-                asm("ld.shared.v2.f32 {%0,%1}, [%2];"
-                    : "=f"(codes[c * 4 + b].x), "=f"(codes[c * 4 + b].y) : "r"(lut_lane + byte * 128u));
-              }
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint32_t out[4];
-#pragma unroll
-              for (int b = 0; b < 4; ++b)
-                out[b] = pack_bf16x2(__fmul_rn(codes[c * 4 + b].x, scale), __fmul_rn(codes[c * 4 + b].y, scale));
-              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + dst_off + ((((uint32_t)(4 * h + c)) ^ swz) << 4)),
-                           "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3])
+            for (int half = 0; half < 2; ++half) {
+              uint32_t words[4];
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3])
+                           : "r"(pk + (half == 0 ? src_off0 : src_off1))
                            : "memory");
+              // 16 table lookups (independent, issued back to back), then 32 multiplies, 16 roundings, 4 stores
+              float2 codes[16];
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  const uint32_t byte = __byte_perm(words[c], 0u, 0x4440u + (uint32_t)b);
+                  asm("ld.shared.v2.f32 {%0,%1}, [%2];"
+                      : "=f"(codes[c * 4 + b].x), "=f"(codes[c * 4 + b].y) : "r"(lut_lane + byte * 128u));
+                }
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint32_t out[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                  out[b] = pack_bf16x2(__fmul_rn(codes[c * 4 + b].x, scale), __fmul_rn(codes[c * 4 + b].y, scale));
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + dst_off + ((((uint32_t)(4 * half + c)) ^ swz) << 4)),
+                             "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3])
+                             : "memory");
+              }
             }
             fence_proxy_async();
           } else {
             // low-rank block: this CTA's half of the ready-made B operand comes by TMA into the B stage
-            if (dt == 0) {
+            if (u == 0) {
               if (!BACKWARD) {
                 mbar_expect_tx(bar_ext, kTileBBytes);
                 tma_load_2d(bt, &map_ext, 0, col0, bar_ext);
@@ -400,21 +427,19 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
               }
             }
             ok = mbar_wait(bar_ext, ext_phase, abort_flag, p.status, 7);
-            ext_phase ^= 1u;
             if (!ok) continue;
           }
           __syncwarp();
           if (lane == 0) mbar_arrive_remote(bfull_remote_base + 8u * (uint32_t)bs);
 #ifdef MOLT_PAIR_TRACE
-          if (dt == 0) MOLT_TRACE(3, g);
+          if (dt == 0 && !(p.debug & 64)) MOLT_TRACE(3, g);
 #endif
-          ++g;
-          if (++ls == kLoadStages) { ls = 0; lphase ^= 1u; }
-          if (++bs == kBStages) bs = 0;
         }
 #pragma unroll
-        for (int u = 0; u < kPrefetch; ++u) cur[u] = nxt[u];
+        for (int q = 0; q < kPrefetch; ++q) cur[q] = nxt[q];
       }
+      // the low-rank barrier completes once per tile, whichever group handled it
+      if (p.ext_steps > 0) ext_phase ^= 1u;
     }
   } else {
     // ================= epilogue: TMEM -> bf16 -> shared -> TMA store (own 128 token rows) =================
@@ -545,6 +570,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
     return rc;
 
   Params p;
+  p.packed = w.packed;
   p.absmax = absmax_f32;
   p.status = device_status_word();
   if (p.status == nullptr) return fail(MOLT_E_RUNTIME, "tcgen05 GEMM: no device status word");
@@ -566,7 +592,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
 
   int variant = 0;
   {
-    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = load/B stages (4,4), 1 = (4,6), 2 = (5,4), 3 = (3,7)
+    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = load/B stages (5,4), 1 = (6,3), 2 = (4,4), 3 = (4,6)
     variant = env != nullptr ? atoi(env) : 0;
     if (variant < 0 || variant > 3) variant = 0;
   }
@@ -589,10 +615,10 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
   } while (0)
 #define MOLT_PAIR_DISPATCH(BWD)                             \
   do {                                                      \
-    if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 4, 6, 1);       \
-    else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 5, 4, 1);  \
-    else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 3, 7, 1);  \
-    else MOLT_PAIR_LAUNCH(BWD, 4, 4, 2);                    \
+    if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1);       \
+    else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 4, 4, 2);  \
+    else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 4, 6, 1);  \
+    else MOLT_PAIR_LAUNCH(BWD, 5, 4, 1);                    \
   } while (0)
   if (backward) MOLT_PAIR_DISPATCH(true);
   else MOLT_PAIR_DISPATCH(false);
