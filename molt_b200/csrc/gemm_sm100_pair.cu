@@ -40,13 +40,14 @@ constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;
 
 constexpr uint32_t kTileABytes = BM * BK * 2;          // 16384
 constexpr uint32_t kPackedBytes = BNH * BK / 2;        // 4096
-constexpr uint32_t kLoadStageBytes = kTileABytes + kPackedBytes;  // 20480
+constexpr uint32_t kLoadStageBytes = kTileABytes;      // activation ring stage
+constexpr int kCodeStages = 8;                         // ring of packed-code tiles; runs further ahead than the activations
 constexpr uint32_t kTileBBytes = BNH * BK * 2;         // 16384
 constexpr uint32_t kStoreBytes = BM * 64 * 2;          // 16384
 constexpr uint32_t kLutBytes = 256 * 16 * 8;           // 32768: [byte][16 copies] of float2
 constexpr uint32_t smem_bytes(int load_stages, int b_stages, int store_bufs) {
-  return load_stages * kLoadStageBytes + b_stages * kTileBBytes + store_bufs * kStoreBytes + kLutBytes +
-         256 /*barriers*/ + 1024 /*alignment*/;
+  return load_stages * kLoadStageBytes + kCodeStages * kPackedBytes + b_stages * kTileBBytes +
+         store_bufs * kStoreBytes + kLutBytes + 512 /*barriers*/ + 1024 /*alignment*/;
 }
 
 struct Params {
@@ -151,7 +152,8 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - raw);
   const uint32_t load0 = base;
-  const uint32_t btile0 = load0 + kLoadStages * kLoadStageBytes;
+  const uint32_t codes0 = load0 + kLoadStages * kLoadStageBytes;
+  const uint32_t btile0 = codes0 + kCodeStages * kPackedBytes;
   const uint32_t store0 = btile0 + kBStages * kTileBBytes;
   const uint32_t lut0 = store0 + kStoreBufs * kStoreBytes;
   const uint32_t bar0 = lut0 + kLutBytes;
@@ -160,13 +162,15 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   // consumed[g % 8] completes when the MMAs of contraction block number g (counted per CTA across tiles) have
   // finished reading their operands; ONE commit per block releases both the load stage and the B stage, in both
   // CTAs.  Eight slots exceed either ring depth, so a waiter can never be lapped.
-  constexpr int kConsumedSlots = 8;
-  static_assert(kLoadStages < kConsumedSlots && kBStages < kConsumedSlots, "ring deeper than the consumed slots");
+  constexpr int kConsumedSlots = 16;
+  static_assert(kLoadStages < kCodeStages && kCodeStages < kConsumedSlots && kBStages < kConsumedSlots,
+                "ring deeper than the consumed slots");
   auto bar_consumed = [&](int g) { return bar0 + 8u * (kLoadStages + (g & (kConsumedSlots - 1))); };
   auto bar_bfull = [&](int s) { return bar0 + 8u * (kLoadStages + kConsumedSlots + s); };          // used in the leader
   auto bar_accfull = [&](int b) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + b); };
   auto bar_accempty = [&](int b) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + 2 + b); };  // leader
   const uint32_t bar_ext = bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + 4);
+  auto bar_pkfull = [&](int s) { return bar_ext + 8u * (1 + s); };
   auto consumed_parity = [&](int g) { return (uint32_t)((g / kConsumedSlots) & 1); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -177,6 +181,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
     for (int s = 0; s < kLoadStages; ++s) mbar_init(bar_ldfull(s), 1);
+    for (int s = 0; s < kCodeStages; ++s) mbar_init(bar_pkfull(s), 1);
     for (int g = 0; g < kConsumedSlots; ++g) mbar_init(bar_consumed(g), 1);
     for (int s = 0; s < kBStages; ++s) mbar_init(bar_bfull(s), 8);   // 4 warps of one group x 2 CTAs
     for (int b = 0; b < 2; ++b) {
@@ -212,36 +217,67 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
 
   if (warp == kProducerWarp) {
     // ================= TMA producer (each CTA loads its own token rows and its own half of the codes) ==========
-    int s = 0;
-    int g = 0;   // running block number
-    bool ok = true;
-    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-      int tm, tn;
-      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-      const int row0 = tm * 2 * BM + (int)rank * BM;
-      for (int kb = 0; kb < blocks_per_tile; ++kb, ++g) {
-        if (g >= kLoadStages)   // the block that used this load stage must have been consumed
-          ok = mbar_wait_cluster(bar_consumed(g - kLoadStages), consumed_parity(g - kLoadStages), abort_flag, p.status, 1);
-        if (!ok) break;
-        if (lane == 0) {
-          const uint32_t a_dst = load0 + s * kLoadStageBytes;
-          if (kb < p.num_kb) {
-            const uint32_t pk_dst = a_dst + kTileABytes;
-            mbar_expect_tx(bar_ldfull(s), kTileABytes + kPackedBytes);
-            tma_load_2d(a_dst, &map_in, kb * BK, row0, bar_ldfull(s));
-            if (!BACKWARD) tma_load_2d(pk_dst, &map_packed, kb * (BK / 2), tn * BN + (int)rank * BNH, bar_ldfull(s));
-            else tma_load_2d(pk_dst, &map_packed, (tn * BN + (int)rank * BNH) / 2, kb * BK, bar_ldfull(s));
-          } else {
-            mbar_expect_tx(bar_ldfull(s), kTileABytes);
-            tma_load_2d(a_dst, &map_low, 0, row0, bar_ldfull(s));
-          }
-#ifdef MOLT_PAIR_TRACE
-          MOLT_TRACE(0, g);
-#endif
-        }
-        __syncwarp();
-        if (++s == kLoadStages) s = 0;
+    // Two streams with the same block order: packed codes (small, kCodeStages deep, needed first by the decoders)
+    // and activation tiles (large, kLoadStages deep, needed last by the MMA).  Step t issues the codes of block t
+    // and the activations of block t - kLag; both ring slots are free once block t - kCodeStages is consumed.
+    constexpr int kLag = kCodeStages - kLoadStages;
+    struct Cursor {
+      int tile, kb, tm, tn;
+      bool valid;
+    };
+    auto start_cursor = [&]() {
+      Cursor c;
+      c.tile = pair_id;
+      c.kb = 0;
+      c.valid = c.tile < num_tiles;
+      c.tm = c.tn = 0;
+      if (c.valid) pair_tile_coords(c.tile, p.tiles_m, p.tiles_n, c.tm, c.tn);
+      return c;
+    };
+    auto advance = [&](Cursor& c) {
+      if (++c.kb == blocks_per_tile) {
+        c.kb = 0;
+        c.tile += num_pairs;
+        c.valid = c.tile < num_tiles;
+        if (c.valid) pair_tile_coords(c.tile, p.tiles_m, p.tiles_n, c.tm, c.tn);
       }
+    };
+    Cursor pc = start_cursor(), ac = start_cursor();
+    bool ok = true;
+    for (int t = 0; ok; ++t) {
+      const bool do_codes = pc.valid;
+      const bool do_act = t >= kLag && ac.valid;
+      if (!do_codes && !do_act) break;
+      if (t >= kCodeStages)
+        ok = mbar_wait_cluster(bar_consumed(t - kCodeStages), consumed_parity(t - kCodeStages), abort_flag, p.status, 1);
+      if (!ok) break;
+      if (lane == 0) {
+        if (do_codes) {
+          const int s = t % kCodeStages;
+          if (pc.kb < p.num_kb) {
+            const uint32_t pk_dst = codes0 + (uint32_t)s * kPackedBytes;
+            mbar_expect_tx(bar_pkfull(s), kPackedBytes);
+            if (!BACKWARD) tma_load_2d(pk_dst, &map_packed, pc.kb * (BK / 2), pc.tn * BN + (int)rank * BNH, bar_pkfull(s));
+            else tma_load_2d(pk_dst, &map_packed, (pc.tn * BN + (int)rank * BNH) / 2, pc.kb * BK, bar_pkfull(s));
+          } else {
+            mbar_arrive(bar_pkfull(s));   // the low-rank block has no codes; keep the ring's phases in step
+          }
+        }
+        if (do_act) {
+          const int s = (t - kLag) % kLoadStages;
+          const uint32_t a_dst = load0 + (uint32_t)s * kLoadStageBytes;
+          const int row0 = ac.tm * 2 * BM + (int)rank * BM;
+          mbar_expect_tx(bar_ldfull(s), kTileABytes);
+          if (ac.kb < p.num_kb) tma_load_2d(a_dst, &map_in, ac.kb * BK, row0, bar_ldfull(s));
+          else tma_load_2d(a_dst, &map_low, 0, row0, bar_ldfull(s));
+        }
+#ifdef MOLT_PAIR_TRACE
+        MOLT_TRACE(0, t);
+#endif
+      }
+      __syncwarp();
+      if (do_codes) advance(pc);
+      if (do_act) advance(ac);
     }
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer (leader CTA only) =================
@@ -373,8 +409,8 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           if (kb >= blocks_per_tile || !ok) continue;
           const float scale = cur[q];
           const int g = g_tile + kb;
-          const int ls = g % kLoadStages, bs = g % kBStages;
-          ok = mbar_wait(bar_ldfull(ls), (uint32_t)((g / kLoadStages) & 1), abort_flag, p.status, 5);
+          const int ls = g % kLoadStages, bs = g % kBStages, cs = g % kCodeStages;
+          ok = mbar_wait(bar_pkfull(cs), (uint32_t)((g / kCodeStages) & 1), abort_flag, p.status, 5);
           if (ok && g >= kBStages)   // the block that used this B stage must have been consumed
             ok = mbar_wait_cluster(bar_consumed(g - kBStages), consumed_parity(g - kBStages), abort_flag, p.status, 6);
           if (!ok) continue;
@@ -384,7 +420,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           const uint32_t bt = btile0 + bs * kTileBBytes;
           if (kb < p.num_kb && (p.debug & 1)) {
           } else if (kb < p.num_kb) {
-            const uint32_t pk = load0 + ls * kLoadStageBytes + kTileABytes;
+            const uint32_t pk = codes0 + (uint32_t)cs * kPackedBytes;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               uint32_t words[4];
@@ -429,6 +465,9 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
             ok = mbar_wait(bar_ext, ext_phase, abort_flag, p.status, 7);
             if (!ok) continue;
           }
+          // this CTA's activation tile must have landed before the block is announced to the MMA thread
+          ok = mbar_wait(bar_ldfull(ls), (uint32_t)((g / kLoadStages) & 1), abort_flag, p.status, 9);
+          if (!ok) continue;
           __syncwarp();
           if (lane == 0) mbar_arrive_remote(bfull_remote_base + 8u * (uint32_t)bs);
 #ifdef MOLT_PAIR_TRACE
@@ -592,7 +631,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
 
   int variant = 0;
   {
-    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = load/B stages (5,4), 1 = (6,3), 2 = (4,4), 3 = (4,6)
+    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (5,4), 1 = (4,4), 2 = (4,5), 3 = (3,6)
     variant = env != nullptr ? atoi(env) : 0;
     if (variant < 0 || variant > 3) variant = 0;
   }
@@ -615,9 +654,9 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
   } while (0)
 #define MOLT_PAIR_DISPATCH(BWD)                             \
   do {                                                      \
-    if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1);       \
-    else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 4, 4, 2);  \
-    else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 4, 6, 1);  \
+    if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 4, 4, 2);       \
+    else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 4, 5, 1);  \
+    else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 3, 6, 1);  \
     else MOLT_PAIR_LAUNCH(BWD, 5, 4, 1);                    \
   } while (0)
   if (backward) MOLT_PAIR_DISPATCH(true);
