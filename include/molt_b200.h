@@ -120,6 +120,17 @@ int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* lora_grad, c
                 int lora_a_dtype, float scaling, int rank, void* dx, int64_t m, void* workspace,
                 size_t workspace_bytes, int path, uintptr_t stream);
 
+/* Same operation and arguments as molt_nf4_lora_fwd, minus t_out and the workspace: the scratch is a fixed
+ * MOLT_STATIC_SCRATCH_BYTES array inside the library's device image, so this call allocates nothing and asks the
+ * caller for nothing.  It is meant for hosts that cannot allocate device memory where they call the library (a
+ * server that pins its whole device budget at start-up, a plugin without an allocator of its own).  It has no
+ * counterpart in the reference.  Problems whose scratch need exceeds the array are refused (MOLT_E_VALUE).  All
+ * calls on a device share the array: calls that may overlap on the GPU must be serialised by the caller.  The
+ * first call on a device looks the array's address up; make it before any stream capture. */
+#define MOLT_STATIC_SCRATCH_BYTES (16u << 20)
+int molt_nf4_lora_fwd_static(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
+                             float scaling, int rank, void* y, int64_t m, int path, uintptr_t stream);
+
 /* Small-token forward (m <= 16): streams the packed weight once.  Same contract as molt_nf4_lora_fwd.
  * Replaces the bitsandbytes GEMV that bnb.matmul_4bit dispatches for few tokens (reference methods/nf4_lora.py:43-47). */
 int molt_nf4_gemv(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,

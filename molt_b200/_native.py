@@ -27,7 +27,7 @@ OP_LORA_FWD, OP_LORA_BWD, OP_DX, OP_MLP_FWD, OP_MLP_BWD = 1, 2, 3, 4, 5
 
 EXPORTS = (
     "molt_version", "molt_last_error", "molt_launch_count", "molt_read_status", "molt_nf4_dequant", "molt_nf4_resolve_absmax",
-    "molt_workspace_bytes", "molt_nf4_lora_fwd", "molt_nf4_lora_bwd", "molt_nf4_dx", "molt_nf4_gemv",
+    "molt_workspace_bytes", "molt_nf4_lora_fwd", "molt_nf4_lora_fwd_static", "molt_nf4_lora_bwd", "molt_nf4_dx", "molt_nf4_gemv",
     "molt_swiglu_fwd", "molt_swiglu_bwd", "molt_rmsnorm_fwd", "molt_mlp_workspace_bytes", "molt_mlp_fwd",
     "molt_mlp_bwd",
 )
@@ -90,6 +90,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.molt_workspace_bytes.argtypes = [i32, i64, i64, i64, i32]
     lib.molt_nf4_lora_fwd.restype = i32
     lib.molt_nf4_lora_fwd.argtypes = [desc, vp, vp, vp, f32, i32, vp, i64, vp, vp, sz, i32, up]
+    lib.molt_nf4_lora_fwd_static.restype = i32
+    lib.molt_nf4_lora_fwd_static.argtypes = [desc, vp, vp, vp, f32, i32, vp, i64, i32, up]
     lib.molt_nf4_lora_bwd.restype = i32
     lib.molt_nf4_lora_bwd.argtypes = [desc, vp, vp, vp, vp, f32, i32, vp, vp, vp, i64, vp, i32, vp, sz, i32, up]
     lib.molt_nf4_dx.restype = i32
