@@ -412,6 +412,76 @@ def profile_case(which, lib, device, desc, packed, state, lora_a, lora_b, x, dy,
     return 0
 
 
+def run_step_workload(args) -> int:
+    """BASELINE configs 4 / 5: a full QLoRA step of a synthetic-weight decoder; metric = training targets per second."""
+    import torch.distributed as dist
+
+    from molt_b200 import _native
+    from molt_b200.qlora_step import LLAMA3_8B, QWEN25_1P5B, QLoRAStep, hot_path_flops_per_token
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    shape = QWEN25_1P5B if args.workload == "step4" else LLAMA3_8B
+    lib = _native.library()
+    step = QLoRAStep(shape, device, layers=args.layers)
+    gen = torch.Generator(device=device).manual_seed(1337 + rank)
+    tokens = torch.randint(0, shape.vocab, (shape.micro_batch, shape.seq_len), device=device, generator=gen)
+    targets = torch.randint(0, shape.vocab, (shape.micro_batch, shape.seq_len), device=device, generator=gen)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        for _ in range(max(args.warmup, 3)):
+            step.run(tokens, targets)
+        barrier()
+        launches_before = lib.molt_launch_count()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as sampler:
+            barrier()
+            start.record()
+            for _ in range(args.steps):
+                loss = step.run(tokens, targets)
+            stop.record()
+            barrier()
+    elapsed = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms_per_step = float(elapsed.item()) / args.steps
+    status = _native.read_status(device)
+    if status:
+        raise SystemExit(f"a bounded device wait expired (status 0x{status:08x})")
+    peaks = measured_peaks()
+    layers = len(step.model.layers)
+    targets_per_s = world * shape.tokens / (ms_per_step * 1e-3)
+    hot_flops = hot_path_flops_per_token(shape) * layers / shape.layers
+    line = {
+        "metric": "qlora_step_targets_per_s", "value": targets_per_s, "unit": "targets/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"QLoRA step, {'Qwen2.5-1.5B' if args.workload == 'step4' else 'Llama-3-8B'} architecture, "
+                               f"{layers} layers, random-init NF4 weights, LoRA r={shape.rank}, seq {shape.seq_len}, "
+                               f"micro-batch {shape.micro_batch} per GPU", "parallelism": f"dp{world}",
+                   "lora_parameters": step.lora_parameter_count()},
+        "hot_path_tflops_per_gpu": hot_flops * shape.tokens / (ms_per_step * 1e-3) / 1e12,
+        "hot_path_frac_of_bf16_peak": hot_flops * shape.tokens / (ms_per_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "loss": float(loss), "gpu_launches": int(lib.molt_launch_count() - launches_before), "clocks": sampler.summary(),
+    }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+    return 0
+
+
 def extras(lib, device, desc, packed, state, lora_a, lora_b, peaks):
     """Secondary measurements: BASELINE config 2's forward M-sweep, SwiGLU bandwidth, config 3's MLP block."""
     from molt_b200 import _native
@@ -496,6 +566,9 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
+    parser.add_argument("--workload", choices=("linear", "step4", "step5"), default="linear",
+                        help="linear = the headline NF4-LoRA linear; step4 / step5 = full QLoRA step of BASELINE config 4 / 5")
+    parser.add_argument("--layers", type=int, default=None, help="step workloads: use fewer decoder layers")
     parser.add_argument("--profile", choices=("gemm_bwd", "linear_fwd", "gemv", "swiglu"), default=None,
                         help="run one kernel family four times and exit (target of an ncu capture)")
     args = parser.parse_args()
@@ -503,6 +576,8 @@ def main() -> int:
         parser.error("--steps must be positive")
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload != "linear":
+        return run_step_workload(args)
     return run_ours(args)
 
 

@@ -382,23 +382,20 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
                     const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
                     cudaStream_t s);
 
-// 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel (MOLT_B200_GEMM_VARIANT, read once; for testing)
+// 0 = default (CTA-pair kernel), 1 = single-CTA kernel, 2 = CTA-pair kernel (MOLT_B200_GEMM_VARIANT; for testing)
 static int forced_variant() {
-  static int value = -1;
-  if (value < 0) {
-    const char* env = getenv("MOLT_B200_GEMM_VARIANT");
-    value = env != nullptr ? atoi(env) : 0;
-    if (value < 0 || value > 2) value = 0;
-  }
-  return value;
+  const char* env = getenv("MOLT_B200_GEMM_VARIANT");
+  const int value = env != nullptr ? atoi(env) : 0;
+  return (value < 0 || value > 2) ? 0 : value;
 }
 
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
                cudaStream_t s) {
-  // The CTA pair works on 256 token rows at a time; up to 128 tokens the single-CTA kernel wastes nothing.
+  // The CTA-pair kernel is the default for every token count: its pipeline is deeper and, even with half of a
+  // pair tile empty (m <= 128), faster than the single-CTA kernel, which is kept as a selectable variant.
   const int variant = forced_variant();
-  if (variant == 2 || (variant == 0 && m > 128))
+  if (variant != 1)
     return sm100_gemm_pair(backward, w, absmax_f32, in, low, ext, rp, out, m, s);
   if (!sm100_gemm_supported(w, rp)) return fail(MOLT_E_CAPABILITY, "tcgen05 GEMM: unsupported shape");
   const long long contraction = backward ? w.n : w.k;

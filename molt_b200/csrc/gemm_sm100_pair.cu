@@ -245,9 +245,9 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     Cursor pc = start_cursor(), ac = start_cursor();
     bool ok = true;
     for (int t = 0; ok; ++t) {
+      if (!pc.valid && !ac.valid) break;
       const bool do_codes = pc.valid;
       const bool do_act = t >= kLag && ac.valid;
-      if (!do_codes && !do_act) break;
       if (t >= kCodeStages)
         ok = mbar_wait_cluster(bar_consumed(t - kCodeStages), consumed_parity(t - kCodeStages), abort_flag, p.status, 1);
       if (!ok) break;

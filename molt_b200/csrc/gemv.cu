@@ -241,22 +241,33 @@ __global__ void gemv_finish_kernel(const float* __restrict__ partial, int kgroup
 }
 
 // t[tok, r] = bf16(sum_k x[tok, k] * bf16(A[r, k])) as fp32, zero elsewhere in the [16, 64] tile.
-// One warp per (token, r).
-__global__ void gemv_lowrank_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ a, int m, int rank,
-                                    long long k, float* __restrict__ t) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= 16 * 64) return;
-  const int tok = warp >> 6, r = warp & 63;
+// One 128-thread CTA per (token, r): every thread sums a strided share of K, then the shares are added in a fixed
+// order (warp shuffles, then the four warp sums), so the result is deterministic.
+__global__ void __launch_bounds__(128) gemv_lowrank_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           const float* __restrict__ a, int m, int rank, long long k,
+                                                           float* __restrict__ t) {
+  __shared__ float warp_sums[4];
+  const int tok = blockIdx.x >> 6, r = blockIdx.x & 63;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float sum = 0.f;
   if (tok < m && r < rank) {
-    for (long long c = lane; c < k; c += 32)
-      sum += __bfloat162float(x[(long long)tok * k + c]) *
-             __bfloat162float(__float2bfloat16_rn(a[(long long)r * k + c]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const __nv_bfloat16* xr = x + (long long)tok * k;
+    const float* ar = a + (long long)r * k;
+    for (long long c = threadIdx.x * 2; c < k; c += 256) {
+      const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(xr + c);
+      const float2 av = *reinterpret_cast<const float2*>(ar + c);
+      sum += __bfloat162float(xv.x) * __bfloat162float(__float2bfloat16_rn(av.x));
+      sum += __bfloat162float(xv.y) * __bfloat162float(__float2bfloat16_rn(av.y));
+    }
   }
-  if (lane == 0) t[warp] = __bfloat162float(__float2bfloat16_rn(sum));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) warp_sums[warp] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const float total = (warp_sums[0] + warp_sums[1]) + (warp_sums[2] + warp_sums[3]);
+    t[blockIdx.x] = __bfloat162float(__float2bfloat16_rn(total));
+  }
 }
 
 size_t gemv_workspace_bytes(long long n, long long k) {
@@ -290,7 +301,7 @@ int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_
   p.t = t;
   p.partial = reinterpret_cast<float*>(ws + 16 * 64 * sizeof(float) + 256 - (16 * 64 * sizeof(float)) % 256);
   p.y = y;
-  gemv_lowrank_kernel<<<(16 * 64 * 32 + 255) / 256, 256, 0, s>>>(x, lora_a, m, rank, w.k, t);
+  gemv_lowrank_kernel<<<16 * 64, 128, 0, s>>>(x, lora_a, m, rank, w.k, t);
   if (int rc = launch_status("gemv_lowrank_kernel")) return rc;
 
   const size_t smem = 256 * 32 * 4 + (size_t)2 * p.warps_per_cta * 256 * 4 + 16 * 64 * 4 + 256 * 4;

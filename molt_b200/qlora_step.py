@@ -1,0 +1,223 @@
+"""A minimal QLoRA training step on a synthetic-weight decoder whose seven projections per layer run through the
+NF4-LoRA kernels: the caller-side harness for BASELINE configs 4 (Qwen2.5-1.5B shape) and 5 (Llama-3-8B shape).
+
+The reference drives this path from its trainer (reference training/qlora.py:485-1109) with Hugging Face
+checkpoints; checkpoints and datasets are not available here, so the decoder is random-initialised with the same
+architecture and fed uniform random token ids.  Attention (torch SDPA), RoPE, RMSNorm, the frozen bf16 embedding /
+LM head with a chunked exact cross-entropy, and AdamW are plain PyTorch -- they are callers of the hot path, not
+part of it.  Data parallelism: one process per GPU, the LoRA gradients live in one flat arena that is all-reduced
+over NCCL (``molt_b200.data_parallel``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+from torch.nn import functional as F
+
+from molt_b200.data_parallel import GradArena, lora_parameters
+from molt_b200.methods.quant_state import NestedState, QuantState
+from molt_b200.modules import GatedMLP, NF4LoRALinear
+from molt_b200.streaming.nf4 import NF4_CODEBOOK
+
+
+@dataclass(frozen=True)
+class DecoderShape:
+    layers: int
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    intermediate: int
+    vocab: int
+    rope_theta: float
+    rank: int
+    alpha: float
+    nested_absmax: bool
+    seq_len: int
+    micro_batch: int
+
+    @property
+    def tokens(self) -> int:
+        return self.seq_len * self.micro_batch
+
+
+QWEN25_1P5B = DecoderShape(28, 1536, 12, 2, 128, 8960, 151936, 1e6, 16, 32.0, False, 1024, 8)      # BASELINE config 4
+LLAMA3_8B = DecoderShape(32, 4096, 32, 8, 128, 14336, 128256, 5e5, 64, 128.0, True, 2048, 4)       # BASELINE config 5
+
+
+def quantize_fast(weight: torch.Tensor, nested: bool, nibble_order: str = "high-first"):
+    """NF4-quantise a freshly drawn synthetic weight on its device.  The nearest level is found through the
+    midpoints between codebook entries (identical to the arg-min quantiser except at exact midpoints), which is
+    what makes building a 28- or 32-layer model take seconds."""
+    device = weight.device
+    blocks = weight.float().reshape(-1, 64)
+    absmax = blocks.abs().amax(dim=1).clamp_min(torch.finfo(torch.float32).tiny)
+    levels = NF4_CODEBOOK.to(device)
+    codes = torch.bucketize(blocks / absmax[:, None], (levels[1:] + levels[:-1]) / 2).to(torch.uint8)
+    packed = ((codes[:, 0::2] << 4) | codes[:, 1::2]) if nibble_order == "high-first" else (codes[:, 0::2] | (codes[:, 1::2] << 4))
+    state = QuantState(absmax=absmax.contiguous(), shape=tuple(weight.shape), code=levels, nibble_order=nibble_order)
+    if nested:
+        table = torch.linspace(-1.0, 1.0, 256, device=device)
+        offset = absmax.mean()
+        residual = absmax - offset
+        pad = (-residual.numel()) % 256
+        groups = (F.pad(residual, (0, pad)) if pad else residual).reshape(-1, 256)
+        absmax2 = groups.abs().amax(dim=1).clamp_min(torch.finfo(torch.float32).tiny)
+        codes2 = torch.bucketize(groups / absmax2[:, None], (table[1:] + table[:-1]) / 2).to(torch.uint8)
+        state.absmax = codes2.reshape(-1)[: residual.numel()].contiguous()
+        state.nested = True
+        state.state2 = NestedState(absmax2.contiguous(), table, 256)
+        state.offset = float(offset)
+    return packed.reshape(-1, 1).contiguous(), state
+
+
+def _projection(out_features: int, in_features: int, shape: DecoderShape, gen: torch.Generator, device) -> NF4LoRALinear:
+    weight = torch.randn(out_features, in_features, device=device, generator=gen) * 0.02
+    packed, state = quantize_fast(weight, shape.nested_absmax)
+    lin = NF4LoRALinear(packed, state, shape.rank, shape.alpha)
+    with torch.no_grad():  # B = 0 would make every dA vanish; draw it as BASELINE's configs do
+        lin.lora_A["default"].weight.normal_(0.0, 0.01, generator=gen)
+        lin.lora_B["default"].weight.normal_(0.0, 0.01, generator=gen)
+    return lin
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, width: int, device, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+
+
+class Attention(nn.Module):
+    def __init__(self, shape: DecoderShape, gen, device):
+        super().__init__()
+        self.shape = shape
+        h, kv, d = shape.heads, shape.kv_heads, shape.head_dim
+        self.q_proj = _projection(h * d, shape.hidden, shape, gen, device)
+        self.k_proj = _projection(kv * d, shape.hidden, shape, gen, device)
+        self.v_proj = _projection(kv * d, shape.hidden, shape, gen, device)
+        self.o_proj = _projection(shape.hidden, h * d, shape, gen, device)
+
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        b, s, _ = x.shape
+        sh = self.shape
+        q = self.q_proj(x).view(b, s, sh.heads, sh.head_dim).transpose(1, 2)
+        k = self.k_proj(x).view(b, s, sh.kv_heads, sh.head_dim).transpose(1, 2)
+        v = self.v_proj(x).view(b, s, sh.kv_heads, sh.head_dim).transpose(1, 2)
+        q = _rope(q, cos, sin)
+        k = _rope(k, cos, sin)
+        out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        return self.o_proj(out.transpose(1, 2).reshape(b, s, sh.heads * sh.head_dim))
+
+
+def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    half = x.shape[-1] // 2
+    rotated = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+    return x * cos + rotated * sin
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, shape: DecoderShape, gen, device):
+        super().__init__()
+        self.input_norm = RMSNorm(shape.hidden, device)
+        self.attn = Attention(shape, gen, device)
+        self.post_norm = RMSNorm(shape.hidden, device)
+        self.mlp = GatedMLP(_projection(shape.intermediate, shape.hidden, shape, gen, device),
+                            _projection(shape.intermediate, shape.hidden, shape, gen, device),
+                            _projection(shape.hidden, shape.intermediate, shape, gen, device))
+
+    def forward(self, x, cos, sin, replay_up: bool):
+        x = x + self.attn(self.input_norm(x), cos, sin)
+        normed = self.post_norm(x)
+        b, s, w = normed.shape
+        return x + self.mlp.fused(normed.reshape(b * s, w), rematerialize_up=replay_up).view(b, s, w)
+
+
+class _FrozenHeadLoss(torch.autograd.Function):
+    """Mean token cross-entropy through a frozen bf16 LM head, in row chunks, without keeping the logits."""
+
+    @staticmethod
+    def forward(ctx, hidden, head, targets, chunk, denominator):
+        rows = hidden.shape[0]
+        grad = torch.empty_like(hidden)
+        total = torch.zeros((), device=hidden.device, dtype=torch.float32)
+        for start in range(0, rows, chunk):
+            h = hidden[start:start + chunk]
+            logits = (h @ head.t()).float()
+            lse = torch.logsumexp(logits, dim=-1)
+            t = targets[start:start + chunk]
+            total += (lse - logits.gather(1, t[:, None]).squeeze(1)).sum()
+            probs = torch.softmax(logits, dim=-1)
+            probs.scatter_add_(1, t[:, None], torch.full_like(t[:, None], -1.0, dtype=torch.float32))
+            grad[start:start + chunk] = (probs / denominator).to(hidden.dtype) @ head
+        ctx.save_for_backward(grad)
+        return total / denominator
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (grad,) = ctx.saved_tensors
+        return grad * grad_output.to(grad.dtype), None, None, None, None
+
+
+class SyntheticDecoder(nn.Module):
+    def __init__(self, shape: DecoderShape, device, seed: int = 1337, layers: Optional[int] = None):
+        super().__init__()
+        self.shape = shape
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.embed = nn.Parameter((torch.randn(shape.vocab, shape.hidden, device=device, generator=gen) * 0.02).bfloat16(),
+                                  requires_grad=False)
+        self.head = nn.Parameter((torch.randn(shape.vocab, shape.hidden, device=device, generator=gen) * 0.02).bfloat16(),
+                                 requires_grad=False)
+        self.layers = nn.ModuleList(DecoderLayer(shape, gen, device) for _ in range(layers or shape.layers))
+        self.final_norm = RMSNorm(shape.hidden, device)
+        inv = 1.0 / (shape.rope_theta ** (torch.arange(0, shape.head_dim, 2, device=device).float() / shape.head_dim))
+        angles = torch.outer(torch.arange(shape.seq_len, device=device).float(), inv)
+        angles = torch.cat((angles, angles), dim=-1)
+        self.register_buffer("cos", angles.cos().bfloat16()[None, None], persistent=False)
+        self.register_buffer("sin", angles.sin().bfloat16()[None, None], persistent=False)
+
+    def loss(self, tokens: torch.Tensor, targets: torch.Tensor, global_tokens: int, replay_up: bool = True) -> torch.Tensor:
+        x = F.embedding(tokens, self.embed).requires_grad_()
+        for layer in self.layers:
+            x = layer(x, self.cos, self.sin, replay_up)
+        hidden = self.final_norm(x).reshape(-1, self.shape.hidden)
+        return _FrozenHeadLoss.apply(hidden, self.head, targets.reshape(-1), 1024, float(global_tokens))
+
+
+class QLoRAStep:
+    """Holds model, gradient arena and optimiser; ``run(tokens, targets)`` is one data-parallel training step."""
+
+    def __init__(self, shape: DecoderShape, device, layers: Optional[int] = None, lr: float = 1e-4):
+        self.shape = shape
+        self.device = device
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.model = SyntheticDecoder(shape, device, layers=layers)
+        self.arena = GradArena(lora_parameters(self.model))
+        self.optimizer = torch.optim.AdamW(self.arena.params, lr=lr, weight_decay=0.0, fused=True)
+
+    def run(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        self.arena.zero()
+        loss = self.model.loss(tokens, targets, self.shape.tokens * self.world)
+        loss.backward()
+        self.arena.all_reduce()
+        self.optimizer.step()
+        return loss.detach()
+
+    def lora_parameter_count(self) -> int:
+        return sum(p.numel() for p in self.arena.params)
+
+
+def hot_path_flops_per_token(shape: DecoderShape) -> float:
+    """Algorithmic forward+backward FLOPs of the seven NF4-LoRA projections per token: 4·N·K + 6·r·(K+N) each."""
+    h, kvw, qw, inter = shape.hidden, shape.kv_heads * shape.head_dim, shape.heads * shape.head_dim, shape.intermediate
+    projections = [(qw, h), (kvw, h), (kvw, h), (h, qw), (inter, h), (inter, h), (h, inter)]
+    per_layer = sum(4.0 * n * k + 6.0 * shape.rank * (n + k) for n, k in projections)
+    return per_layer * shape.layers

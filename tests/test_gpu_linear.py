@@ -99,6 +99,25 @@ def test_dimension_tails_use_the_general_kernels(native_library):
         run_forward(case, _native.PATH_TCGEN05)
 
 
+def test_single_cta_variant_still_matches(native_library, monkeypatch):
+    """The single-CTA tcgen05 kernel (selectable variant) against the oracle and against the default pair kernel."""
+    case = make_case(512, 320, 200, 16, seed=31)
+    y_pair, _ = run_forward(case, PATHS["tcgen05"])
+    monkeypatch.setenv("MOLT_B200_GEMM_VARIANT", "1")
+    errors = _check_all(case, PATHS["tcgen05"])
+    y_single, _ = run_forward(case, PATHS["tcgen05"])
+    monkeypatch.delenv("MOLT_B200_GEMM_VARIANT")
+    assert max(errors.values()) <= TOL
+    assert oracle.rel_frobenius(y_single, y_pair.float()) < 2e-3
+
+
+@pytest.mark.parametrize("n,k,m", [(64, 64, 256), (64, 128, 300), (128, 64, 40), (192, 64, 513)])
+def test_short_contractions(native_library, n, k, m):
+    """One or two contraction blocks per tile: shorter than the pipeline's lead of codes over activations."""
+    case = make_case(n, k, m, 8, seed=n + k + m)
+    _check_all(case, PATHS["tcgen05"])
+
+
 def test_empty_batch(native_library):
     case = make_case(128, 64, 0, 8)
     y, _ = run_forward(case)
