@@ -428,7 +428,7 @@ def run_step_workload(args) -> int:
         dist.init_process_group("nccl", device_id=device)
     shape = QWEN25_1P5B if args.workload == "step4" else LLAMA3_8B
     lib = _native.library()
-    step = QLoRAStep(shape, device, layers=args.layers)
+    step = QLoRAStep(shape, device, layers=args.layers, cuda_graph=not args.no_graph)
     gen = torch.Generator(device=device).manual_seed(1337 + rank)
     tokens = torch.randint(0, shape.vocab, (shape.micro_batch, shape.seq_len), device=device, generator=gen)
     targets = torch.randint(0, shape.vocab, (shape.micro_batch, shape.seq_len), device=device, generator=gen)
@@ -469,7 +469,7 @@ def run_step_workload(args) -> int:
         "config": {"workload": f"QLoRA step, {'Qwen2.5-1.5B' if args.workload == 'step4' else 'Llama-3-8B'} architecture, "
                                f"{layers} layers, random-init NF4 weights, LoRA r={shape.rank}, seq {shape.seq_len}, "
                                f"micro-batch {shape.micro_batch} per GPU", "parallelism": f"dp{world}",
-                   "lora_parameters": step.lora_parameter_count()},
+                   "lora_parameters": step.lora_parameter_count(), "cuda_graph": not args.no_graph},
         "hot_path_tflops_per_gpu": hot_flops * shape.tokens / (ms_per_step * 1e-3) / 1e12,
         "hot_path_frac_of_bf16_peak": hot_flops * shape.tokens / (ms_per_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
         "loss": float(loss), "gpu_launches": int(lib.molt_launch_count() - launches_before), "clocks": sampler.summary(),
@@ -568,6 +568,7 @@ def main() -> int:
     parser.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
     parser.add_argument("--workload", choices=("linear", "step4", "step5"), default="linear",
                         help="linear = the headline NF4-LoRA linear; step4 / step5 = full QLoRA step of BASELINE config 4 / 5")
+    parser.add_argument("--no-graph", action="store_true", help="step workloads: run eagerly instead of replaying a CUDA graph")
     parser.add_argument("--layers", type=int, default=None, help="step workloads: use fewer decoder layers")
     parser.add_argument("--profile", choices=("gemm_bwd", "linear_fwd", "gemv", "swiglu"), default=None,
                         help="run one kernel family four times and exit (target of an ncu capture)")

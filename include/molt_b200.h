@@ -153,6 +153,13 @@ int molt_swiglu_bwd(const void* grad_out, const void* gate, const void* up, void
 int molt_rmsnorm_fwd(const void* x, const void* weight, int weight_dtype, float eps, float weight_offset,
                      void* out, int64_t rows, int64_t width, uintptr_t stream);
 
+/* Frozen-head cross-entropy on bf16 logits [rows, vocab]: row_loss[row] = logsumexp(logits) - logits[target], and
+ * logits is overwritten by (softmax - onehot) * grad_scale (bf16).  fp32 arithmetic, two passes over each row.
+ * Replaces _fused_ce_loss_kernel_online / _fused_ce_softmax_grad_kernel_online
+ * (reference kernels/frozen_linear_cross_entropy.py:27-139). */
+int molt_ce_softmax_grad(void* logits, const int64_t* targets, float* row_loss, int64_t rows, int64_t vocab,
+                         float grad_scale, uintptr_t stream);
+
 /* Gated MLP block: gate = P_g(x), up = P_u(x), y = P_d(silu(gate) * up).
  * gate_out [m, inter] is always written (it is what the replay schedule saves); up_out may be NULL when the
  * caller re-materialises `up` in backward.  Replaces _ResidualRecipeGatedNF4LoRA.forward

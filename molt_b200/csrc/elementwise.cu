@@ -317,3 +317,105 @@ extern "C" int molt_rmsnorm_fwd(const void* x, const void* weight, int weight_dt
                                                        weight_offset, (__nv_bfloat16*)out, rows, width);
   return launch_status("rmsnorm_kernel");
 }
+
+// ------------------------------------------------------------------------------------------------
+// Frozen-head cross-entropy: per row, loss = logsumexp(logits) - logits[target] and, in place,
+// logits <- (softmax(logits) - onehot(target)) * grad_scale, both from bf16 logits with fp32 arithmetic.
+// One CTA per row: an online max/sum pass, then the gradient pass (the row stays in L2 in between).
+// Replaces the two Triton kernels of reference kernels/frozen_linear_cross_entropy.py:27-139.
+// ------------------------------------------------------------------------------------------------
+namespace molt {
+
+__global__ void __launch_bounds__(512) ce_softmax_grad_kernel(__nv_bfloat16* __restrict__ logits,
+                                                              const long long* __restrict__ targets,
+                                                              float* __restrict__ row_loss, long long vocab,
+                                                              float grad_scale) {
+  __shared__ float red_max[16], red_sum[16];
+  __shared__ float row_stats[2];
+  const long long row = blockIdx.x;
+  __nv_bfloat16* x = logits + row * vocab;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long vectors = vocab / 8;
+  float m = -INFINITY, s = 0.f;
+  for (long long v = threadIdx.x; v < vectors; v += blockDim.x) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + v * 8);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float vals[8];
+    float local = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      vals[2 * i] = bf16_lo(w[i]);
+      vals[2 * i + 1] = bf16_hi(w[i]);
+      local = fmaxf(local, fmaxf(vals[2 * i], vals[2 * i + 1]));
+    }
+    const float nm = fmaxf(m, local);
+    float add = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) add += __expf(vals[i] - nm);
+    s = s * __expf(m - nm) + add;
+    m = nm;
+  }
+  for (long long c = vectors * 8 + threadIdx.x; c < vocab; c += blockDim.x) {
+    const float val = __bfloat162float(x[c]);
+    const float nm = fmaxf(m, val);
+    s = s * __expf(m - nm) + __expf(val - nm);
+    m = nm;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
+    const float nm = fmaxf(m, om);
+    s = (m == -INFINITY ? 0.f : s * __expf(m - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+    m = nm;
+  }
+  if (lane == 0) { red_max[warp] = m; red_sum[warp] = s; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float gm = -INFINITY, gs = 0.f;
+    const int warps = blockDim.x >> 5;
+    for (int i = 0; i < warps; ++i) gm = fmaxf(gm, red_max[i]);
+    for (int i = 0; i < warps; ++i) gs += red_max[i] == -INFINITY ? 0.f : red_sum[i] * __expf(red_max[i] - gm);
+    row_stats[0] = gm;
+    row_stats[1] = gs;
+    const long long t = targets[row];
+    row_loss[row] = logf(gs) + gm - __bfloat162float(x[t]);
+  }
+  __syncthreads();
+  const float gm = row_stats[0];
+  const float inv = grad_scale / row_stats[1];
+  const long long t = targets[row];
+  for (long long v = threadIdx.x; v < vectors; v += blockDim.x) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + v * 8);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float a = __expf(bf16_lo(w[i]) - gm) * inv, b = __expf(bf16_hi(w[i]) - gm) * inv;
+      const long long c = v * 8 + 2 * i;
+      if (c == t) a -= grad_scale;
+      if (c + 1 == t) b -= grad_scale;
+      out[i] = pack_bf16x2(a, b);
+    }
+    *reinterpret_cast<uint4*>(x + v * 8) = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+  for (long long c = vectors * 8 + threadIdx.x; c < vocab; c += blockDim.x) {
+    float a = __expf(__bfloat162float(x[c]) - gm) * inv;
+    if (c == t) a -= grad_scale;
+    x[c] = __float2bfloat16_rn(a);
+  }
+}
+
+}  // namespace molt
+
+extern "C" int molt_ce_softmax_grad(void* logits, const int64_t* targets, float* row_loss, int64_t rows, int64_t vocab,
+                                    float grad_scale, uintptr_t stream) {
+  MOLT_REQUIRE(logits && targets && row_loss, MOLT_E_VALUE, "molt_ce_softmax_grad: NULL tensor pointer");
+  MOLT_REQUIRE(rows >= 0 && vocab > 0, MOLT_E_VALUE, "molt_ce_softmax_grad: bad shape");
+  MOLT_REQUIRE(aligned16(logits) && vocab % 8 == 0, MOLT_E_VALUE,
+               "molt_ce_softmax_grad: logits must be 16-byte aligned with a vocabulary that is a multiple of 8");
+  if (rows == 0) return MOLT_OK;
+  ce_softmax_grad_kernel<<<(unsigned)rows, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(logits), reinterpret_cast<const long long*>(targets), row_loss, vocab,
+      grad_scale);
+  return launch_status("ce_softmax_grad_kernel");
+}

@@ -142,24 +142,30 @@ class DecoderLayer(nn.Module):
 
 
 class _FrozenHeadLoss(torch.autograd.Function):
-    """Mean token cross-entropy through a frozen bf16 LM head, in row chunks, without keeping the logits."""
+    """Mean token cross-entropy through a frozen bf16 LM head, in row chunks, without keeping the logits:
+    logits = h . head^T (cuBLAS), then one fused kernel turns the bf16 logits in place into the softmax gradient
+    and emits the per-row loss, then dh = grad . head (the chunked scheme of reference
+    kernels/frozen_linear_cross_entropy.py:181-236)."""
 
     @staticmethod
     def forward(ctx, hidden, head, targets, chunk, denominator):
-        rows = hidden.shape[0]
+        from molt_b200 import _native
+
+        lib = _native.library()
+        rows, vocab = hidden.shape[0], head.shape[0]
         grad = torch.empty_like(hidden)
-        total = torch.zeros((), device=hidden.device, dtype=torch.float32)
+        row_loss = torch.empty(rows, device=hidden.device, dtype=torch.float32)
+        targets = targets.contiguous()
         for start in range(0, rows, chunk):
             h = hidden[start:start + chunk]
-            logits = (h @ head.t()).float()
-            lse = torch.logsumexp(logits, dim=-1)
-            t = targets[start:start + chunk]
-            total += (lse - logits.gather(1, t[:, None]).squeeze(1)).sum()
-            probs = torch.softmax(logits, dim=-1)
-            probs.scatter_add_(1, t[:, None], torch.full_like(t[:, None], -1.0, dtype=torch.float32))
-            grad[start:start + chunk] = (probs / denominator).to(hidden.dtype) @ head
+            logits = h @ head.t()
+            with torch.cuda.device(hidden.device):
+                _native.check(lib.molt_ce_softmax_grad(
+                    logits.data_ptr(), targets[start:start + chunk].data_ptr(), row_loss[start:start + chunk].data_ptr(),
+                    logits.shape[0], vocab, 1.0 / denominator, _native.stream_handle(hidden.device)))
+            grad[start:start + chunk] = logits @ head
         ctx.save_for_backward(grad)
-        return total / denominator
+        return row_loss.sum() / denominator
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -195,21 +201,48 @@ class SyntheticDecoder(nn.Module):
 class QLoRAStep:
     """Holds model, gradient arena and optimiser; ``run(tokens, targets)`` is one data-parallel training step."""
 
-    def __init__(self, shape: DecoderShape, device, layers: Optional[int] = None, lr: float = 1e-4):
+    def __init__(self, shape: DecoderShape, device, layers: Optional[int] = None, lr: float = 1e-4,
+                 cuda_graph: bool = False):
         self.shape = shape
         self.device = device
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.model = SyntheticDecoder(shape, device, layers=layers)
         self.arena = GradArena(lora_parameters(self.model))
         self.optimizer = torch.optim.AdamW(self.arena.params, lr=lr, weight_decay=0.0, fused=True)
+        self.cuda_graph = cuda_graph
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._static_tokens = self._static_targets = self._static_loss = None
+        self._eager_steps = 0
 
-    def run(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    def _forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         self.arena.zero()
         loss = self.model.loss(tokens, targets, self.shape.tokens * self.world)
         loss.backward()
+        return loss.detach()
+
+    def _capture(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
+        """Record forward + backward of one micro-batch once; every later step replays the recording (the kernels
+        take raw pointers and never allocate or synchronise, so they are capture-safe)."""
+        self._static_tokens = tokens.clone()
+        self._static_targets = targets.clone()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._static_loss = self._forward_backward(self._static_tokens, self._static_targets)
+
+    def run(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        if self.cuda_graph and self._graph is None and self._eager_steps >= 2:
+            self._capture(tokens, targets)
+        if self._graph is not None:
+            self._static_tokens.copy_(tokens)
+            self._static_targets.copy_(targets)
+            self._graph.replay()
+            loss = self._static_loss
+        else:
+            loss = self._forward_backward(tokens, targets)
+            self._eager_steps += 1
         self.arena.all_reduce()
         self.optimizer.step()
-        return loss.detach()
+        return loss
 
     def lora_parameter_count(self) -> int:
         return sum(p.numel() for p in self.arena.params)

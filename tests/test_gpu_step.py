@@ -27,3 +27,23 @@ def test_tiny_decoder_trains(native_library):
     assert _native.read_status() == 0
     assert step.lora_parameter_count() == 2 * 8 * ((128 + 128) + 2 * (64 + 128) + (128 + 128) + 2 * (256 + 128) + (128 + 256))
     assert hot_path_flops_per_token(shape) > 0
+
+
+@pytest.mark.parametrize("rows,vocab", [(5, 512), (3, 151936), (2, 1000)])
+def test_ce_softmax_grad_kernel(native_library, rows, vocab):
+    """Loss and in-place gradient of the frozen-head cross-entropy against torch in fp32."""
+    from molt_b200 import _native
+
+    gen = torch.Generator().manual_seed(rows + vocab)
+    logits = (torch.randn(rows, vocab, generator=gen) * 3).bfloat16()
+    targets = torch.randint(0, vocab, (rows,), generator=gen)
+    dev_logits = logits.cuda()
+    loss = torch.empty(rows, device="cuda")
+    _native.check(_native.library().molt_ce_softmax_grad(dev_logits.data_ptr(), targets.cuda().data_ptr(), loss.data_ptr(),
+                                                         rows, vocab, 0.25, _native.stream_handle()))
+    ref_logits = logits.float().requires_grad_()
+    ref_loss = torch.nn.functional.cross_entropy(ref_logits, targets, reduction="none")
+    (ref_loss.sum() * 0.25).backward()
+    torch.testing.assert_close(loss.cpu(), ref_loss.detach(), rtol=1e-4, atol=1e-4)
+    got = dev_logits.float().cpu()
+    assert (got - ref_logits.grad).abs().max() <= 2e-3 * 0.25 + 1e-6   # bf16 rounding of values in [-0.25, 0.25]
