@@ -400,8 +400,9 @@ def profile_case(which, lib, device, desc, packed, state, lora_a, lora_b, x, dy,
                                                 SCALING, RANK, y.data_ptr(), m, None, ws.data_ptr(), ws_bytes,
                                                 _native.PATH_TCGEN05, stream))
         elif which == "gemv":
-            _native.check(lib.molt_nf4_gemv(ctypes.byref(desc), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(), SCALING,
-                                            RANK, y.data_ptr(), 16, ws.data_ptr(), ws_bytes, stream))
+            for d in (desc, plain_desc):   # nested absmax (the configuration's own form), then plain fp32 absmax
+                _native.check(lib.molt_nf4_gemv(ctypes.byref(d), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
+                                                SCALING, RANK, y.data_ptr(), 16, ws.data_ptr(), ws_bytes, stream))
         elif which == "swiglu":
             swiglu_forward(dy, dy)
             swiglu_backward(dy, dy, dy)

@@ -110,14 +110,15 @@ int add_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out,
 }
 
 static bool aligned_case(const molt_nf4_desc* w, int rank) {
-  return w->blocksize == 64 && w->k % 64 == 0 && w->n % 64 == 0 && rank >= 1 && rank <= 64;
+  return w->blocksize == 64 && w->k % 64 == 0 && w->n % 64 == 0 && rank >= 1 && rank <= 64 &&
+         (reinterpret_cast<uintptr_t>(w->packed) & 15) == 0;
 }
 
 static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m, bool forward, int* chosen) {
   const bool aligned = aligned_case(w, rank);
   if (requested == MOLT_PATH_AUTO) {
     if (!aligned) *chosen = MOLT_PATH_GENERAL;
-    else if (forward && m <= 16) *chosen = MOLT_PATH_GEMV;
+    else if (forward && m <= 16 && w->k <= 16384) *chosen = MOLT_PATH_GEMV;
     else *chosen = MOLT_PATH_TCGEN05;
     return MOLT_OK;
   }
@@ -125,7 +126,8 @@ static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m,
                MOLT_E_VALUE, "unknown kernel path %d", requested);
   if (requested != MOLT_PATH_GENERAL)
     MOLT_REQUIRE(aligned, MOLT_E_CAPABILITY,
-                 "the tcgen05 and GEMV kernels need blocksize 64, K %% 64 == 0, N %% 64 == 0 and rank <= 64 "
+                 "the tcgen05 and GEMV kernels need blocksize 64, K %% 64 == 0, N %% 64 == 0, rank <= 64 and a packed "
+                 "weight that starts on a 16-byte boundary "
                  "(got N=%lld K=%lld blocksize=%d rank=%d)",
                  (long long)w->n, (long long)w->k, w->blocksize, rank);
   if (requested == MOLT_PATH_GEMV)
@@ -164,7 +166,15 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
       if (int rc = general_rowsum(true, xb, lora_a, 1.0f, m, w->k, rank, reinterpret_cast<__nv_bfloat16*>(t_out), 64, s))
         return rc;
     }
-    return gemv_forward(view, xb, lora_a, lora_b, scaling, rank, yb, (int)m, ws, gemv_workspace_bytes(w->n, w->k), s);
+    WeightView gview = view;
+    if (w->absmax_kind == MOLT_ABSMAX_NESTED && !gemv_reads_nested(view)) {
+      // a nested layout the kernel cannot stage with 4-byte copies: resolve it to fp32 once per call
+      float* resolved = gemv_resolved_absmax_slot(ws, w->n, w->k);
+      if (int rc = molt_nf4_resolve_absmax(w, resolved, reinterpret_cast<uintptr_t>(s))) return rc;
+      gview.absmax = resolved;
+      gview.absmax_kind = MOLT_ABSMAX_F32;
+    }
+    return gemv_forward(gview, xb, lora_a, lora_b, scaling, rank, yb, (int)m, ws, gemv_workspace_bytes(w->n, w->k), s);
   }
   __nv_bfloat16* t = t_out != nullptr ? reinterpret_cast<__nv_bfloat16*>(t_out)
                                       : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));

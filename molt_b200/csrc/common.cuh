@@ -52,6 +52,7 @@ struct WeightView {
   float offset;
   int absmax_kind;
   int block2;
+  int block2_shift;   // log2(block2) when block2 is a power of two, else -1
   int blocksize;
   int nibble_order;
   long long n, k;
@@ -67,6 +68,9 @@ inline WeightView make_view(const molt_nf4_desc* w) {
   v.offset = w->offset;
   v.absmax_kind = w->absmax_kind;
   v.block2 = w->block2 > 0 ? w->block2 : 256;
+  v.block2_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == v.block2) v.block2_shift = sh;
   v.blocksize = w->blocksize;
   v.nibble_order = w->nibble_order;
   v.n = w->n;
@@ -84,7 +88,8 @@ int32_t* device_status_word();
 __device__ __forceinline__ float load_absmax(const WeightView& w, long long blk) {
   if (w.absmax_kind == MOLT_ABSMAX_F32) return __ldg(reinterpret_cast<const float*>(w.absmax) + blk);
   unsigned code = __ldg(reinterpret_cast<const uint8_t*>(w.absmax) + blk);
-  float scaled = __fmul_rn(__ldg(w.code2 + code), __ldg(w.absmax2 + blk / w.block2));
+  const long long group = w.block2_shift >= 0 ? (blk >> w.block2_shift) : blk / w.block2;
+  float scaled = __fmul_rn(__ldg(w.code2 + code), __ldg(w.absmax2 + group));
   return __fadd_rn(scaled, w.offset);
 }
 

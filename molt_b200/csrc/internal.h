@@ -27,6 +27,8 @@ int colsum_mma(bool transpose_out, const __nv_bfloat16* low, const __nv_bfloat16
 
 // gemv.cu
 size_t gemv_workspace_bytes(long long n, long long k);
+bool gemv_reads_nested(const WeightView& w);
+float* gemv_resolved_absmax_slot(void* workspace, long long n, long long k);
 int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_a, const float* lora_b, float scaling,
                  int rank, __nv_bfloat16* y, int m, void* workspace, size_t workspace_bytes, cudaStream_t s);
 
