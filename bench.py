@@ -32,6 +32,9 @@ if str(ROOT) not in sys.path:
 
 N_OUT, K_IN, RANK, ALPHA, M_PER_GPU = 14336, 4096, 16, 32.0, 4096
 SCALING = ALPHA / RANK
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward GEMM launch at M = 4096 (354.9 MB + 29.3 MB), taken from
+# an ncu --set full capture of `bench.py --profile gemm_bwd`; the summary of that capture sits under profiles/.
+GEMM_BWD_DRAM_BYTES_PER_LAUNCH = 384.2e6
 METRIC = "nf4_lora_linear_fwd_bwd_tflops"
 WORKLOAD = ("NF4-LoRA linear fwd+bwd, W[14336,4096] NF4 bs64 double-quant absmax, r=16 alpha=32, "
             "M=4096 tokens per GPU, bf16")
@@ -352,10 +355,11 @@ def run_ours(args) -> int:
 
     gemm_ms = event_time_ms(gemm_only, iters=max(5, args.steps), warmup=3)
     achieved = 2.0 * m * N_OUT * K_IN / (gemm_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": "nf4_gemm_sm100_kernel<backward> (dX = dY . deq(W), M=4096)",
+    roofline = {"bound": "tensor", "kernel": "nf4_gemm_sm100_pair_kernel<backward> (dX = dY . deq(W), M=4096)",
                 "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"], "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
-                "peak_source": f"{peaks['source']} (cuBLAS bf16 burst)", "ms_per_launch": gemm_ms, "traffic": None}
+                "peak_source": f"{peaks['source']} (cuBLAS bf16 burst)", "ms_per_launch": gemm_ms,
+                "traffic": GEMM_BWD_DRAM_BYTES_PER_LAUNCH if m == 4096 else None, "traffic_unit": "bytes per launch (ncu)"}
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -404,8 +408,9 @@ def profile_case(which, lib, device, desc, packed, state, lora_a, lora_b, x, dy,
                 _native.check(lib.molt_nf4_gemv(ctypes.byref(d), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
                                                 SCALING, RANK, y.data_ptr(), 16, ws.data_ptr(), ws_bytes, stream))
         elif which == "swiglu":
-            swiglu_forward(dy, dy)
-            swiglu_backward(dy, dy, dy)
+            gate, up, grad = dy, torch.roll(dy, 1, 0), torch.roll(dy, 2, 0)   # three distinct [M, N] tensors
+            swiglu_forward(gate, up)
+            swiglu_backward(grad, gate, up)
         else:
             raise SystemExit(f"unknown profile case {which}")
     torch.cuda.synchronize()
@@ -443,7 +448,7 @@ def run_step_workload(args) -> int:
         for _ in range(max(args.warmup, 3)):
             step.run(tokens, targets)
         barrier()
-        launches_before = lib.molt_launch_count()
+        launches_before = lib.molt_launch_count() + step.replayed_launches   # eager launches + graph-replayed ones
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local_rank) as sampler:
             barrier()
@@ -473,7 +478,8 @@ def run_step_workload(args) -> int:
                    "lora_parameters": step.lora_parameter_count(), "cuda_graph": not args.no_graph},
         "hot_path_tflops_per_gpu": hot_flops * shape.tokens / (ms_per_step * 1e-3) / 1e12,
         "hot_path_frac_of_bf16_peak": hot_flops * shape.tokens / (ms_per_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
-        "loss": float(loss), "gpu_launches": int(lib.molt_launch_count() - launches_before), "clocks": sampler.summary(),
+        "loss": float(loss), "gpu_launches": int(lib.molt_launch_count() + step.replayed_launches - launches_before),
+        "clocks": sampler.summary(),
     }
     if world > 1:
         dist.barrier()

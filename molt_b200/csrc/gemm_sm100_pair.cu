@@ -408,6 +408,8 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           const int kb = kb0 + kDecodeGroups * q;
           if (kb >= blocks_per_tile || !ok) continue;
           const float scale = cur[q];
+          unsigned long long scale2;   // (scale, scale)
+          asm("mov.b64 %0, {%1, %1};" : "=l"(scale2) : "f"(scale));
           const int g = g_tile + kb;
           const int ls = g % kLoadStages, bs = g % kBStages, cs = g % kCodeStages;
           ok = mbar_wait(bar_pkfull(cs), (uint32_t)((g / kCodeStages) & 1), abort_flag, p.status, 5);
@@ -428,22 +430,25 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
                            : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3])
                            : "r"(pk + (half == 0 ? src_off0 : src_off1))
                            : "memory");
-              // 16 table lookups (independent, issued back to back), then 32 multiplies, 16 roundings, 4 stores
-              float2 codes[16];
+              // 16 table lookups (independent, issued back to back), then 16 two-wide multiplies (mul.rn.f32x2 rounds
+              // each lane like a scalar multiply), 16 roundings, 4 stores
+              unsigned long long codes[16];
 #pragma unroll
               for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
                   const uint32_t byte = __byte_perm(words[c], 0u, 0x4440u + (uint32_t)b);
-                  asm("ld.shared.v2.f32 {%0,%1}, [%2];"
-                      : "=f"(codes[c * 4 + b].x), "=f"(codes[c * 4 + b].y) : "r"(lut_lane + byte * 128u));
+                  asm("ld.shared.b64 %0, [%1];" : "=l"(codes[c * 4 + b]) : "r"(lut_lane + byte * 128u));
                 }
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
                 uint32_t out[4];
 #pragma unroll
-                for (int b = 0; b < 4; ++b)
-                  out[b] = pack_bf16x2(__fmul_rn(codes[c * 4 + b].x, scale), __fmul_rn(codes[c * 4 + b].y, scale));
+                for (int b = 0; b < 4; ++b) {
+                  unsigned long long prod;
+                  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(prod) : "l"(codes[c * 4 + b]), "l"(scale2));
+                  asm("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.bf16x2.f32 %0, hi, lo;\n\t}" : "=r"(out[b]) : "l"(prod));
+                }
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + dst_off + ((((uint32_t)(4 * half + c)) ^ swz) << 4)),
                              "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3])
                              : "memory");

@@ -19,6 +19,7 @@ import torch.distributed as dist
 from torch import nn
 from torch.nn import functional as F
 
+from molt_b200 import _native
 from molt_b200.data_parallel import GradArena, lora_parameters
 from molt_b200.methods.quant_state import NestedState, QuantState
 from molt_b200.modules import GatedMLP, NF4LoRALinear
@@ -213,6 +214,8 @@ class QLoRAStep:
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._static_tokens = self._static_targets = self._static_loss = None
         self._eager_steps = 0
+        self.graph_launches = 0      # library kernel launches recorded in the CUDA graph
+        self.replayed_launches = 0   # library kernel launches executed through graph replays so far
 
     def _forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         self.arena.zero()
@@ -226,8 +229,11 @@ class QLoRAStep:
         self._static_tokens = tokens.clone()
         self._static_targets = targets.clone()
         self._graph = torch.cuda.CUDAGraph()
+        lib = _native.library()
+        before = lib.molt_launch_count()
         with torch.cuda.graph(self._graph):
             self._static_loss = self._forward_backward(self._static_tokens, self._static_targets)
+        self.graph_launches = int(lib.molt_launch_count() - before)   # library kernels recorded; each replay runs them
 
     def run(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         if self.cuda_graph and self._graph is None and self._eager_steps >= 2:
@@ -236,6 +242,7 @@ class QLoRAStep:
             self._static_tokens.copy_(tokens)
             self._static_targets.copy_(targets)
             self._graph.replay()
+            self.replayed_launches += self.graph_launches
             loss = self._static_loss
         else:
             loss = self._forward_backward(tokens, targets)
