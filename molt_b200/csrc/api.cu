@@ -72,12 +72,24 @@ struct Arena {
   size_t size;
   size_t used;
   bool dry;
-  Arena(void* p, size_t bytes, bool sizing_only = false)
-      : base(reinterpret_cast<unsigned char*>(p)), size(bytes), used(0), dry(sizing_only) {}
+  bool size_optional;   // while sizing: count the optional regions too
+  Arena(void* p, size_t bytes, bool sizing_only = false, bool with_optional = true)
+      : base(reinterpret_cast<unsigned char*>(p)), size(bytes), used(0), dry(sizing_only), size_optional(with_optional) {}
   void* take(size_t bytes) {
     const size_t start = (used + 255) & ~size_t(255);
     used = start + bytes;
     if (dry) return reinterpret_cast<void*>(uintptr_t(256));  // non-NULL placeholder while sizing
+    return base + start;
+  }
+  // A region the caller can do without: NULL when the workspace has no room for it.  Take it after the required ones.
+  void* take_optional(size_t bytes) {
+    const size_t start = (used + 255) & ~size_t(255);
+    if (dry) {
+      if (size_optional) used = start + bytes;
+      return nullptr;
+    }
+    if (base == nullptr || start + bytes > size) return nullptr;
+    used = start + bytes;
     return base + start;
   }
   bool fits() const { return dry || (used <= size && (used == 0 || base != nullptr)); }
@@ -189,11 +201,13 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
   auto* bs = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)w->n * 64 * 2));
   const float* absmax = nullptr;
   if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
+  const bool fits = arena.fits();
+  void* split = arena.take_optional(sm100_split_bytes());
   if (arena.dry) return MOLT_OK;
-  MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
+  MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
   if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, bs, nullptr, s)) return rc;
   if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t, s)) return rc;
-  return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, s);
+  return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, split, s);
 }
 
 // ---- backward --------------------------------------------------------------------------------------
@@ -238,12 +252,14 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
   const float* absmax = nullptr;
   if (dxb != nullptr)
     if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
+  const bool fits = arena.fits();
+  void* split = dxb != nullptr ? arena.take_optional(sm100_split_bytes()) : nullptr;
   if (arena.dry) return MOLT_OK;
-  MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace too small");
+  MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace too small");
   if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, nullptr, bt, s)) return rc;
   if (int rc = rowsum_mma(gb, bt, rp, m, w->n, u, s)) return rc;  // U = dY . (sB)
   if (dxb != nullptr)
-    if (int rc = sm100_gemm(true, view, absmax, gb, u, a16, rp, dxb, m, s)) return rc;
+    if (int rc = sm100_gemm(true, view, absmax, gb, u, a16, rp, dxb, m, split, s)) return rc;
   if (want_grads) {
     if (t_own != nullptr)
       if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t_own, s)) return rc;
@@ -266,9 +282,11 @@ static int dx_impl(const molt_nf4_desc* w, const void* dy, const void* lora_grad
   if (path == MOLT_PATH_TCGEN05 && lora_grad == nullptr) {
     const float* absmax = nullptr;
     if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
+    const bool fits = arena.fits();
+    void* split = arena.take_optional(sm100_split_bytes());
     if (arena.dry) return MOLT_OK;
-    MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_dx: workspace too small");
-    return sm100_gemm(true, view, absmax, gb, nullptr, nullptr, 0, dxb, m, s);
+    MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_dx: workspace too small");
+    return sm100_gemm(true, view, absmax, gb, nullptr, nullptr, 0, dxb, m, split, s);
   }
   if (arena.dry) return MOLT_OK;
   return general_backward_input(view, gb, reinterpret_cast<const __nv_bfloat16*>(lora_grad), rank, lora_a,
@@ -304,7 +322,9 @@ static int check_linear_args(const char* who, const molt_nf4_desc* w, int rank, 
   return MOLT_OK;
 }
 
-extern "C" size_t molt_workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank) {
+// with_optional = false gives the smallest workspace the entry points accept (the tcgen05 GEMMs then keep their plain
+// tile schedule instead of splitting the tiles of the last wave).
+size_t molt::workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank, bool with_optional) {
   if (m < 0 || n <= 0 || k <= 0 || rank < 1 || rank > 64) return 0;
   molt_nf4_desc fake;
   memset(&fake, 0, sizeof(fake));
@@ -319,7 +339,7 @@ extern "C" size_t molt_workspace_bytes(int op, int64_t m, int64_t n, int64_t k, 
   for (int path : paths) {
     if (path != MOLT_PATH_GENERAL && !(k % 64 == 0 && n % 64 == 0)) continue;
     if (path == MOLT_PATH_GEMV && !(op == MOLT_OP_LORA_FWD && m <= 16)) continue;
-    Arena arena(nullptr, 0, true);
+    Arena arena(nullptr, 0, true, with_optional);
     if (op == MOLT_OP_LORA_FWD) lora_fwd_impl(&fake, nullptr, nullptr, nullptr, 1.f, rank, nullptr, m, nullptr, arena, path, 0);
     else if (op == MOLT_OP_LORA_BWD)
       lora_bwd_impl(&fake, nullptr, nullptr, nullptr, nullptr, 1.f, rank, reinterpret_cast<void*>(uintptr_t(256)),
@@ -330,6 +350,10 @@ extern "C" size_t molt_workspace_bytes(int op, int64_t m, int64_t n, int64_t k, 
     if (arena.used > best) best = arena.used;
   }
   return best + 256;
+}
+
+extern "C" size_t molt_workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank) {
+  return molt::workspace_bytes(op, m, n, k, rank, true);
 }
 
 extern "C" int molt_nf4_lora_fwd(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,

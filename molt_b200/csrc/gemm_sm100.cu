@@ -380,7 +380,7 @@ bool sm100_gemm_supported(const WeightView& w, int rank) {
 
 int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                     const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
-                    cudaStream_t s);
+                    void* split_ws, cudaStream_t s);
 
 // 0 = default (CTA-pair kernel), 1 = single-CTA kernel, 2 = CTA-pair kernel (MOLT_B200_GEMM_VARIANT; for testing)
 static int forced_variant() {
@@ -391,12 +391,12 @@ static int forced_variant() {
 
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
-               cudaStream_t s) {
+               void* split_ws, cudaStream_t s) {
   // The CTA-pair kernel is the default for every token count: its pipeline is deeper and, even with half of a
   // pair tile empty (m <= 128), faster than the single-CTA kernel, which is kept as a selectable variant.
   const int variant = forced_variant();
   if (variant != 1)
-    return sm100_gemm_pair(backward, w, absmax_f32, in, low, ext, rp, out, m, s);
+    return sm100_gemm_pair(backward, w, absmax_f32, in, low, ext, rp, out, m, split_ws, s);
   if (!sm100_gemm_supported(w, rp)) return fail(MOLT_E_CAPABILITY, "tcgen05 GEMM: unsupported shape");
   const long long contraction = backward ? w.n : w.k;
   const long long out_cols = backward ? w.k : w.n;

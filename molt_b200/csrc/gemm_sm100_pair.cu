@@ -58,6 +58,9 @@ struct Params {
   int num_kb;
   int ext_steps;         // rp / 16, 0 = no low-rank block
   int tiles_m, tiles_n;  // pair tiles: 256 tokens x 256 columns
+  int full_tiles;        // tiles on the static schedule (whole waves); the tiles after them are split along the contraction
+  float* split_partial;  // [pairs][2 CTAs][256 columns][128 rows] fp32 partial accumulators of the split tiles
+  int* split_flags;      // [tiles - full_tiles] arrival counters (zero before the launch)
   int nibble_high_first;
   unsigned long long* trace;   // optional [2 CTAs][4 roles][256 events] timestamps (ns) for pipeline analysis
   int debug;             // timing experiments only: 1 = skip decode, 2 = skip MMA issue, 4 = skip epilogue stores
@@ -140,8 +143,77 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
   tm = first_m + inside % rows;
 }
 
+// Work of one CTA pair.  Whole waves of tiles follow the static schedule (tile = pair, pair + pairs, ...).  The tiles
+// of the last, partial wave are cut along the contraction instead: their blocks, laid end to end, are dealt out in
+// equal contiguous ranges, so every pair gets at most the tail of one tile and the head of the next.  The pair that
+// computes a tile's head owns the tile: the others write their fp32 partial accumulators to global memory and
+// count themselves in on the tile's flag; the owner waits for the count, adds the partials in pair order
+// (deterministic) and stores the tile.  A pair first works off whatever it contributes and only then waits as an
+// owner, and what it waits for is the first thing the later pairs do, so the waits cannot form a cycle.
+struct WorkPlan {
+  int num_pairs, pair_id, blocks;   // blocks per tile, the low-rank block included
+  int full_tiles, num_tiles;
+  int tail_units;                   // blocks of all split tiles (at most pairs x blocks: fits easily)
+  int tail_begin, tail_end;         // this pair's range of them
+};
+struct WorkItem {
+  int tile, kb0, kb1;
+  int u;                            // position in the tail (split tiles only)
+  bool valid;
+};
+__device__ __forceinline__ int tail_range_begin(const WorkPlan& w, int pair) {
+  return w.tail_units * pair / w.num_pairs;   // at most pairs^2 x blocks < 2^31 (the host checks)
+}
+__device__ __forceinline__ void tail_item(const WorkPlan& w, WorkItem& it) {
+  if (it.u >= w.tail_end) {
+    it.valid = false;
+    return;
+  }
+  it.tile = w.full_tiles + it.u / w.blocks;
+  it.kb0 = it.u % w.blocks;
+  const int left = w.tail_end - it.u;
+  it.kb1 = left < w.blocks - it.kb0 ? it.kb0 + left : w.blocks;
+  it.valid = true;
+}
+__device__ __forceinline__ WorkItem first_item(const WorkPlan& w) {
+  WorkItem it;
+  it.tile = w.pair_id;
+  it.kb0 = 0;
+  it.kb1 = w.blocks;
+  it.u = w.tail_begin;
+  it.valid = true;
+  if (it.tile >= w.full_tiles) tail_item(w, it);
+  return it;
+}
+__device__ __forceinline__ void next_item(const WorkPlan& w, WorkItem& it) {
+  if (it.tile < w.full_tiles) {
+    it.tile += w.num_pairs;
+    if (it.tile < w.full_tiles) return;
+    it.u = w.tail_begin;
+  } else {
+    it.u += it.kb1 - it.kb0;
+  }
+  tail_item(w, it);
+}
+// a split tile's part that does not start at block 0 is handed to the tile's owner
+__device__ __forceinline__ bool item_contributes(const WorkPlan& w, const WorkItem& it) {
+  return it.tile >= w.full_tiles && it.kb0 > 0;
+}
+// Number of pairs that contribute to the split tile this pair owns (it holds blocks [0, kb1) of it).  Every pair has a
+// non-empty range (the host splits only when there are at least as many tail blocks as pairs), so the contributors
+// are the pairs right after this one.
+__device__ __forceinline__ int item_contributors(const WorkPlan& w, const WorkItem& it) {
+  if (it.tile < w.full_tiles || it.kb0 > 0 || it.kb1 == w.blocks) return 0;
+  const int tile_end = (it.tile - w.full_tiles + 1) * w.blocks;
+  int count = 0;
+  for (int c = w.pair_id + 1; c < w.num_pairs && tail_range_begin(w, c) < tile_end; ++c) ++count;
+  return count;
+}
+
 template <bool BACKWARD, int kLoadStages, int kBStages, int kStoreBufs>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+// 576 threads x 112 registers = 63 K of the SM's 64 K registers (a launch bound of 576 threads would be rounded to 640
+// threads and cap the kernel at 96)
+__global__ void __cluster_dims__(2, 1, 1) __maxnreg__(112)
 nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_packed,
                            const __grid_constant__ CUtensorMap map_low, const __grid_constant__ CUtensorMap map_ext,
                            const __grid_constant__ CUtensorMap map_out, const __grid_constant__ Params p) {
@@ -214,6 +286,15 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   const int num_pairs = gridDim.x >> 1;
   const int pair_id = blockIdx.x >> 1;
   const int blocks_per_tile = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
+  WorkPlan plan;
+  plan.num_pairs = num_pairs;
+  plan.pair_id = pair_id;
+  plan.blocks = blocks_per_tile;
+  plan.full_tiles = p.full_tiles;
+  plan.num_tiles = num_tiles;
+  plan.tail_units = (num_tiles - p.full_tiles) * blocks_per_tile;
+  plan.tail_begin = tail_range_begin(plan, pair_id);
+  plan.tail_end = tail_range_begin(plan, pair_id + 1);
 
   if (warp == kProducerWarp) {
     // ================= TMA producer (each CTA loads its own token rows and its own half of the codes) ==========
@@ -222,24 +303,25 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     // and the activations of block t - kLag; both ring slots are free once block t - kCodeStages is consumed.
     constexpr int kLag = kCodeStages - kLoadStages;
     struct Cursor {
-      int tile, kb, tm, tn;
+      WorkItem item;
+      int kb, tm, tn;
       bool valid;
     };
     auto start_cursor = [&]() {
       Cursor c;
-      c.tile = pair_id;
-      c.kb = 0;
-      c.valid = c.tile < num_tiles;
+      c.item = first_item(plan);
+      c.valid = c.item.valid;
+      c.kb = c.item.kb0;
       c.tm = c.tn = 0;
-      if (c.valid) pair_tile_coords(c.tile, p.tiles_m, p.tiles_n, c.tm, c.tn);
+      if (c.valid) pair_tile_coords(c.item.tile, p.tiles_m, p.tiles_n, c.tm, c.tn);
       return c;
     };
     auto advance = [&](Cursor& c) {
-      if (++c.kb == blocks_per_tile) {
-        c.kb = 0;
-        c.tile += num_pairs;
-        c.valid = c.tile < num_tiles;
-        if (c.valid) pair_tile_coords(c.tile, p.tiles_m, p.tiles_n, c.tm, c.tn);
+      if (++c.kb == c.item.kb1) {
+        next_item(plan, c.item);
+        c.valid = c.item.valid;
+        c.kb = c.item.kb0;
+        if (c.valid) pair_tile_coords(c.item.tile, p.tiles_m, p.tiles_n, c.tm, c.tn);
       }
     };
     Cursor pc = start_cursor(), ac = start_cursor();
@@ -295,13 +377,13 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         int ls = 0, bs = 0, acc = 0, g = 0;
         uint32_t bphase = 0, acc_phase = 0;
         bool ok = true;
-        for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        for (WorkItem item = first_item(plan); item.valid && ok; next_item(plan, item)) {
           ok = mbar_wait_cluster(bar_accempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2);
           if (!ok) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
           uint32_t accumulate = 0u;
-          for (int kb = 0; kb < p.num_kb; ++kb) {
+          for (int kb = item.kb0; kb < item.kb1; ++kb) {
             // The decoders of both CTAs arrive on b_full only after their own activation tile has landed, so
             // this one wait covers both operands in both CTAs.
             ok = mbar_wait_cluster(bar_bfull(bs), bphase, abort_flag, p.status, 4);
@@ -309,32 +391,23 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
             tc_fence_after();
             const uint32_t a_lo = a_lo0 + (uint32_t)ls * (kLoadStageBytes >> 4);
             const uint32_t b_lo = b_lo0 + (uint32_t)bs * (kTileBBytes >> 4);
-            umma_bf16_pair(d_tmem, desc64(a_lo, desc_hi), desc64(b_lo, desc_hi), idesc, accumulate);
+            if (kb < p.num_kb) {
+              umma_bf16_pair(d_tmem, desc64(a_lo, desc_hi), desc64(b_lo, desc_hi), idesc, accumulate);
 #pragma unroll
-            for (int ks = 1; ks < BK / 16; ++ks)
-              umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc, 1u);
+              for (int ks = 1; ks < BK / 16; ++ks)
+                umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc, 1u);
+            } else {   // the low-rank block
+              for (int ks = 0; ks < p.ext_steps; ++ks)
+                umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc,
+                               (accumulate | (uint32_t)(ks > 0)));
+            }
             accumulate = 1u;
             // one commit releases this block's load stage and B stage in both CTAs once the MMAs have read them
             umma_commit_both(bar_consumed(g));
-            if (kb == blocks_per_tile - 1) umma_commit_both(bar_accfull(acc));
+            if (kb == item.kb1 - 1) umma_commit_both(bar_accfull(acc));
 #ifdef MOLT_PAIR_TRACE
             MOLT_TRACE(1, g);
 #endif
-            ++g;
-            if (++ls == kLoadStages) ls = 0;
-            if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
-          }
-          if (ok && p.ext_steps > 0) {   // the low-rank block
-            ok = mbar_wait_cluster(bar_bfull(bs), bphase, abort_flag, p.status, 4);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t a_lo = a_lo0 + (uint32_t)ls * (kLoadStageBytes >> 4);
-            const uint32_t b_lo = b_lo0 + (uint32_t)bs * (kTileBBytes >> 4);
-            for (int ks = 0; ks < p.ext_steps; ++ks)
-              umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc,
-                             (accumulate | (uint32_t)(ks > 0)));
-            umma_commit_both(bar_consumed(g));
-            umma_commit_both(bar_accfull(acc));
             ++g;
             if (++ls == kLoadStages) ls = 0;
             if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
@@ -372,10 +445,10 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     const uint32_t dst_off = !BACKWARD ? (uint32_t)u * 128u : (uint32_t)seg_a * 8192u + (uint32_t)seg_j * 128u;
     const uint32_t swz = (dst_off >> 7) & 7u;
     constexpr int kPrefetch = 4;   // absmax values are fetched this many of the group's blocks ahead of their use
-    int g_tile = 0;                // running block number of the tile's first block
-    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, g_tile += blocks_per_tile) {
+    int g_tile = 0;                // running block number of the item's first block
+    for (WorkItem item = first_item(plan); item.valid && ok; g_tile += item.kb1 - item.kb0, next_item(plan, item)) {
       int tm, tn;
-      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      pair_tile_coords(item.tile, p.tiles_m, p.tiles_n, tm, tn);
       const int col0 = tn * BN + (int)rank * BNH;   // first B row (forward: weight row; backward: weight column)
       // forward : absmax[(col0 + i) * kpr + kb]            backward: absmax[(kb * 64 + j) * kpr + col0 / 64 + a]
       const float* scale_ptr;
@@ -395,22 +468,23 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       auto load_scale = [&](int kb) -> float {
         return (kb < p.num_kb && scale_ok) ? __ldg(scale_ptr + (long long)kb * scale_step) : 0.f;
       };
-      const int kb_first = ((grp - g_tile) % kDecodeGroups + kDecodeGroups) % kDecodeGroups;   // group's first block
+      // the group's first block of this item: running block number g_tile + (kb - kb0) is congruent to grp
+      const int kb_first = item.kb0 + ((grp - g_tile) % kDecodeGroups + kDecodeGroups) % kDecodeGroups;
       float cur[kPrefetch];
 #pragma unroll
       for (int q = 0; q < kPrefetch; ++q) cur[q] = load_scale(kb_first + kDecodeGroups * q);
-      for (int kb0 = kb_first; kb0 < blocks_per_tile && ok; kb0 += kDecodeGroups * kPrefetch) {
+      for (int kb0 = kb_first; kb0 < item.kb1 && ok; kb0 += kDecodeGroups * kPrefetch) {
         float nxt[kPrefetch];
 #pragma unroll
         for (int q = 0; q < kPrefetch; ++q) nxt[q] = load_scale(kb0 + kDecodeGroups * (kPrefetch + q));
 #pragma unroll
         for (int q = 0; q < kPrefetch; ++q) {
           const int kb = kb0 + kDecodeGroups * q;
-          if (kb >= blocks_per_tile || !ok) continue;
+          if (kb >= item.kb1 || !ok) continue;
           const float scale = cur[q];
           unsigned long long scale2;   // (scale, scale)
           asm("mov.b64 %0, {%1, %1};" : "=l"(scale2) : "f"(scale));
-          const int g = g_tile + kb;
+          const int g = g_tile + (kb - item.kb0);
           const int ls = g % kLoadStages, bs = g % kBStages, cs = g % kCodeStages;
           ok = mbar_wait(bar_pkfull(cs), (uint32_t)((g / kCodeStages) & 1), abort_flag, p.status, 5);
           if (ok && g >= kBStages)   // the block that used this B stage must have been consumed
@@ -482,8 +556,8 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
 #pragma unroll
         for (int q = 0; q < kPrefetch; ++q) cur[q] = nxt[q];
       }
-      // the low-rank barrier completes once per tile, whichever group handled it
-      if (p.ext_steps > 0) ext_phase ^= 1u;
+      // the low-rank barrier completes once per item that holds the low-rank block, whichever group handled it
+      if (p.ext_steps > 0 && item.kb1 == blocks_per_tile) ext_phase ^= 1u;
     }
   } else {
     // ================= epilogue: TMEM -> bf16 -> shared -> TMA store (own 128 token rows) =================
@@ -493,14 +567,53 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     uint32_t acc_phase = 0;
     int store_buf = 0;
     bool ok = true;
-    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+    for (WorkItem item = first_item(plan); item.valid && ok; next_item(plan, item)) {
       int tm, tn;
-      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      pair_tile_coords(item.tile, p.tiles_m, p.tiles_n, tm, tn);
       const int row0 = tm * 2 * BM + (int)rank * BM;
       ok = mbar_wait_cluster(bar_accfull(acc), acc_phase, abort_flag, p.status, 8);
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)acc * BN;
+      if (item_contributes(plan, item)) {
+        // ---- part of a split tile: fp32 partial accumulator -> global, then count this CTA in on the tile's flag ----
+        // layout [column][row] so that a warp's 32 rows of one column are one 128-byte line
+        float* part = p.split_partial + ((size_t)(pair_id * 2 + (int)rank) * BN) * BM + row;
+        for (int cg = 0; cg < BN / 32; ++cg) {
+          uint32_t v[32];
+          tmem_ld32(t_row + (uint32_t)cg * 32u, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) __stcg(part + (size_t)(cg * 32 + c) * BM, __uint_as_float(v[c]));
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 0) atomicAdd(p.split_flags + (item.tile - plan.full_tiles), 1);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(accempty_remote_base + 8u * (uint32_t)acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        continue;
+      }
+      const int contributors = item_contributors(plan, item);
+      if (contributors > 0) {
+        // ---- owner of a split tile: every contributing CTA must have counted itself in (bounded wait) ----
+        if (threadIdx.x == 0) {
+          const volatile int* flag = p.split_flags + (item.tile - plan.full_tiles);
+          const long long start = clock64();
+          while (*flag < 2 * contributors) {
+            if (*abort_flag || clock64() - start > 2000000000LL) {
+              *abort_flag = 1;
+              atomicCAS(p.status, 0, (kStatusTimeout << 24) | (10 << 16) | (int)(blockIdx.x & 0xffff));
+              break;
+            }
+            __nanosleep(200);
+          }
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*abort_flag) { ok = false; break; }
+      }
       for (int cg = 0; cg < BN / 64 && !(p.debug & 4); ++cg) {
         const uint32_t stage_addr = store0 + (uint32_t)store_buf * kStoreBytes;
         // the store that last read this staging buffer must have finished reading it
@@ -513,6 +626,17 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         tmem_ld32(t_row + (uint32_t)cg * 64u, v0);
         tmem_ld32(t_row + (uint32_t)cg * 64u + 32u, v1);
         tmem_ld_wait();
+        if (contributors > 0) {
+          // add the other pairs' partial sums of this tile, in pair order
+          for (int c = pair_id + 1; c <= pair_id + contributors; ++c) {
+            const float* part = p.split_partial + ((size_t)(c * 2 + (int)rank) * BN + cg * 64) * BM + row;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              v0[i] = __float_as_uint(__uint_as_float(v0[i]) + __ldcg(part + (size_t)i * BM));
+              v1[i] = __float_as_uint(__uint_as_float(v1[i]) + __ldcg(part + (size_t)(32 + i) * BM));
+            }
+          }
+        }
         const uint32_t dst_row = stage_addr + (uint32_t)row * 128u;
         const uint32_t swz = (uint32_t)row & 7u;
 #pragma unroll
@@ -571,9 +695,15 @@ int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* ptr
                     uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
                     const char* what);
 
+// Scratch for splitting the last wave: one fp32 partial tile per CTA pair, then one counter per split tile.
+constexpr size_t kSplitFlagBytes = 1024;
+size_t sm100_split_bytes() {
+  return (size_t)(sm_count() / 2) * 2 * pair::BN * pair::BM * sizeof(float) + kSplitFlagBytes;
+}
+
 int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                     const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
-                    cudaStream_t s) {
+                    void* split_ws, cudaStream_t s) {
   using namespace pair;
   if (!sm100_gemm_supported(w, rp)) return fail(MOLT_E_CAPABILITY, "tcgen05 GEMM: unsupported shape");
   const long long contraction = backward ? w.n : w.k;
@@ -644,6 +774,23 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
   long long pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
   const int grid = (int)pairs * 2;
+  // Whole waves run the static schedule; a last partial wave is split along the contraction when scratch was given.
+  p.full_tiles = (int)tiles;
+  p.split_partial = nullptr;
+  p.split_flags = nullptr;
+  {
+    const char* env = getenv("MOLT_B200_NO_SPLIT");   // timing experiments: keep the plain schedule
+    const long long rem = tiles % pairs;
+    const long long blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
+    if (split_ws != nullptr && rem != 0 && tiles > pairs && pairs == sm_count() / 2 && rem * blocks >= pairs &&
+        rem * blocks * pairs < (1LL << 30) && !(env != nullptr && atoi(env) != 0)) {
+      p.full_tiles = (int)(tiles - rem);
+      p.split_partial = reinterpret_cast<float*>(split_ws);
+      p.split_flags = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(split_ws) + sm100_split_bytes() - kSplitFlagBytes);
+      if (rem * (long long)sizeof(int) > (long long)kSplitFlagBytes) return fail(MOLT_E_RUNTIME, "tcgen05 GEMM: too many split tiles");
+      MOLT_CUDA(cudaMemsetAsync(p.split_flags, 0, (size_t)rem * sizeof(int), s));
+    }
+  }
   static thread_local bool configured[64][2][4] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));

@@ -36,9 +36,12 @@ int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_
 //   forward : out[m, n] = in[m, k] . deq(W)^T + low[m, 0..rp) . ext[n, 0..rp)^T        (ext = bf16(s B) [n, 64])
 //   backward: out[m, k] = in[m, n] . deq(W)   + low[m, 0..rp) . ext[0..rp, k]           (ext = bf16(A)   [rp, k])
 // low is bf16 [m, 64]; low == nullptr skips the low-rank block.
+// split_ws: sm100_split_bytes() bytes of scratch for splitting the tiles of the last wave, or NULL (plain schedule)
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
-               cudaStream_t s);
+               void* split_ws, cudaStream_t s);
+size_t sm100_split_bytes();
+size_t workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank, bool with_optional);
 bool sm100_gemm_supported(const WeightView& w, int rank);
 
 // elementwise helpers used by the block op

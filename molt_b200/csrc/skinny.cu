@@ -71,15 +71,32 @@ __global__ void __launch_bounds__(256) rowsum_mma_kernel(const __nv_bfloat16* __
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
   const long long chunks = cols / 32;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (long long c = warp; c < chunks; c += 8) {
-    const long long col = c * 32 + t * 8;
-    const uint4 lo = lo_ok ? __ldg(reinterpret_cast<const uint4*>(in + r_lo * cols + col)) : zero;
-    const uint4 hi = hi_ok ? __ldg(reinterpret_cast<const uint4*>(in + r_hi * cols + col)) : zero;
+  // Four chunks per trip: the eight activation loads (the HBM stream) are requested before anything is used, so a
+  // warp keeps 4 KB in flight; the weight-side loads hit L1/L2.
+  constexpr int kUnroll = 4;
+  const __nv_bfloat16* lo_ptr = in + (lo_ok ? r_lo : 0) * cols + t * 8;
+  const __nv_bfloat16* hi_ptr = in + (hi_ok ? r_hi : 0) * cols + t * 8;
+  for (long long c0 = warp; c0 < chunks; c0 += 8 * kUnroll) {
+    uint4 lo[kUnroll], hi[kUnroll];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      const uint4 b = __ldg(reinterpret_cast<const uint4*>(wt + (long long)(j * 8 + g) * cols + col));
-      mma_bf16_16816(acc[j], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
-      mma_bf16_16816(acc[j], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long c = c0 + 8 * u;
+      const bool in_range = c < chunks;
+      lo[u] = (lo_ok && in_range) ? __ldcs(reinterpret_cast<const uint4*>(lo_ptr + c * 32)) : zero;
+      hi[u] = (hi_ok && in_range) ? __ldcs(reinterpret_cast<const uint4*>(hi_ptr + c * 32)) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long c = c0 + 8 * u;
+      if (c < chunks) {
+        const long long col = c * 32 + t * 8;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const uint4 b = __ldg(reinterpret_cast<const uint4*>(wt + (long long)(j * 8 + g) * cols + col));
+          mma_bf16_16816(acc[j], lo[u].x, hi[u].x, lo[u].y, hi[u].y, b.x, b.y);
+          mma_bf16_16816(acc[j], lo[u].z, hi[u].z, lo[u].w, hi[u].w, b.z, b.w);
+        }
+      }
     }
   }
 #pragma unroll

@@ -57,7 +57,8 @@ extern "C" int molt_nf4_lora_fwd_static(const molt_nf4_desc* w, const void* x, c
                                         const float* lora_b, float scaling, int rank, void* y, int64_t m, int path,
                                         uintptr_t stream) {
   MOLT_REQUIRE(w != nullptr, MOLT_E_VALUE, "molt_nf4_lora_fwd_static: weight descriptor is NULL");
-  const size_t need = molt_workspace_bytes(MOLT_OP_LORA_FWD, m, w->n, w->k, rank);
+  // the smallest workspace the forward accepts (without the optional scratch of the tensor-core kernel's split schedule)
+  const size_t need = workspace_bytes(MOLT_OP_LORA_FWD, m, w->n, w->k, rank, false);
   MOLT_REQUIRE(need != 0, MOLT_E_VALUE, "molt_nf4_lora_fwd_static: invalid sizes (m=%lld n=%lld k=%lld rank=%d)",
                (long long)m, (long long)w->n, (long long)w->k, rank);
   MOLT_REQUIRE(need <= kStaticScratchBytes, MOLT_E_VALUE,
