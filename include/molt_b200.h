@@ -91,7 +91,10 @@ int molt_nf4_dequant(const molt_nf4_desc* w, void* out, int out_dtype, uintptr_t
  * (reference methods/nf4_backward.py:145-164). */
 int molt_nf4_resolve_absmax(const molt_nf4_desc* w, float* out, uintptr_t stream);
 
-/* Scratch bytes the given op needs for these sizes (0 if none). */
+/* Scratch bytes the given op uses for these sizes (0 if none).  The figure includes an optional part (about 38 MB on a
+ * 148-SM device): room for the fp32 partial tiles with which the tensor-core GEMMs split the tiles of their last,
+ * partial wave along the contraction.  A smaller workspace that still holds the required buffers is accepted; the
+ * GEMMs then keep the plain tile schedule. */
 size_t molt_workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank);
 
 /* y[m, n] = x[m, k] . deq(W)^T + scaling * (x . A^T) . B^T      (x, y bf16; A[rank, k], B[n, rank] fp32)

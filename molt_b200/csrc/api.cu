@@ -149,7 +149,11 @@ static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m,
 }
 
 // fp32 absmax for the tcgen05 kernels: the descriptor's own array, or the nested form resolved into the arena.
-static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s, const float** out) {
+// With `deferred` the resolve is not launched here: *deferred gets the buffer and the caller folds the work into its
+// next preparation kernel.
+static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s, const float** out,
+                           float** deferred = nullptr) {
+  if (deferred != nullptr) *deferred = nullptr;
   if (w->absmax_kind == MOLT_ABSMAX_F32) {
     *out = reinterpret_cast<const float*>(w->absmax);
     return MOLT_OK;
@@ -159,6 +163,10 @@ static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s,
   *out = buf;
   if (arena.dry) return MOLT_OK;
   MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "workspace too small");
+  if (deferred != nullptr) {
+    *deferred = buf;
+    return MOLT_OK;
+  }
   return molt_nf4_resolve_absmax(w, buf, reinterpret_cast<uintptr_t>(s));
 }
 
@@ -200,12 +208,13 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
   auto* a16 = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
   auto* bs = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)w->n * 64 * 2));
   const float* absmax = nullptr;
-  if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
+  float* to_resolve = nullptr;
+  if (int rc = resolved_absmax(w, arena, s, &absmax, &to_resolve)) return rc;
   const bool fits = arena.fits();
   void* split = arena.take_optional(sm100_split_bytes());
   if (arena.dry) return MOLT_OK;
   MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
-  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, bs, nullptr, s)) return rc;
+  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, bs, nullptr, &view, to_resolve, s)) return rc;
   if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t, s)) return rc;
   return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, split, s);
 }
@@ -250,13 +259,14 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
     partial = reinterpret_cast<float*>(arena.take(pa > pb ? pa : pb));
   }
   const float* absmax = nullptr;
+  float* to_resolve = nullptr;
   if (dxb != nullptr)
-    if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
+    if (int rc = resolved_absmax(w, arena, s, &absmax, &to_resolve)) return rc;
   const bool fits = arena.fits();
   void* split = dxb != nullptr ? arena.take_optional(sm100_split_bytes()) : nullptr;
   if (arena.dry) return MOLT_OK;
   MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace too small");
-  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, nullptr, bt, s)) return rc;
+  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, nullptr, bt, &view, to_resolve, s)) return rc;
   if (int rc = rowsum_mma(gb, bt, rp, m, w->n, u, s)) return rc;  // U = dY . (sB)
   if (dxb != nullptr)
     if (int rc = sm100_gemm(true, view, absmax, gb, u, a16, rp, dxb, m, split, s)) return rc;

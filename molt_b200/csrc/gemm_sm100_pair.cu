@@ -59,11 +59,11 @@ struct Params {
   int ext_steps;         // rp / 16, 0 = no low-rank block
   int tiles_m, tiles_n;  // pair tiles: 256 tokens x 256 columns
   int full_tiles;        // tiles on the static schedule (whole waves); the tiles after them are split along the contraction
-  float* split_partial;  // [pairs][2 CTAs][256 columns][128 rows] fp32 partial accumulators of the split tiles
-  int* split_flags;      // [tiles - full_tiles] arrival counters (zero before the launch)
+  float* split_partial;  // [pairs][2 parts][2 CTAs][128 rows][256 columns] fp32 partial accumulators of the split tiles
   int nibble_high_first;
   unsigned long long* trace;   // optional [2 CTAs][4 roles][256 events] timestamps (ns) for pipeline analysis
-  int debug;             // timing experiments only: 1 = skip decode, 2 = skip MMA issue, 4 = skip epilogue stores
+  int debug;             // timing experiments only: 1 = skip decode, 2 = skip MMA issue, 4 = skip epilogue stores,
+                         // 16 = skip writing split partials
   float codebook[16];
 };
 
@@ -145,11 +145,10 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
 
 // Work of one CTA pair.  Whole waves of tiles follow the static schedule (tile = pair, pair + pairs, ...).  The tiles
 // of the last, partial wave are cut along the contraction instead: their blocks, laid end to end, are dealt out in
-// equal contiguous ranges, so every pair gets at most the tail of one tile and the head of the next.  The pair that
-// computes a tile's head owns the tile: the others write their fp32 partial accumulators to global memory and
-// count themselves in on the tile's flag; the owner waits for the count, adds the partials in pair order
-// (deterministic) and stores the tile.  A pair first works off whatever it contributes and only then waits as an
-// owner, and what it waits for is the first thing the later pairs do, so the waits cannot form a cycle.
+// equal contiguous ranges, so every pair gets at most the tail of one tile and the head of the next.  Every part of
+// a split tile leaves the kernel as an fp32 partial accumulator in global memory; a small second kernel adds the
+// parts of each tile in pair order (deterministic) and writes the bf16 output.  Nothing inside the GEMM kernel waits
+// for another pair.
 struct WorkPlan {
   int num_pairs, pair_id, blocks;   // blocks per tile, the low-rank block included
   int full_tiles, num_tiles;
@@ -161,7 +160,7 @@ struct WorkItem {
   int u;                            // position in the tail (split tiles only)
   bool valid;
 };
-__device__ __forceinline__ int tail_range_begin(const WorkPlan& w, int pair) {
+__host__ __device__ __forceinline__ int tail_range_begin(const WorkPlan& w, int pair) {
   return w.tail_units * pair / w.num_pairs;   // at most pairs^2 x blocks < 2^31 (the host checks)
 }
 __device__ __forceinline__ void tail_item(const WorkPlan& w, WorkItem& it) {
@@ -195,31 +194,20 @@ __device__ __forceinline__ void next_item(const WorkPlan& w, WorkItem& it) {
   }
   tail_item(w, it);
 }
-// a split tile's part that does not start at block 0 is handed to the tile's owner
-__device__ __forceinline__ bool item_contributes(const WorkPlan& w, const WorkItem& it) {
-  return it.tile >= w.full_tiles && it.kb0 > 0;
-}
-// Number of pairs that contribute to the split tile this pair owns (it holds blocks [0, kb1) of it).  Every pair has a
-// non-empty range (the host splits only when there are at least as many tail blocks as pairs), so the contributors
-// are the pairs right after this one.
-__device__ __forceinline__ int item_contributors(const WorkPlan& w, const WorkItem& it) {
-  if (it.tile < w.full_tiles || it.kb0 > 0 || it.kb1 == w.blocks) return 0;
-  const int tile_end = (it.tile - w.full_tiles + 1) * w.blocks;
-  int count = 0;
-  for (int c = w.pair_id + 1; c < w.num_pairs && tail_range_begin(w, c) < tile_end; ++c) ++count;
-  return count;
+// Slot of a pair's partial accumulator: two per pair, [0] for the part that ends a tile, [1] for the part that starts one.
+__host__ __device__ __forceinline__ size_t split_slot_offset(int pair, int starts_tile, int rank) {
+  return ((size_t)(pair * 2 + starts_tile) * 2 + rank) * BM * BN;
 }
 
 template <bool BACKWARD, int kLoadStages, int kBStages, int kStoreBufs>
-// 576 threads x 112 registers = 63 K of the SM's 64 K registers (a launch bound of 576 threads would be rounded to 640
-// threads and cap the kernel at 96)
-__global__ void __cluster_dims__(2, 1, 1) __maxnreg__(112)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_packed,
                            const __grid_constant__ CUtensorMap map_low, const __grid_constant__ CUtensorMap map_ext,
                            const __grid_constant__ CUtensorMap map_out, const __grid_constant__ Params p) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag_s;
+  __shared__ WorkPlan plan_s;
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_dyn + (base - raw);
@@ -252,6 +240,14 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
 
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
+    plan_s.num_pairs = (int)(gridDim.x >> 1);
+    plan_s.pair_id = (int)(blockIdx.x >> 1);
+    plan_s.blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
+    plan_s.full_tiles = p.full_tiles;
+    plan_s.num_tiles = p.tiles_m * p.tiles_n;
+    plan_s.tail_units = (plan_s.num_tiles - p.full_tiles) * plan_s.blocks;
+    plan_s.tail_begin = tail_range_begin(plan_s, plan_s.pair_id);
+    plan_s.tail_end = tail_range_begin(plan_s, plan_s.pair_id + 1);
     for (int s = 0; s < kLoadStages; ++s) mbar_init(bar_ldfull(s), 1);
     for (int s = 0; s < kCodeStages; ++s) mbar_init(bar_pkfull(s), 1);
     for (int g = 0; g < kConsumedSlots; ++g) mbar_init(bar_consumed(g), 1);
@@ -282,19 +278,9 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
-  const int num_pairs = gridDim.x >> 1;
   const int pair_id = blockIdx.x >> 1;
   const int blocks_per_tile = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
-  WorkPlan plan;
-  plan.num_pairs = num_pairs;
-  plan.pair_id = pair_id;
-  plan.blocks = blocks_per_tile;
-  plan.full_tiles = p.full_tiles;
-  plan.num_tiles = num_tiles;
-  plan.tail_units = (num_tiles - p.full_tiles) * blocks_per_tile;
-  plan.tail_begin = tail_range_begin(plan, pair_id);
-  plan.tail_end = tail_range_begin(plan, pair_id + 1);
+  const WorkPlan& plan = plan_s;   // in shared memory: read at item boundaries only, so it does not occupy registers
 
   if (warp == kProducerWarp) {
     // ================= TMA producer (each CTA loads its own token rows and its own half of the codes) ==========
@@ -575,44 +561,24 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)acc * BN;
-      if (item_contributes(plan, item)) {
-        // ---- part of a split tile: fp32 partial accumulator -> global, then count this CTA in on the tile's flag ----
-        // layout [column][row] so that a warp's 32 rows of one column are one 128-byte line
-        float* part = p.split_partial + ((size_t)(pair_id * 2 + (int)rank) * BN) * BM + row;
-        for (int cg = 0; cg < BN / 32; ++cg) {
+      if (item.tile >= plan.full_tiles) {
+        // ---- part of a split tile: the fp32 accumulator goes to this pair's slot, row-major ----
+        float* part = p.split_partial + split_slot_offset(pair_id, item.kb0 == 0 ? 1 : 0, (int)rank) + (size_t)row * BN;
+        for (int cg = 0; cg < BN / 32 && !(p.debug & 16); ++cg) {
           uint32_t v[32];
           tmem_ld32(t_row + (uint32_t)cg * 32u, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 32; ++c) __stcg(part + (size_t)(cg * 32 + c) * BM, __uint_as_float(v[c]));
+          for (int c = 0; c < 8; ++c)
+            __stcg(reinterpret_cast<float4*>(part + cg * 32 + c * 4),
+                   make_float4(__uint_as_float(v[4 * c]), __uint_as_float(v[4 * c + 1]), __uint_as_float(v[4 * c + 2]),
+                               __uint_as_float(v[4 * c + 3])));
         }
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 0) atomicAdd(p.split_flags + (item.tile - plan.full_tiles), 1);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(accempty_remote_base + 8u * (uint32_t)acc);
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         continue;
-      }
-      const int contributors = item_contributors(plan, item);
-      if (contributors > 0) {
-        // ---- owner of a split tile: every contributing CTA must have counted itself in (bounded wait) ----
-        if (threadIdx.x == 0) {
-          const volatile int* flag = p.split_flags + (item.tile - plan.full_tiles);
-          const long long start = clock64();
-          while (*flag < 2 * contributors) {
-            if (*abort_flag || clock64() - start > 2000000000LL) {
-              *abort_flag = 1;
-              atomicCAS(p.status, 0, (kStatusTimeout << 24) | (10 << 16) | (int)(blockIdx.x & 0xffff));
-              break;
-            }
-            __nanosleep(200);
-          }
-          __threadfence();
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*abort_flag) { ok = false; break; }
       }
       for (int cg = 0; cg < BN / 64 && !(p.debug & 4); ++cg) {
         const uint32_t stage_addr = store0 + (uint32_t)store_buf * kStoreBytes;
@@ -626,17 +592,6 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         tmem_ld32(t_row + (uint32_t)cg * 64u, v0);
         tmem_ld32(t_row + (uint32_t)cg * 64u + 32u, v1);
         tmem_ld_wait();
-        if (contributors > 0) {
-          // add the other pairs' partial sums of this tile, in pair order
-          for (int c = pair_id + 1; c <= pair_id + contributors; ++c) {
-            const float* part = p.split_partial + ((size_t)(c * 2 + (int)rank) * BN + cg * 64) * BM + row;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              v0[i] = __float_as_uint(__uint_as_float(v0[i]) + __ldcg(part + (size_t)i * BM));
-              v1[i] = __float_as_uint(__uint_as_float(v1[i]) + __ldcg(part + (size_t)(32 + i) * BM));
-            }
-          }
-        }
         const uint32_t dst_row = stage_addr + (uint32_t)row * 128u;
         const uint32_t swz = (uint32_t)row & 7u;
 #pragma unroll
@@ -688,6 +643,35 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   }
 }
 
+// out[row, col] = bf16(sum over the parts of a split tile), parts added in pair order.  One thread per 8 columns.
+__global__ void __launch_bounds__(256) split_fixup_kernel(const float* __restrict__ partial, WorkPlan plan, int tiles_m,
+                                                          int tiles_n, long long m, long long out_cols,
+                                                          __nv_bfloat16* __restrict__ out) {
+  const int tail_tile = blockIdx.y;
+  const int tile = plan.full_tiles + tail_tile;
+  int tm, tn;
+  pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+  const int idx = blockIdx.x * 256 + threadIdx.x;          // 2 * BM rows x BN / 8 column groups
+  const int r = idx / (BN / 8), cgroup = idx % (BN / 8);
+  const long long row = (long long)tm * 2 * BM + r, col = (long long)tn * BN + cgroup * 8;
+  if (row >= m || col >= out_cols) return;
+  const int unit0 = tail_tile * plan.blocks, unit1 = unit0 + plan.blocks;
+  int first = (int)(((long long)unit0 * plan.num_pairs) / plan.tail_units);   // the pair whose range holds unit0
+  while (first + 1 < plan.num_pairs && tail_range_begin(plan, first + 1) <= unit0) ++first;
+  while (first > 0 && tail_range_begin(plan, first) > unit0) --first;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int c = first; c < plan.num_pairs && tail_range_begin(plan, c) < unit1; ++c) {
+    const int start = tail_range_begin(plan, c) > unit0 ? tail_range_begin(plan, c) : unit0;
+    const float* src = partial + split_slot_offset(c, start == unit0 ? 1 : 0, r / BM) + (size_t)(r % BM) * BN + cgroup * 8;
+    const float4 lo = __ldcg(reinterpret_cast<const float4*>(src)), hi = __ldcg(reinterpret_cast<const float4*>(src + 4));
+    acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+    acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+  }
+  const uint4 packed = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                                  pack_bf16x2(acc[6], acc[7]));
+  *reinterpret_cast<uint4*>(out + row * out_cols + col) = packed;
+}
+
 }  // namespace pair
 
 // ---- host side -----------------------------------------------------------------------------------------
@@ -695,10 +679,9 @@ int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* ptr
                     uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
                     const char* what);
 
-// Scratch for splitting the last wave: one fp32 partial tile per CTA pair, then one counter per split tile.
-constexpr size_t kSplitFlagBytes = 1024;
+// Scratch for splitting the last wave: two fp32 partial tiles per CTA pair.
 size_t sm100_split_bytes() {
-  return (size_t)(sm_count() / 2) * 2 * pair::BN * pair::BM * sizeof(float) + kSplitFlagBytes;
+  return pair::split_slot_offset(sm_count() / 2, 0, 0) * sizeof(float);
 }
 
 int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
@@ -777,18 +760,19 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
   // Whole waves run the static schedule; a last partial wave is split along the contraction when scratch was given.
   p.full_tiles = (int)tiles;
   p.split_partial = nullptr;
-  p.split_flags = nullptr;
   {
-    const char* env = getenv("MOLT_B200_NO_SPLIT");   // timing experiments: keep the plain schedule
+    const char* env = getenv("MOLT_B200_NO_SPLIT");   // tests and timing experiments: 1 = keep the plain schedule
+    const char* force = getenv("MOLT_B200_FORCE_SPLIT");   // 1 = split whenever the shape allows it
     const long long rem = tiles % pairs;
     const long long blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
-    if (split_ws != nullptr && rem != 0 && tiles > pairs && pairs == sm_count() / 2 && rem * blocks >= pairs &&
+    // Splitting costs about 40 us (fp32 partial tiles out and in again, one more launch).  It pays when the last wave is
+    // at most half full and every pair still gets a run of blocks long enough to fill its pipeline (measured on the
+    // 14336 x 4096 weight: backward at 4096 tokens -8 %, forward with its 65-block tiles no gain).
+    const bool worth_it = (rem * 2 <= pairs && rem * blocks / pairs >= 32) || (force != nullptr && atoi(force) != 0);
+    if (split_ws != nullptr && rem != 0 && tiles > pairs && pairs == sm_count() / 2 && worth_it &&
         rem * blocks * pairs < (1LL << 30) && !(env != nullptr && atoi(env) != 0)) {
       p.full_tiles = (int)(tiles - rem);
       p.split_partial = reinterpret_cast<float*>(split_ws);
-      p.split_flags = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(split_ws) + sm100_split_bytes() - kSplitFlagBytes);
-      if (rem * (long long)sizeof(int) > (long long)kSplitFlagBytes) return fail(MOLT_E_RUNTIME, "tcgen05 GEMM: too many split tiles");
-      MOLT_CUDA(cudaMemsetAsync(p.split_flags, 0, (size_t)rem * sizeof(int), s));
     }
   }
   static thread_local bool configured[64][2][4] = {};
@@ -816,7 +800,21 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
 #undef MOLT_PAIR_DISPATCH
 #undef MOLT_PAIR_LAUNCH
   if (need_config) configured[dev][backward ? 1 : 0][variant] = true;
-  return launch_status("nf4_gemm_sm100_pair_kernel");
+  if (int rc = launch_status("nf4_gemm_sm100_pair_kernel")) return rc;
+  if (p.full_tiles < tiles) {
+    WorkPlan plan;
+    plan.num_pairs = (int)pairs;
+    plan.pair_id = 0;
+    plan.blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
+    plan.full_tiles = p.full_tiles;
+    plan.num_tiles = (int)tiles;
+    plan.tail_units = (int)(tiles - p.full_tiles) * plan.blocks;
+    plan.tail_begin = plan.tail_end = 0;
+    dim3 fgrid((unsigned)(2 * BM * (BN / 8) / 256), (unsigned)(tiles - p.full_tiles));
+    split_fixup_kernel<<<fgrid, 256, 0, s>>>(p.split_partial, plan, p.tiles_m, p.tiles_n, m, out_cols, out);
+    return launch_status("split_fixup_kernel");
+  }
+  return MOLT_OK;
 }
 
 }  // namespace molt

@@ -18,7 +18,8 @@ int general_colsum(bool out_by_rows, const __nv_bfloat16* low, int low_ld, const
 
 // skinny.cu -- aligned shapes
 int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, long long n, long long k,
-              __nv_bfloat16* a16, __nv_bfloat16* bs, __nv_bfloat16* bt, cudaStream_t s);
+              __nv_bfloat16* a16, __nv_bfloat16* bs, __nv_bfloat16* bt, const WeightView* w, float* resolved,
+              cudaStream_t s);
 int rowsum_mma(const __nv_bfloat16* in, const __nv_bfloat16* wt, int rp, long long m, long long cols,
                __nv_bfloat16* out, cudaStream_t s);
 size_t colsum_partial_bytes(long long m, long long cols, int rp);

@@ -21,13 +21,17 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 //   a16  [rp, k]  bf16(A), rows >= rank zero
 //   bs   [n, 64]  bf16(scaling * B), columns >= rank zero      (forward low-rank k-block, K-major)
 //   bt   [rp, n]  bf16(scaling * B)^T, rows >= rank zero       (U = dY . (sB))
-// Any of the three outputs may be NULL.
+// Any of the three outputs may be NULL.  The same launch also resolves a nested absmax to fp32 when `resolved` is given
+// (one launch instead of two in front of every GEMM).
 // ------------------------------------------------------------------------------------------------
 __global__ void lora_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, float scaling, int rank,
                                  int rp, long long n, long long k, __nv_bfloat16* __restrict__ a16,
-                                 __nv_bfloat16* __restrict__ bs, __nv_bfloat16* __restrict__ bt) {
+                                 __nv_bfloat16* __restrict__ bs, __nv_bfloat16* __restrict__ bt, WeightView w,
+                                 float* __restrict__ resolved, long long absmax_blocks) {
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  if (resolved != nullptr)
+    for (long long i = tid; i < absmax_blocks; i += stride) resolved[i] = load_absmax(w, i);
   if (a16 != nullptr)
     for (long long i = tid; i < (long long)rp * k; i += stride) {
       const int r = (int)(i / k);
@@ -243,8 +247,11 @@ __global__ void colsum_reduce_kernel(const float* __restrict__ partial, int spli
 
 // ---- host wrappers --------------------------------------------------------------------------------
 int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, long long n, long long k,
-              __nv_bfloat16* a16, __nv_bfloat16* bs, __nv_bfloat16* bt, cudaStream_t s) {
+              __nv_bfloat16* a16, __nv_bfloat16* bs, __nv_bfloat16* bt, const WeightView* w, float* resolved,
+              cudaStream_t s) {
   long long work = 0;
+  const long long absmax_blocks = (w != nullptr && resolved != nullptr) ? (w->n * w->k + w->blocksize - 1) / w->blocksize : 0;
+  if (absmax_blocks > work) work = absmax_blocks;
   if (a16) work = (long long)rp * k;
   if (bs && n * 64 > work) work = n * 64;
   if (bt && (long long)rp * n > work) work = (long long)rp * n;
@@ -252,7 +259,10 @@ int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, l
   long long blocks = (work + 255) / 256;
   const long long cap = (long long)sm_count() * 4;
   if (blocks > cap) blocks = cap;
-  lora_prep_kernel<<<(unsigned)blocks, 256, 0, s>>>(a, b, scaling, rank, rp, n, k, a16, bs, bt);
+  WeightView view{};
+  if (absmax_blocks > 0) view = *w;
+  lora_prep_kernel<<<(unsigned)blocks, 256, 0, s>>>(a, b, scaling, rank, rp, n, k, a16, bs, bt, view,
+                                                    absmax_blocks > 0 ? resolved : nullptr, absmax_blocks);
   return launch_status("lora_prep_kernel");
 }
 

@@ -121,17 +121,21 @@ def test_short_contractions(native_library, n, k, m):
 @pytest.mark.parametrize("n,k", [(2560, 1024), (1024, 2560)])
 def test_split_last_wave(native_library, monkeypatch, n, k):
     """80 output tiles on 74 CTA pairs (forward for the first shape, backward for the second): the six tiles of the
-    last wave are cut along the contraction and summed through global memory.  Results must match the oracle and,
-    up to the order of fp32 additions, the plain schedule."""
+    last wave are cut along the contraction, leave the GEMM as fp32 partial tiles and are summed by the fix-up kernel
+    (forced here: for tiles this short the library would keep the plain schedule).  Results must match the oracle
+    and, up to the order of fp32 additions, the plain schedule."""
+    monkeypatch.setenv("MOLT_B200_FORCE_SPLIT", "1")
     case = make_case(n, k, 2048, 16, seed=n + k, nested=True, order="high-first")
     _check_all(case, PATHS["tcgen05"])
     y_split, _ = run_forward(case, PATHS["tcgen05"])
     dx_split, da_split, db_split = run_backward(case, PATHS["tcgen05"])
+    monkeypatch.delenv("MOLT_B200_FORCE_SPLIT")
     monkeypatch.setenv("MOLT_B200_NO_SPLIT", "1")
     y_plain, _ = run_forward(case, PATHS["tcgen05"])
     dx_plain, da_plain, db_plain = run_backward(case, PATHS["tcgen05"])
     assert oracle.rel_frobenius(y_split, y_plain.float()) < 1e-3
     assert oracle.rel_frobenius(dx_split, dx_plain.float()) < 1e-3
+    assert not (torch.equal(y_split, y_plain) and torch.equal(dx_split, dx_plain))   # the split schedule really ran
     assert torch.equal(da_split, da_plain) and torch.equal(db_split, db_plain)
     assert_clean_status()
 
