@@ -53,16 +53,19 @@ __global__ void lora_prep_kernel(const float* __restrict__ a, const float* __res
 
 // ------------------------------------------------------------------------------------------------
 // rowsum: out[m, 0..63] = bf16(sum_c in[m, c] * wt[r, c]), zero for r >= RP.
-// One CTA = 16 rows; its 8 warps split the contraction in 32-column chunks and are summed in warp order.
+// One CTA = 16 rows; its warps split the contraction in 32-column chunks and are summed in warp order.
 // The k index inside each MMA is permuted (thread t owns 8 consecutive columns) so that both operands are
 // fetched with 16-byte loads; the permutation is applied to both operands, so the sum is unchanged.
 // ------------------------------------------------------------------------------------------------
+// warps per CTA of 16 rows: they split the contraction; 16 where the partial sums still fit in 48 KB of shared memory
+constexpr int rowsum_warps(int rp) { return rp <= 32 ? 16 : 8; }   // 32 warps measured slower than 16
 template <int RP>
-__global__ void __launch_bounds__(256) rowsum_mma_kernel(const __nv_bfloat16* __restrict__ in,
+__global__ void __launch_bounds__(rowsum_warps(RP) * 32) rowsum_mma_kernel(const __nv_bfloat16* __restrict__ in,
                                                          const __nv_bfloat16* __restrict__ wt, long long m_total,
                                                          long long cols, __nv_bfloat16* __restrict__ out) {
   constexpr int NT = RP / 8;
-  __shared__ float partial[8][16][RP + 1];
+  constexpr int kRowsumWarps = rowsum_warps(RP);
+  __shared__ float partial[kRowsumWarps][16][RP + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const long long row0 = blockIdx.x * 16LL;
@@ -75,25 +78,22 @@ __global__ void __launch_bounds__(256) rowsum_mma_kernel(const __nv_bfloat16* __
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
   const long long chunks = cols / 32;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  // Four chunks per trip: the eight activation loads (the HBM stream) are requested before anything is used, so a
-  // warp keeps 4 KB in flight; the weight-side loads hit L1/L2.
-  constexpr int kUnroll = 4;
-  const __nv_bfloat16* lo_ptr = in + (lo_ok ? r_lo : 0) * cols + t * 8;
-  const __nv_bfloat16* hi_ptr = in + (hi_ok ? r_hi : 0) * cols + t * 8;
-  for (long long c0 = warp; c0 < chunks; c0 += 8 * kUnroll) {
+  // Two chunks per trip: the four activation loads (the HBM stream) are requested before anything is used.  Default
+  // caching on purpose: a 128-byte line is shared by two neighbouring warps (64 bytes each).
+  constexpr int kUnroll = 2;
+  for (long long c0 = warp; c0 < chunks; c0 += kRowsumWarps * kUnroll) {
     uint4 lo[kUnroll], hi[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const long long c = c0 + 8 * u;
-      const bool in_range = c < chunks;
-      lo[u] = (lo_ok && in_range) ? __ldcs(reinterpret_cast<const uint4*>(lo_ptr + c * 32)) : zero;
-      hi[u] = (hi_ok && in_range) ? __ldcs(reinterpret_cast<const uint4*>(hi_ptr + c * 32)) : zero;
+      const long long col = (c0 + kRowsumWarps * u) * 32 + t * 8;
+      const bool in_range = c0 + kRowsumWarps * u < chunks;
+      lo[u] = (lo_ok && in_range) ? __ldg(reinterpret_cast<const uint4*>(in + r_lo * cols + col)) : zero;
+      hi[u] = (hi_ok && in_range) ? __ldg(reinterpret_cast<const uint4*>(in + r_hi * cols + col)) : zero;
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const long long c = c0 + 8 * u;
-      if (c < chunks) {
-        const long long col = c * 32 + t * 8;
+      if (c0 + kRowsumWarps * u < chunks) {
+        const long long col = (c0 + kRowsumWarps * u) * 32 + t * 8;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
           const uint4 b = __ldg(reinterpret_cast<const uint4*>(wt + (long long)(j * 8 + g) * cols + col));
@@ -111,13 +111,13 @@ __global__ void __launch_bounds__(256) rowsum_mma_kernel(const __nv_bfloat16* __
     partial[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < 16 * 64; idx += 256) {
+  for (int idx = threadIdx.x; idx < 16 * 64; idx += kRowsumWarps * 32) {
     const int row = idx >> 6, r = idx & 63;
     if (row0 + row >= m_total) continue;
     float sum = 0.f;
     if (r < RP) {
 #pragma unroll
-      for (int wv = 0; wv < 8; ++wv) sum += partial[wv][row][r];
+      for (int wv = 0; wv < kRowsumWarps; ++wv) sum += partial[wv][row][r];
     }
     out[(row0 + row) * 64 + r] = __float2bfloat16_rn(sum);
   }
@@ -271,10 +271,10 @@ int rowsum_mma(const __nv_bfloat16* in, const __nv_bfloat16* wt, int rp, long lo
   if (m == 0) return MOLT_OK;
   const unsigned grid = (unsigned)((m + 15) / 16);
   switch (rp) {
-    case 16: rowsum_mma_kernel<16><<<grid, 256, 0, s>>>(in, wt, m, cols, out); break;
-    case 32: rowsum_mma_kernel<32><<<grid, 256, 0, s>>>(in, wt, m, cols, out); break;
-    case 48: rowsum_mma_kernel<48><<<grid, 256, 0, s>>>(in, wt, m, cols, out); break;
-    case 64: rowsum_mma_kernel<64><<<grid, 256, 0, s>>>(in, wt, m, cols, out); break;
+    case 16: rowsum_mma_kernel<16><<<grid, rowsum_warps(16) * 32, 0, s>>>(in, wt, m, cols, out); break;
+    case 32: rowsum_mma_kernel<32><<<grid, rowsum_warps(32) * 32, 0, s>>>(in, wt, m, cols, out); break;
+    case 48: rowsum_mma_kernel<48><<<grid, rowsum_warps(48) * 32, 0, s>>>(in, wt, m, cols, out); break;
+    case 64: rowsum_mma_kernel<64><<<grid, rowsum_warps(64) * 32, 0, s>>>(in, wt, m, cols, out); break;
     default: return fail(MOLT_E_CAPABILITY, "rowsum_mma: padded rank %d unsupported", rp);
   }
   return launch_status("rowsum_mma_kernel");
