@@ -214,6 +214,8 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
   void* split = arena.take_optional(sm100_split_bytes());
   if (arena.dry) return MOLT_OK;
   MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
+  MOLT_REQUIRE((reinterpret_cast<uintptr_t>(lora_a) & 15) == 0, MOLT_E_CAPABILITY,
+               "molt_nf4_lora_fwd: lora_a must start on a 16-byte boundary for the tensor-core path");
   if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, bs, nullptr, &view, to_resolve, s)) return rc;
   if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t, s)) return rc;
   return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, split, s);
@@ -253,10 +255,11 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
   }
   auto* a16 = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
   auto* bt = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->n * 2));
-  float* partial = nullptr;
+  float* partial_a = nullptr;
+  float* partial_b = nullptr;
   if (want_grads) {
-    size_t pa = colsum_partial_bytes(m, w->k, rp), pb = colsum_partial_bytes(m, w->n, rp);
-    partial = reinterpret_cast<float*>(arena.take(pa > pb ? pa : pb));
+    partial_a = reinterpret_cast<float*>(arena.take(colsum_partial_bytes(m, w->k, rp)));
+    partial_b = reinterpret_cast<float*>(arena.take(colsum_partial_bytes(m, w->n, rp)));
   }
   const float* absmax = nullptr;
   float* to_resolve = nullptr;
@@ -266,6 +269,8 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
   void* split = dxb != nullptr ? arena.take_optional(sm100_split_bytes()) : nullptr;
   if (arena.dry) return MOLT_OK;
   MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace too small");
+  MOLT_REQUIRE((reinterpret_cast<uintptr_t>(lora_a) & 15) == 0, MOLT_E_CAPABILITY,
+               "molt_nf4_lora_bwd: lora_a must start on a 16-byte boundary for the tensor-core path");
   if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, nullptr, bt, &view, to_resolve, s)) return rc;
   if (int rc = rowsum_mma(gb, bt, rp, m, w->n, u, s)) return rc;  // U = dY . (sB)
   if (dxb != nullptr)
@@ -273,8 +278,8 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
   if (want_grads) {
     if (t_own != nullptr)
       if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t_own, s)) return rc;
-    if (int rc = colsum_mma(false, u, xb, rp, rank, m, w->k, 1.0f, partial, da, accumulate, s)) return rc;
-    if (int rc = colsum_mma(true, t, gb, rp, rank, m, w->n, scaling, partial, db, accumulate, s)) return rc;
+    if (int rc = colsum_pair(u, xb, w->k, partial_a, da, t, gb, w->n, scaling, partial_b, db, rp, rank, m, accumulate, s))
+      return rc;
   }
   return MOLT_OK;
 }

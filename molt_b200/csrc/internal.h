@@ -23,8 +23,9 @@ int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, l
 int rowsum_mma(const __nv_bfloat16* in, const __nv_bfloat16* wt, int rp, long long m, long long cols,
                __nv_bfloat16* out, cudaStream_t s);
 size_t colsum_partial_bytes(long long m, long long cols, int rp);
-int colsum_mma(bool transpose_out, const __nv_bfloat16* low, const __nv_bfloat16* in, int rp, int rank, long long m,
-               long long cols, float scale, float* partial, float* grad, int accumulate, cudaStream_t s);
+int colsum_pair(const __nv_bfloat16* u, const __nv_bfloat16* x, long long k, float* partial_a, float* grad_a,
+                const __nv_bfloat16* t, const __nv_bfloat16* dy, long long n, float scale_b, float* partial_b,
+                float* grad_b, int rp, int rank, long long m, int accumulate, cudaStream_t s);
 
 // gemv.cu
 size_t gemv_workspace_bytes(long long n, long long k);

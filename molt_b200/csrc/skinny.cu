@@ -28,27 +28,52 @@ __global__ void lora_prep_kernel(const float* __restrict__ a, const float* __res
                                  int rp, long long n, long long k, __nv_bfloat16* __restrict__ a16,
                                  __nv_bfloat16* __restrict__ bs, __nv_bfloat16* __restrict__ bt, WeightView w,
                                  float* __restrict__ resolved, long long absmax_blocks) {
-  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  if (resolved != nullptr)
-    for (long long i = tid; i < absmax_blocks; i += stride) resolved[i] = load_absmax(w, i);
-  if (a16 != nullptr)
-    for (long long i = tid; i < (long long)rp * k; i += stride) {
-      const int r = (int)(i / k);
-      a16[i] = __float2bfloat16_rn(r < rank ? a[i] : 0.f);
+  // One item per thread out of the four lists laid end to end, so that all of them are in flight together:
+  // a16 (8 elements), bs (one row of 64), bt (one column), resolved absmax (4 blocks).
+  const long long items_a = a16 != nullptr ? (long long)rp * k / 8 : 0;
+  const long long items_bs = bs != nullptr ? n : 0;
+  const long long items_bt = bt != nullptr ? n : 0;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i < items_a) {
+    const long long e = i * 8;
+    const int r = (int)(e / k);
+    uint32_t out[4] = {0u, 0u, 0u, 0u};
+    if (r < rank) {
+      const float4 lo = __ldg(reinterpret_cast<const float4*>(a + e)), hi = __ldg(reinterpret_cast<const float4*>(a + e + 4));
+      out[0] = pack_bf16x2(lo.x, lo.y); out[1] = pack_bf16x2(lo.z, lo.w);
+      out[2] = pack_bf16x2(hi.x, hi.y); out[3] = pack_bf16x2(hi.z, hi.w);
     }
-  if (bs != nullptr)
-    for (long long i = tid; i < n * 64; i += stride) {
-      const long long row = i >> 6;
-      const int r = (int)(i & 63);
-      bs[i] = __float2bfloat16_rn(r < rank ? scaling * b[row * rank + r] : 0.f);
+    *reinterpret_cast<uint4*>(a16 + e) = make_uint4(out[0], out[1], out[2], out[3]);
+    return;
+  }
+  i -= items_a;
+  if (i < items_bs) {   // one row of B -> one 64-wide row of bs (128 bytes)
+    uint32_t out[32];
+#pragma unroll
+    for (int q = 0; q < 32; ++q) {
+      const float v0 = 2 * q < rank ? scaling * __ldg(b + i * rank + 2 * q) : 0.f;
+      const float v1 = 2 * q + 1 < rank ? scaling * __ldg(b + i * rank + 2 * q + 1) : 0.f;
+      out[q] = pack_bf16x2(v0, v1);
     }
-  if (bt != nullptr)
-    for (long long i = tid; i < (long long)rp * n; i += stride) {
-      const int r = (int)(i / n);
-      const long long row = i % n;
-      bt[i] = __float2bfloat16_rn(r < rank ? scaling * b[row * rank + r] : 0.f);
+    uint4* dst = reinterpret_cast<uint4*>(bs + i * 64);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) dst[q] = make_uint4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
+    return;
+  }
+  i -= items_bs;
+  if (i < items_bt) {   // one row of B -> one column of bt: neighbouring threads write neighbouring elements of every row
+    for (int r = 0; r < rp; ++r)
+      bt[(long long)r * n + i] = __float2bfloat16_rn(r < rank ? scaling * __ldg(b + i * rank + r) : 0.f);
+    return;
+  }
+  i -= items_bt;
+  if (resolved != nullptr) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const long long blk = i * 4 + q;
+      if (blk < absmax_blocks) resolved[blk] = load_absmax(w, blk);
     }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -144,16 +169,32 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
 constexpr int kColsumRowBytes = 144;  // 128 data bytes + 16 pad: conflict-free ldmatrix rows
 constexpr int kColsumTileBytes = 64 * kColsumRowBytes;
 
+struct ColsumProblem {
+  const __nv_bfloat16* low;   // [m, 64]
+  const __nv_bfloat16* in;    // [m, cols]
+  long long cols;
+  int tiles_per_split, splits;
+  float* partial;             // [splits][RP][cols]
+  unsigned blocks;            // slabs * splits
+};
+
+// One launch serves up to two problems (dA and dB of one backward): the first `first.blocks` CTAs work on the first.
 template <int RP>
-__global__ void __launch_bounds__(128) colsum_mma_kernel(const __nv_bfloat16* __restrict__ low,
-                                                         const __nv_bfloat16* __restrict__ in, long long m_total,
-                                                         long long cols, int tiles_per_split,
-                                                         float* __restrict__ partial) {
+__global__ void __launch_bounds__(128) colsum_mma_kernel(ColsumProblem first, ColsumProblem second, long long m_total) {
   constexpr int MT = RP / 16;
   __shared__ __align__(16) unsigned char smem[2][2][kColsumTileBytes];  // [stage][0 = in, 1 = low]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long col0 = blockIdx.x * 64LL;
-  const int split = blockIdx.y;
+  const bool use_second = blockIdx.x >= first.blocks;
+  const ColsumProblem& pr = use_second ? second : first;
+  const unsigned local = use_second ? blockIdx.x - first.blocks : blockIdx.x;
+  const __nv_bfloat16* __restrict__ low = pr.low;
+  const __nv_bfloat16* __restrict__ in = pr.in;
+  const long long cols = pr.cols;
+  const int tiles_per_split = pr.tiles_per_split;
+  float* __restrict__ partial = pr.partial;
+  const unsigned slabs = (unsigned)(cols / 64);
+  const long long col0 = (local % slabs) * 64LL;
+  const int split = (int)(local / slabs);
   const long long tiles_total = (m_total + 63) / 64;
   const long long tile_begin = (long long)split * tiles_per_split;
   long long tile_end = tile_begin + tiles_per_split;
@@ -231,38 +272,42 @@ __global__ void __launch_bounds__(128) colsum_mma_kernel(const __nv_bfloat16* __
     }
 }
 
-// grad (+)= scale * sum_split partial[split][r][c];  TRANSPOSE writes grad[c, r] (dB), else grad[r, c] (dA).
-template <bool TRANSPOSE>
-__global__ void colsum_reduce_kernel(const float* __restrict__ partial, int splits, int rp, int rank, long long cols,
-                                     float scale, float* __restrict__ grad, int accumulate) {
-  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (idx >= cols * rank) return;
-  const int r = TRANSPOSE ? (int)(idx % rank) : (int)(idx / cols);
-  const long long c = TRANSPOSE ? idx / rank : idx % cols;
+// grad (+)= scale * sum_split partial[split][r][c];  transpose writes grad[c, r] (dB), else grad[r, c] (dA).
+struct ReduceProblem {
+  const float* partial;
+  int splits, transpose;
+  long long cols;
+  float scale;
+  float* grad;
+  long long total;   // cols * rank
+};
+__global__ void colsum_reduce_kernel(ReduceProblem first, ReduceProblem second, int rp, int rank, int accumulate) {
+  long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const bool use_second = idx >= first.total;
+  const ReduceProblem& pr = use_second ? second : first;
+  if (use_second) idx -= first.total;
+  if (idx >= pr.total) return;
+  const int r = pr.transpose ? (int)(idx % rank) : (int)(idx / pr.cols);
+  const long long c = pr.transpose ? idx / rank : idx % pr.cols;
   float sum = 0.f;
-  for (int s = 0; s < splits; ++s) sum += partial[((long long)s * rp + r) * cols + c];
-  sum *= scale;
-  grad[idx] = accumulate ? grad[idx] + sum : sum;
+  for (int s = 0; s < pr.splits; ++s) sum += pr.partial[((long long)s * rp + r) * pr.cols + c];
+  sum *= pr.scale;
+  pr.grad[idx] = accumulate ? pr.grad[idx] + sum : sum;
 }
 
 // ---- host wrappers --------------------------------------------------------------------------------
 int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, long long n, long long k,
               __nv_bfloat16* a16, __nv_bfloat16* bs, __nv_bfloat16* bt, const WeightView* w, float* resolved,
               cudaStream_t s) {
-  long long work = 0;
+  // k and n are multiples of 64 on this path, so the 8-element items never straddle a row
   const long long absmax_blocks = (w != nullptr && resolved != nullptr) ? (w->n * w->k + w->blocksize - 1) / w->blocksize : 0;
-  if (absmax_blocks > work) work = absmax_blocks;
-  if (a16) work = (long long)rp * k;
-  if (bs && n * 64 > work) work = n * 64;
-  if (bt && (long long)rp * n > work) work = (long long)rp * n;
-  if (work == 0) return MOLT_OK;
-  long long blocks = (work + 255) / 256;
-  const long long cap = (long long)sm_count() * 4;
-  if (blocks > cap) blocks = cap;
+  const long long items = (a16 ? (long long)rp * k / 8 : 0) + (bs ? n : 0) + (bt ? n : 0) +
+                          (absmax_blocks + 3) / 4;
+  if (items == 0) return MOLT_OK;
   WeightView view{};
   if (absmax_blocks > 0) view = *w;
-  lora_prep_kernel<<<(unsigned)blocks, 256, 0, s>>>(a, b, scaling, rank, rp, n, k, a16, bs, bt, view,
-                                                    absmax_blocks > 0 ? resolved : nullptr, absmax_blocks);
+  lora_prep_kernel<<<(unsigned)((items + 255) / 256), 256, 0, s>>>(a, b, scaling, rank, rp, n, k, a16, bs, bt, view,
+                                                                    absmax_blocks > 0 ? resolved : nullptr, absmax_blocks);
   return launch_status("lora_prep_kernel");
 }
 
@@ -296,27 +341,37 @@ size_t colsum_partial_bytes(long long m, long long cols, int rp) {
   return (size_t)colsum_splits(m, cols) * rp * cols * sizeof(float);
 }
 
-int colsum_mma(bool transpose_out, const __nv_bfloat16* low, const __nv_bfloat16* in, int rp, int rank, long long m,
-               long long cols, float scale, float* partial, float* grad, int accumulate, cudaStream_t s) {
-  if (cols == 0 || rank == 0) return MOLT_OK;
-  const int splits = colsum_splits(m, cols);
+// dA = U^T . X ([rp, k]) and dB = scale_b * (T^T . dY)^T ([n, rank]) of one backward: one launch for the split-M
+// partial sums of both and one for the two reductions.  partial_a / partial_b: colsum_partial_bytes each.
+int colsum_pair(const __nv_bfloat16* u, const __nv_bfloat16* x, long long k, float* partial_a, float* grad_a,
+                const __nv_bfloat16* t, const __nv_bfloat16* dy, long long n, float scale_b, float* partial_b,
+                float* grad_b, int rp, int rank, long long m, int accumulate, cudaStream_t s) {
+  if (rank == 0 || m == 0) return MOLT_OK;
   const long long tiles = (m + 63) / 64;
-  const int per = (int)((tiles + splits - 1) / splits);
-  dim3 grid((unsigned)(cols / 64), (unsigned)splits);
+  ColsumProblem pa{}, pb{};
+  ReduceProblem ra{}, rb{};
+  auto fill = [&](ColsumProblem& pr, ReduceProblem& rr, const __nv_bfloat16* low, const __nv_bfloat16* in, long long cols,
+                  float* partial, float* grad, float scale, int transpose) {
+    pr.low = low; pr.in = in; pr.cols = cols; pr.partial = partial;
+    pr.splits = colsum_splits(m, cols);
+    pr.tiles_per_split = (int)((tiles + pr.splits - 1) / pr.splits);
+    pr.blocks = (unsigned)(cols / 64) * (unsigned)pr.splits;
+    rr.partial = partial; rr.splits = pr.splits; rr.transpose = transpose; rr.cols = cols; rr.scale = scale;
+    rr.grad = grad; rr.total = cols * rank;
+  };
+  fill(pa, ra, u, x, k, partial_a, grad_a, 1.0f, 0);
+  fill(pb, rb, t, dy, n, partial_b, grad_b, scale_b, 1);
+  const unsigned grid = pa.blocks + pb.blocks;
   switch (rp) {
-    case 16: colsum_mma_kernel<16><<<grid, 128, 0, s>>>(low, in, m, cols, per, partial); break;
-    case 32: colsum_mma_kernel<32><<<grid, 128, 0, s>>>(low, in, m, cols, per, partial); break;
-    case 48: colsum_mma_kernel<48><<<grid, 128, 0, s>>>(low, in, m, cols, per, partial); break;
-    case 64: colsum_mma_kernel<64><<<grid, 128, 0, s>>>(low, in, m, cols, per, partial); break;
+    case 16: colsum_mma_kernel<16><<<grid, 128, 0, s>>>(pa, pb, m); break;
+    case 32: colsum_mma_kernel<32><<<grid, 128, 0, s>>>(pa, pb, m); break;
+    case 48: colsum_mma_kernel<48><<<grid, 128, 0, s>>>(pa, pb, m); break;
+    case 64: colsum_mma_kernel<64><<<grid, 128, 0, s>>>(pa, pb, m); break;
     default: return fail(MOLT_E_CAPABILITY, "colsum_mma: padded rank %d unsupported", rp);
   }
   if (int rc = launch_status("colsum_mma_kernel")) return rc;
-  const long long total = cols * rank;
-  const unsigned rgrid = (unsigned)((total + 255) / 256);
-  if (transpose_out)
-    colsum_reduce_kernel<true><<<rgrid, 256, 0, s>>>(partial, splits, rp, rank, cols, scale, grad, accumulate);
-  else
-    colsum_reduce_kernel<false><<<rgrid, 256, 0, s>>>(partial, splits, rp, rank, cols, scale, grad, accumulate);
+  const long long total = ra.total + rb.total;
+  colsum_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(ra, rb, rp, rank, accumulate);
   return launch_status("colsum_reduce_kernel");
 }
 
