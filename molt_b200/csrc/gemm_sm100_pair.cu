@@ -428,7 +428,6 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       src_off0 = (uint32_t)seg_j * 64u + ((((uint32_t)(2 * seg_a)) ^ x) << 4);
       src_off1 = (uint32_t)seg_j * 64u + ((((uint32_t)(2 * seg_a + 1)) ^ x) << 4);
     }
-    const int half_flip = (u >> 2) & 1;
     const uint32_t dst_off = !BACKWARD ? (uint32_t)u * 128u : (uint32_t)seg_a * 8192u + (uint32_t)seg_j * 128u;
     const uint32_t swz = (dst_off >> 7) & 7u;
     constexpr int kPrefetch = 4;   // absmax values are fetched this many of the group's blocks ahead of their use
@@ -485,11 +484,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           } else if (kb < p.num_kb) {
             const uint32_t pk = codes0 + (uint32_t)cs * kPackedBytes;
 #pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
-              // Forward: a thread's 32 bytes of codes are contiguous and the threads 32 bytes apart, so lanes i and i + 4
-              // of a quarter-warp would hit the same banks; every second group of four lanes takes its halves in the
-              // other order.
-              const int half = BACKWARD ? pass : (pass ^ half_flip);
+            for (int half = 0; half < 2; ++half) {
               uint32_t words[4];
               asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                            : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3])
