@@ -749,9 +749,9 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
 
   int variant = 0;
   {
-    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (5,4), 1 = (4,4), 2 = (4,5), 3 = (3,6)
+    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (5,4), 1 = (4,4), 2 = (4,5), 3 = (3,6), 4 = (6,3)
     variant = env != nullptr ? atoi(env) : 0;
-    if (variant < 0 || variant > 3) variant = 0;
+    if (variant < 0 || variant > 4) variant = 0;
   }
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long pairs = sm_count() / 2;
@@ -775,7 +775,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
       p.split_partial = reinterpret_cast<float*>(split_ws);
     }
   }
-  static thread_local bool configured[64][2][4] = {};
+  static thread_local bool configured[64][2][5] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));
   const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0][variant];
@@ -793,6 +793,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
     if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 4, 4, 2);       \
     else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 4, 5, 1);  \
     else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 3, 6, 1);  \
+    else if (variant == 4) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1);  \
     else MOLT_PAIR_LAUNCH(BWD, 5, 4, 1);                    \
   } while (0)
   if (backward) MOLT_PAIR_DISPATCH(true);
