@@ -33,6 +33,33 @@ def weight_desc(packed: torch.Tensor, quant_state: Any) -> _native.NF4Desc:
     return desc
 
 
+def weight_desc_for_tokens(packed: torch.Tensor, quant_state: Any, tokens: int) -> _native.NF4Desc:
+    """Descriptor to use for a call with this many tokens.  A double-quantised absmax is resolved to fp32 once and the
+    result cached on the state, as the reference does (methods/nf4_backward.py:145-164); the tensor-core kernels then
+    read it directly instead of resolving it in front of every GEMM.  Up to 16 tokens the streaming kernel reads the
+    8-bit form itself (fewer bytes), so those calls keep the state's own descriptor."""
+    if tokens <= 16 or not getattr(quant_state, "nested", False):
+        return weight_desc(packed, quant_state)
+    cached = getattr(quant_state, "_molt_desc_resolved", None)
+    key = (packed.data_ptr(), quant_state.absmax.data_ptr())
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    from molt_b200.methods.nf4_backward import resolved_nf4_scales
+    from molt_b200.methods.quant_state import QuantState, describe
+
+    fields = dict(absmax=resolved_nf4_scales(quant_state), shape=tuple(quant_state.shape),
+                  nibble_order=getattr(quant_state, "nibble_order", "high-first"))
+    if getattr(quant_state, "code", None) is not None:
+        fields["code"] = quant_state.code
+    plain = QuantState(**fields)
+    desc = describe(packed, plain)
+    try:
+        quant_state._molt_desc_resolved = (key, desc, plain)   # `plain` keeps the resolved scales alive
+    except AttributeError:
+        pass
+    return desc
+
+
 def check_linear_inputs(x: torch.Tensor, packed: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tensor,
                         who: str) -> None:
     """Guards of reference methods/nf4_lora.py:36-41, with the same error type and wording stem."""
@@ -121,11 +148,11 @@ class NF4LoRAFunction(torch.autograd.Function):
     def forward(ctx: Any, x: torch.Tensor, packed_weight: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tensor,
                 quant_state: Any, scaling: float, desc: Optional[_native.NF4Desc], who: str) -> torch.Tensor:
         check_linear_inputs(x, packed_weight, lora_a, lora_b, who)
-        if desc is None:
-            desc = weight_desc(packed_weight, quant_state)
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
+        if desc is None:
+            desc = weight_desc_for_tokens(packed_weight, quant_state, int(x2.shape[0]))
         needs_backward = any(ctx.needs_input_grad[i] for i in (0, 2, 3))
         y, t = linear_forward(desc, x2, lora_a, lora_b, float(scaling), keep_low_rank=needs_backward)
         ctx.desc = desc
