@@ -193,6 +193,22 @@ def test_gemv_path(native_library, m, n, k, nested):
     assert torch.equal(y, y_again)  # deterministic, tickets left clean
 
 
+def test_gemv_widest_rows_and_the_fallback_beyond(native_library):
+    """K = 16384 is the widest row the streaming kernel takes (8 K-groups); one block more and AUTO hands a 4-token
+    call to the tensor-core kernels instead.  Both must match the oracle."""
+    case = make_case(128, 16384, 4, 16, seed=77, nested=True, order="high-first")
+    y, _ = run_forward(case, _native.PATH_GEMV)
+    y_ref = oracle.nf4_lora_forward(case.x, case.weight, case.a, case.b, case.scaling)
+    assert oracle.rel_frobenius(y, y_ref) <= TOL
+    wide = make_case(128, 16448, 4, 16, seed=78)
+    y_wide, _ = run_forward(wide, _native.PATH_AUTO)
+    y_wide_ref = oracle.nf4_lora_forward(wide.x, wide.weight, wide.a, wide.b, wide.scaling)
+    assert oracle.rel_frobenius(y_wide, y_wide_ref) <= TOL
+    with pytest.raises(Exception):
+        run_forward(wide, _native.PATH_GEMV)
+    assert_clean_status()
+
+
 def test_gemv_is_the_auto_path_for_few_tokens(native_library):
     case = make_case(512, 256, 4, 8, seed=21)
     y_auto, _ = run_forward(case, _native.PATH_AUTO)
