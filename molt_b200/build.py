@@ -41,9 +41,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     BUILD_DIR.mkdir(parents=True, exist_ok=True)
     header_time = _newest_header()
     common = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS, "-Xcompiler", "-fPIC,-O3", "--expt-relaxed-constexpr"]
+    extra = os.environ.get("MOLT_B200_NVCC_FLAGS", "")  # e.g. -DMOLT_PAIR_TRACE for pipeline timelines
+    common += extra.split()
+    # objects built with other flags are stale: remember the command line they were built with
+    stamp = BUILD_DIR / "flags.txt"
+    signature = " ".join(common)
     if verbose:
         common += ["-Xptxas", "-v"]
-    common += os.environ.get("MOLT_B200_NVCC_FLAGS", "").split()  # e.g. -DMOLT_PAIR_TRACE for pipeline timelines
+    if not stamp.exists() or stamp.read_text() != signature:
+        force = True
     jobs = []
     objects = []
     for name in SOURCES:
@@ -65,6 +71,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                     sys.stderr.write(proc.stdout + proc.stderr)
                 if proc.returncode != 0:
                     raise RuntimeError("nvcc failed: " + " ".join(cmd))
+    stamp.write_text(signature)
     if jobs or not LIBRARY.exists():
         link = [nvcc, "-shared", *ARCH_FLAGS, "-o", str(LIBRARY), *map(str, objects), "-lcudart"]
         proc = subprocess.run(link, capture_output=True, text=True)
