@@ -421,8 +421,11 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     const int seg_j = u & 63, seg_a = u >> 6;        // backward: contraction row, 64-column atom
     uint32_t src_off0, src_off1;                     // the two 16-byte halves of the segment's packed codes
     if (!BACKWARD) {
-      src_off0 = (uint32_t)u * 32u;
-      src_off1 = src_off0 + 16u;
+      // 32-byte rows loaded with the 32-byte TMA swizzle: the halves of rows 4..7 (mod 8) are exchanged, so the eight
+      // lanes of a quarter-warp, all reading the same logical half, touch eight different 16-byte bank groups
+      const uint32_t flip = ((uint32_t)u >> 2) & 1u;
+      src_off0 = (uint32_t)u * 32u + flip * 16u;
+      src_off1 = (uint32_t)u * 32u + (flip ^ 1u) * 16u;
     } else {
       const uint32_t x = ((uint32_t)seg_j >> 1) & 3u;   // 64-byte swizzle of the packed tile
       src_off0 = (uint32_t)seg_j * 64u + ((((uint32_t)(2 * seg_a)) ^ x) << 4);
@@ -697,7 +700,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
     return rc;
   if (!backward) {
     if (int rc = make_tensor_map(&map_packed, CU_TENSOR_MAP_DATA_TYPE_UINT8, w.packed, w.k / 2, w.n, w.k / 2, BK / 2,
-                                 BNH, CU_TENSOR_MAP_SWIZZLE_NONE, "packed weight"))
+                                 BNH, CU_TENSOR_MAP_SWIZZLE_32B, "packed weight"))
       return rc;
   } else {
     if (int rc = make_tensor_map(&map_packed, CU_TENSOR_MAP_DATA_TYPE_UINT8, w.packed, w.k / 2, w.n, w.k / 2, BNH / 2,
