@@ -31,12 +31,14 @@ constexpr int BN = 256;            // output columns per pair tile
 constexpr int BNH = 128;           // B rows decoded per CTA
 constexpr int BK = 64;
 constexpr int kEpilogueWarps = 4;
-constexpr int kDecodeGroups = 3;   // groups of four warps that take the contraction blocks in turn
-constexpr int kDecodeWarps = 4 * kDecodeGroups;
+// Decode groups: groups of four warps that take the contraction blocks in turn.  Measured on the 14336 x 4096 weight at
+// 4096 tokens (same box): forward 453.5 us with 2 or 4 groups against 474.7 us with 3; backward 459 us with 3 against
+// 462-465 us with 2 or 4.  Two groups also leave 128 registers per thread.
+constexpr int decode_groups(bool backward) { return backward ? 3 : 2; }
 constexpr int kProducerWarp = 4;
 constexpr int kMmaWarp = 5;
 constexpr int kFirstDecodeWarp = 6;
-constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;
+constexpr int pair_threads(bool backward) { return (kFirstDecodeWarp + 4 * decode_groups(backward)) * 32; }
 
 constexpr uint32_t kTileABytes = BM * BK * 2;          // 16384
 constexpr uint32_t kPackedBytes = BNH * BK / 2;        // 4096
@@ -200,10 +202,12 @@ __host__ __device__ __forceinline__ size_t split_slot_offset(int pair, int start
 }
 
 template <bool BACKWARD, int kLoadStages, int kBStages, int kStoreBufs>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(BACKWARD), 1)
 nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_packed,
                            const __grid_constant__ CUtensorMap map_low, const __grid_constant__ CUtensorMap map_ext,
                            const __grid_constant__ CUtensorMap map_out, const __grid_constant__ Params p) {
+  constexpr int kDecodeGroups = decode_groups(BACKWARD);
+  constexpr int kThreads = pair_threads(BACKWARD);
   extern __shared__ unsigned char smem_dyn[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag_s;
@@ -752,9 +756,9 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
 
   int variant = 0;
   {
-    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (5,4), 1 = (4,4), 2 = (4,5), 3 = (3,6), 4 = (6,3)
+    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (6,3), the default; 1 = (4,4), 2 = (4,5), 3 = (3,6), 4 = (5,4), 5 = (7,2)
     variant = env != nullptr ? atoi(env) : 0;
-    if (variant < 0 || variant > 4) variant = 0;
+    if (variant < 0 || variant > 5) variant = 0;
   }
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long pairs = sm_count() / 2;
@@ -778,7 +782,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
       p.split_partial = reinterpret_cast<float*>(split_ws);
     }
   }
-  static thread_local bool configured[64][2][5] = {};
+  static thread_local bool configured[64][2][6] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));
   const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0][variant];
@@ -788,7 +792,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
       MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB>,                          \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,                          \
                                      (int)smem_bytes(LS, BS, SB)));                                        \
-    nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB><<<grid, kThreads, smem_bytes(LS, BS, SB), s>>>(            \
+    nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB><<<grid, pair_threads(BWD), smem_bytes(LS, BS, SB), s>>>(            \
         map_in, map_packed, map_low, map_ext, map_out, p);                                                 \
   } while (0)
 #define MOLT_PAIR_DISPATCH(BWD)                             \
@@ -796,8 +800,9 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
     if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 4, 4, 2);       \
     else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 4, 5, 1);  \
     else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 3, 6, 1);  \
-    else if (variant == 4) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1);  \
-    else MOLT_PAIR_LAUNCH(BWD, 5, 4, 1);                    \
+    else if (variant == 4) MOLT_PAIR_LAUNCH(BWD, 5, 4, 1);  \
+    else if (variant == 5) MOLT_PAIR_LAUNCH(BWD, 7, 2, 1);  \
+    else MOLT_PAIR_LAUNCH(BWD, 6, 3, 1);                    \
   } while (0)
   if (backward) MOLT_PAIR_DISPATCH(true);
   else MOLT_PAIR_DISPATCH(false);
