@@ -32,13 +32,13 @@ constexpr int BNH = 128;           // B rows decoded per CTA
 constexpr int BK = 64;
 constexpr int kEpilogueWarps = 4;
 // Decode groups: groups of four warps that take the contraction blocks in turn.  Measured on the 14336 x 4096 weight at
-// 4096 tokens (same box): forward 453.5 us with 2 or 4 groups against 474.7 us with 3; backward 459 us with 3 against
-// 462-465 us with 2 or 4.  Two groups also leave 128 registers per thread.
-constexpr int decode_groups(bool backward) { return backward ? 3 : 2; }
+// 4096 tokens with the (6, 3) rings, same box, forward / backward: 2 groups 451-457 / 439-444 us, 3 groups 478-482 /
+// 459-471 us, 4 groups 476 / 479-485 us.  Two groups also leave 128 registers per thread (no spills).
+constexpr int decode_groups(bool) { return 2; }
 constexpr int kProducerWarp = 4;
 constexpr int kMmaWarp = 5;
 constexpr int kFirstDecodeWarp = 6;
-constexpr int pair_threads(bool backward) { return (kFirstDecodeWarp + 4 * decode_groups(backward)) * 32; }
+constexpr int pair_threads(int groups) { return (kFirstDecodeWarp + 4 * groups) * 32; }
 
 constexpr uint32_t kTileABytes = BM * BK * 2;          // 16384
 constexpr uint32_t kPackedBytes = BNH * BK / 2;        // 4096
@@ -201,13 +201,12 @@ __host__ __device__ __forceinline__ size_t split_slot_offset(int pair, int start
   return ((size_t)(pair * 2 + starts_tile) * 2 + rank) * BM * BN;
 }
 
-template <bool BACKWARD, int kLoadStages, int kBStages, int kStoreBufs>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(BACKWARD), 1)
+template <bool BACKWARD, int kLoadStages, int kBStages, int kStoreBufs, int kDecodeGroups>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(kDecodeGroups), 1)
 nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_packed,
                            const __grid_constant__ CUtensorMap map_low, const __grid_constant__ CUtensorMap map_ext,
                            const __grid_constant__ CUtensorMap map_out, const __grid_constant__ Params p) {
-  constexpr int kDecodeGroups = decode_groups(BACKWARD);
-  constexpr int kThreads = pair_threads(BACKWARD);
+  constexpr int kThreads = pair_threads(kDecodeGroups);
   extern __shared__ unsigned char smem_dyn[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag_s;
@@ -756,9 +755,9 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
 
   int variant = 0;
   {
-    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (6,3), the default; 1 = (4,4), 2 = (4,5), 3 = (3,6), 4 = (5,4), 5 = (7,2)
+    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (6,3), the default; 1 = (4,4), 2 = (4,5), 3 = (3,6), 4 = (5,4); 5, 6, 7, 8 = (6,3) with 2, 3, 4, 1 decode groups
     variant = env != nullptr ? atoi(env) : 0;
-    if (variant < 0 || variant > 5) variant = 0;
+    if (variant < 0 || variant > 8) variant = 0;
   }
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long pairs = sm_count() / 2;
@@ -782,27 +781,30 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
       p.split_partial = reinterpret_cast<float*>(split_ws);
     }
   }
-  static thread_local bool configured[64][2][6] = {};
+  static thread_local bool configured[64][2][9] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));
   const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0][variant];
-#define MOLT_PAIR_LAUNCH(BWD, LS, BS, SB)                                                                  \
+#define MOLT_PAIR_LAUNCH(BWD, LS, BS, SB, GR)                                                              \
   do {                                                                                                     \
     if (need_config)                                                                                       \
-      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB>,                          \
+      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB, GR>,                      \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,                          \
                                      (int)smem_bytes(LS, BS, SB)));                                        \
-    nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB><<<grid, pair_threads(BWD), smem_bytes(LS, BS, SB), s>>>(            \
+    nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB, GR><<<grid, pair_threads(GR), smem_bytes(LS, BS, SB), s>>>( \
         map_in, map_packed, map_low, map_ext, map_out, p);                                                 \
   } while (0)
-#define MOLT_PAIR_DISPATCH(BWD)                             \
-  do {                                                      \
-    if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 4, 4, 2);       \
-    else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 4, 5, 1);  \
-    else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 3, 6, 1);  \
-    else if (variant == 4) MOLT_PAIR_LAUNCH(BWD, 5, 4, 1);  \
-    else if (variant == 5) MOLT_PAIR_LAUNCH(BWD, 7, 2, 1);  \
-    else MOLT_PAIR_LAUNCH(BWD, 6, 3, 1);                    \
+#define MOLT_PAIR_DISPATCH(BWD)                                                  \
+  do {                                                                           \
+    if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 4, 4, 2, decode_groups(BWD));        \
+    else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 4, 5, 1, decode_groups(BWD));   \
+    else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 3, 6, 1, decode_groups(BWD));   \
+    else if (variant == 4) MOLT_PAIR_LAUNCH(BWD, 5, 4, 1, decode_groups(BWD));   \
+    else if (variant == 5) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 2);                    \
+    else if (variant == 6) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 3);                    \
+    else if (variant == 7) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 4);                    \
+    else if (variant == 8) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 1);                    \
+    else MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, decode_groups(BWD));                     \
   } while (0)
   if (backward) MOLT_PAIR_DISPATCH(true);
   else MOLT_PAIR_DISPATCH(false);
