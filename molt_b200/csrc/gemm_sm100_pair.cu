@@ -755,9 +755,9 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
 
   int variant = 0;
   {
-    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (6,3), the default; 1 = (4,4), 2 = (4,5), 3 = (3,6), 4 = (5,4); 5, 6, 7, 8 = (6,3) with 2, 3, 4, 1 decode groups
+    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (6,3), the default; 1 = (4,4), 2 = (4,5), 3 = (3,6), 4 = (5,4); 5, 6, 7, 8 = (6,3) with 2, 3, 4, 1 decode groups; 9 = (5,3) with two store buffers
     variant = env != nullptr ? atoi(env) : 0;
-    if (variant < 0 || variant > 8) variant = 0;
+    if (variant < 0 || variant > 9) variant = 0;
   }
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long pairs = sm_count() / 2;
@@ -781,7 +781,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
       p.split_partial = reinterpret_cast<float*>(split_ws);
     }
   }
-  static thread_local bool configured[64][2][9] = {};
+  static thread_local bool configured[64][2][10] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));
   const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0][variant];
@@ -804,6 +804,7 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
     else if (variant == 6) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 3);                    \
     else if (variant == 7) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 4);                    \
     else if (variant == 8) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 1);                    \
+    else if (variant == 9) MOLT_PAIR_LAUNCH(BWD, 5, 3, 2, 2);                    \
     else MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, decode_groups(BWD));                     \
   } while (0)
   if (backward) MOLT_PAIR_DISPATCH(true);
