@@ -570,10 +570,12 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       if (item.tile >= plan.full_tiles) {
         // ---- part of a split tile: the fp32 accumulator goes to this pair's slot, row-major ----
         float* part = p.split_partial + split_slot_offset(pair_id, item.kb0 == 0 ? 1 : 0, (int)rank) + (size_t)row * BN;
+        const bool row_valid = (long long)row0 + row < p.m;   // the fix-up kernel never reads rows past the end
         for (int cg = 0; cg < BN / 32 && !(p.debug & 16); ++cg) {
           uint32_t v[32];
           tmem_ld32(t_row + (uint32_t)cg * 32u, v);
           tmem_ld_wait();
+          if (!row_valid) continue;
 #pragma unroll
           for (int c = 0; c < 8; ++c)
             __stcg(reinterpret_cast<float4*>(part + cg * 32 + c * 4),
@@ -760,27 +762,35 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
     if (variant < 0 || variant > 9) variant = 0;
   }
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
-  long long pairs = sm_count() / 2;
+  const long long all_pairs = sm_count() / 2;
+  long long pairs = all_pairs;
   if (tiles < pairs) pairs = tiles;
-  const int grid = (int)pairs * 2;
   // Whole waves run the static schedule; a last partial wave is split along the contraction when scratch was given.
   p.full_tiles = (int)tiles;
   p.split_partial = nullptr;
   {
     const char* env = getenv("MOLT_B200_NO_SPLIT");   // tests and timing experiments: 1 = keep the plain schedule
     const char* force = getenv("MOLT_B200_FORCE_SPLIT");   // 1 = split whenever the shape allows it
-    const long long rem = tiles % pairs;
+    const bool allowed = split_ws != nullptr && !(env != nullptr && atoi(env) != 0);
+    const bool forced = force != nullptr && atoi(force) != 0;
     const long long blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
-    // Splitting costs about 40 us (fp32 partial tiles out and in again, one more launch).  It pays when the last wave is
-    // at most half full and every pair still gets a run of blocks long enough to fill its pipeline (measured on the
-    // 14336 x 4096 weight: backward at 4096 tokens -8 %, forward with its 65-block tiles no gain).
-    const bool worth_it = (rem * 2 <= pairs && rem * blocks / pairs >= 32) || (force != nullptr && atoi(force) != 0);
-    if (split_ws != nullptr && rem != 0 && tiles > pairs && pairs == sm_count() / 2 && worth_it &&
-        rem * blocks * pairs < (1LL << 30) && !(env != nullptr && atoi(env) != 0)) {
-      p.full_tiles = (int)(tiles - rem);
-      p.split_partial = reinterpret_cast<float*>(split_ws);
+    if (tiles < all_pairs) {
+      // Fewer tiles than CTA pairs (few tokens): cutting all tiles along the contraction so that every pair of the device
+      // gets an equal run of blocks was measured and is slower (14336 x 4096 weight, 32..256 tokens: 55-69 us against
+      // 52-54 us) -- the fp32 partial tiles and the fix-up launch cost more than the shorter runs save.
+    } else {
+      const long long rem = tiles % pairs;
+      // Splitting costs about 40 us (fp32 partial tiles out and in again, one more launch).  It pays when the last wave
+      // is at most half full and every pair still gets a run of blocks long enough to fill its pipeline (measured on
+      // the 14336 x 4096 weight: backward at 4096 tokens -8 %, forward with its 65-block tiles no gain).
+      const bool worth_it = (rem * 2 <= pairs && rem * blocks / pairs >= 32) || forced;
+      if (allowed && rem != 0 && tiles > pairs && worth_it && rem * blocks >= pairs && rem * blocks * pairs < (1LL << 30)) {
+        p.full_tiles = (int)(tiles - rem);
+        p.split_partial = reinterpret_cast<float*>(split_ws);
+      }
     }
   }
+  const int grid = (int)pairs * 2;
   static thread_local bool configured[64][2][10] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));
