@@ -32,9 +32,10 @@ if str(ROOT) not in sys.path:
 
 N_OUT, K_IN, RANK, ALPHA, M_PER_GPU = 14336, 4096, 16, 32.0, 4096
 SCALING = ALPHA / RANK
-# dram__bytes_read.sum + dram__bytes_write.sum of one backward GEMM launch at M = 4096 (354.9 MB + 29.3 MB), taken from
-# an ncu --set full capture of `bench.py --profile gemm_bwd`; the summary of that capture sits under profiles/.
-GEMM_BWD_DRAM_BYTES_PER_LAUNCH = 384.2e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward GEMM launch at M = 4096 (353.0 MB + 39.9 MB, the fp32
+# partial tiles of the split last wave included), taken from an ncu --set full capture of `bench.py --profile gemm_bwd`;
+# the summary of that capture sits under profiles/.
+GEMM_BWD_DRAM_BYTES_PER_LAUNCH = 392.9e6
 METRIC = "nf4_lora_linear_fwd_bwd_tflops"
 WORKLOAD = ("NF4-LoRA linear fwd+bwd, W[14336,4096] NF4 bs64 double-quant absmax, r=16 alpha=32, "
             "M=4096 tokens per GPU, bf16")
