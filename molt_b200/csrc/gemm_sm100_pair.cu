@@ -9,7 +9,7 @@
 // whole 256-wide tile.  Compared with a single-CTA tile this halves the decode work and the shared-memory operand
 // traffic per FLOP.
 //
-// Per CTA: a TMA ring (activation tile + 4 KB of packed codes per stage) runs several blocks ahead of a
+// Per CTA: two TMA rings (16 KB activation tiles; 4 KB packed-code tiles, deeper) run several blocks ahead of a
 // separate ring of decoded B half-tiles, so the global-memory latency is not serialised with the decode.
 // Decode: one 8-byte shared-memory lookup per packed byte returns both fp32 codebook values (table replicated
 // per bank pair, conflict free), multiplied by the fp32 absmax and rounded once to bf16 -- the bits of the
@@ -224,7 +224,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   auto bar_ldfull = [&](int s) { return bar0 + 8u * s; };
   // consumed[g % 8] completes when the MMAs of contraction block number g (counted per CTA across tiles) have
   // finished reading their operands; ONE commit per block releases both the load stage and the B stage, in both
-  // CTAs.  Eight slots exceed either ring depth, so a waiter can never be lapped.
+  // CTAs.  Sixteen slots exceed every ring depth, so a waiter can never be lapped.
   constexpr int kConsumedSlots = 16;
   static_assert(kLoadStages < kCodeStages && kCodeStages < kConsumedSlots && kBStages < kConsumedSlots,
                 "ring deeper than the consumed slots");
