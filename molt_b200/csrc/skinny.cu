@@ -90,6 +90,8 @@ __global__ void __launch_bounds__(rowsum_warps(RP) * 32) rowsum_mma_kernel(const
                                                          long long cols, __nv_bfloat16* __restrict__ out) {
   constexpr int NT = RP / 8;
   constexpr int kRowsumWarps = rowsum_warps(RP);
+  // the GEMM that follows in the stream may begin its set-up (it waits for this grid before it touches global memory)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ float partial[kRowsumWarps][16][RP + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
