@@ -44,6 +44,9 @@ extern "C" {
 #define MOLT_PATH_GENERAL 1
 #define MOLT_PATH_TCGEN05 2
 #define MOLT_PATH_GEMV 3
+/* Optional flags, OR-ed onto a path: schedule of the tensor-core GEMMs when the last wave of output tiles is partial. */
+#define MOLT_PATH_NO_SPLIT 0x100    /* keep the plain tile schedule                                      */
+#define MOLT_PATH_FORCE_SPLIT 0x200 /* cut the tiles of the last wave along the contraction whenever the shape allows it */
 
 /* operations for molt_workspace_bytes */
 #define MOLT_OP_LORA_FWD 1
@@ -78,8 +81,19 @@ const char* molt_last_error(void);
 /* Number of kernels this library has launched in this process (all threads, all devices). */
 uint64_t molt_launch_count(void);
 
-/* Device-side status word.  The tcgen05 kernels bound every wait; when one expires the kernel
- * records a code here and returns.  Reads and clears it (synchronises the given stream). 0 = clean. */
+/* Process-wide options.
+ * MOLT_OPT_WAIT_LIMIT_US: limit of every bounded device-side wait in microseconds (default 1,000,000; 100 .. 60,000,000).
+ * MOLT_OPT_WITHHOLD_BLOCKS: failure injection for tests, made on the host: the NEXT tensor-core GEMM launch is told to
+ *   request this many contraction blocks fewer than its consumers expect, so that a bounded wait runs out, the kernel
+ *   records MOLT_E_TIMEOUT in the status word and returns (its output is then incomplete).  Cleared by that launch. */
+#define MOLT_OPT_WAIT_LIMIT_US 1
+#define MOLT_OPT_WITHHOLD_BLOCKS 2
+int molt_set_option(int option, int64_t value);
+
+/* Device-side status word.  The kernels bound every wait; when one expires the kernel records
+ * (MOLT_E_TIMEOUT << 24) | (wait site << 16) | block index here and returns with its output incomplete.
+ * Reads and clears it (synchronises the given stream). 0 = clean.  Callers of the C ABI must poll this word at a
+ * step boundary: it is the only report of an expired wait. */
 int molt_read_status(uintptr_t stream, int32_t* status_out);
 
 /* out[n, k] = codebook[code] * absmax, one fp32 multiply, cast last.
@@ -118,7 +132,9 @@ int molt_nf4_lora_bwd(const molt_nf4_desc* w, const void* x, const void* dy, con
 
 /* dx[m, k] = dy[m, n] . deq(W) (+ scaling * lora_grad[m, rank] . A[rank, k] when lora_grad != NULL).
  * Replaces packed_nf4_backward_input and packed_nf4_lora_backward_input
- * (reference methods/nf4_backward.py:167-284).  lora_a_dtype: MOLT_DTYPE_BF16 or MOLT_DTYPE_F32. */
+ * (reference methods/nf4_backward.py:167-284).  lora_a_dtype: MOLT_DTYPE_BF16 or MOLT_DTYPE_F32.
+ * On the tensor-core path both terms accumulate in fp32 and are rounded once; the general path rounds the base to
+ * bf16 before adding the low-rank term as the reference does (:127-136). */
 int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* lora_grad, const void* lora_a,
                 int lora_a_dtype, float scaling, int rank, void* dx, int64_t m, void* workspace,
                 size_t workspace_bytes, int path, uintptr_t stream);
@@ -127,7 +143,8 @@ int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* lora_grad, c
  * MOLT_STATIC_SCRATCH_BYTES array inside the library's device image, so this call allocates nothing and asks the
  * caller for nothing.  It is meant for hosts that cannot allocate device memory where they call the library (a
  * server that pins its whole device budget at start-up, a plugin without an allocator of its own).  It has no
- * counterpart in the reference.  Problems whose scratch need exceeds the array are refused (MOLT_E_VALUE).  All
+ * counterpart in the reference.  The result is that of molt_nf4_lora_fwd given a workspace without the optional
+ * split region.  Problems whose scratch need exceeds the array are refused (MOLT_E_VALUE).  All
  * calls on a device share the array: calls that may overlap on the GPU must be serialised by the caller.  The
  * first call on a device looks the array's address up; make it before any stream capture. */
 #define MOLT_STATIC_SCRATCH_BYTES (16u << 20)
@@ -155,6 +172,20 @@ int molt_swiglu_bwd(const void* grad_out, const void* gate, const void* up, void
  * Replaces _RMSNormReplayRecipe.materialize (reference methods/gated_replay.py:22-29). */
 int molt_rmsnorm_fwd(const void* x, const void* weight, int weight_dtype, float eps, float weight_offset,
                      void* out, int64_t rows, int64_t width, uintptr_t stream);
+
+/* grad_x = bf16(inv * (dy (w + offset) - x inv * mean(dy (w + offset) * x inv))), inv = rsqrt(mean(x^2) + eps); the weight is
+ * frozen, so there is no weight gradient.  Replaces _FrozenRMSNormFunction.backward
+ * (reference kernels/frozen_rmsnorm.py:25-37); molt_rmsnorm_fwd is also its forward (:11-23). */
+int molt_rmsnorm_bwd(const void* grad_out, const void* x, const void* weight, int weight_dtype, float eps,
+                     float weight_offset, void* grad_x, int64_t rows, int64_t width, uintptr_t stream);
+
+/* One AdamW step (decoupled weight decay, bias correction as in torch.optim.AdamW) over flat fp32 arrays of `count`
+ * elements (a multiple of 4): every adapter's parameters, gradients and moments laid end to end, so one launch steps
+ * them all.  grad is multiplied by grad_scale first (1 / world size after a summing all-reduce).  step counts from 1.
+ * Replaces the per-parameter optimizer loop the reference builds at training/qlora.py:218-243 and steps at :982-986. */
+int molt_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, int64_t count, float lr,
+                    float beta1, float beta2, float eps, float weight_decay, int64_t step, float grad_scale,
+                    uintptr_t stream);
 
 /* Frozen-head cross-entropy on bf16 logits [rows, vocab]: row_loss[row] = logsumexp(logits) - logits[target], and
  * logits is overwritten by (softmax - onehot) * grad_scale (bf16).  fp32 arithmetic, two passes over each row.

@@ -23,12 +23,14 @@ ABSMAX_F32, ABSMAX_NESTED = 0, 1
 NIBBLE_LOW_FIRST, NIBBLE_HIGH_FIRST = 0, 1
 DTYPE_BF16, DTYPE_F32 = 0, 1
 PATH_AUTO, PATH_GENERAL, PATH_TCGEN05, PATH_GEMV = 0, 1, 2, 3
+PATH_NO_SPLIT, PATH_FORCE_SPLIT = 0x100, 0x200   # flags OR-ed onto a path
+OPT_WAIT_LIMIT_US, OPT_WITHHOLD_BLOCKS = 1, 2
 OP_LORA_FWD, OP_LORA_BWD, OP_DX, OP_MLP_FWD, OP_MLP_BWD = 1, 2, 3, 4, 5
 
 EXPORTS = (
-    "molt_version", "molt_last_error", "molt_launch_count", "molt_read_status", "molt_nf4_dequant", "molt_nf4_resolve_absmax",
+    "molt_version", "molt_last_error", "molt_launch_count", "molt_set_option", "molt_read_status", "molt_nf4_dequant", "molt_nf4_resolve_absmax",
     "molt_workspace_bytes", "molt_nf4_lora_fwd", "molt_nf4_lora_fwd_static", "molt_nf4_lora_bwd", "molt_nf4_dx", "molt_nf4_gemv",
-    "molt_swiglu_fwd", "molt_swiglu_bwd", "molt_rmsnorm_fwd", "molt_ce_softmax_grad", "molt_mlp_workspace_bytes", "molt_mlp_fwd",
+    "molt_swiglu_fwd", "molt_swiglu_bwd", "molt_rmsnorm_fwd", "molt_rmsnorm_bwd", "molt_adamw_step", "molt_ce_softmax_grad", "molt_mlp_workspace_bytes", "molt_mlp_fwd",
     "molt_mlp_bwd",
 )
 
@@ -80,6 +82,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.molt_last_error.argtypes = []
     lib.molt_launch_count.restype = ctypes.c_uint64
     lib.molt_launch_count.argtypes = []
+    lib.molt_set_option.restype = i32
+    lib.molt_set_option.argtypes = [i32, i64]
     lib.molt_read_status.restype = i32
     lib.molt_read_status.argtypes = [up, ctypes.POINTER(ctypes.c_int32)]
     lib.molt_nf4_dequant.restype = i32
@@ -104,6 +108,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.molt_swiglu_bwd.argtypes = [vp, vp, vp, vp, vp, vp, i64, i32, up]
     lib.molt_rmsnorm_fwd.restype = i32
     lib.molt_rmsnorm_fwd.argtypes = [vp, vp, i32, f32, f32, vp, i64, i64, up]
+    lib.molt_rmsnorm_bwd.restype = i32
+    lib.molt_rmsnorm_bwd.argtypes = [vp, vp, vp, i32, f32, f32, vp, i64, i64, up]
+    lib.molt_adamw_step.restype = i32
+    lib.molt_adamw_step.argtypes = [vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, i64, f32, up]
     lib.molt_ce_softmax_grad.restype = i32
     lib.molt_ce_softmax_grad.argtypes = [vp, vp, vp, i64, i64, f32, up]
     lib.molt_mlp_workspace_bytes.restype = sz
@@ -156,6 +164,11 @@ def read_status(device: Optional[torch.device] = None) -> int:
     out = ctypes.c_int32(0)
     check(library().molt_read_status(stream_handle(device), ctypes.byref(out)))
     return int(out.value)
+
+
+def set_option(option: int, value: int) -> None:
+    """Process-wide library option (``OPT_*``)."""
+    check(library().molt_set_option(int(option), int(value)))
 
 
 def workspace(nbytes: int, device: torch.device) -> torch.Tensor:

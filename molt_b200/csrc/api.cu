@@ -21,6 +21,27 @@ int fail(int code, const char* fmt, ...) {
 static unsigned long long g_launches = 0;
 void count_launch() { __atomic_fetch_add(&g_launches, 1ULL, __ATOMIC_RELAXED); }
 
+// ---- process-wide options --------------------------------------------------------------------------
+static long long g_wait_limit_us = 1000000;   // one second
+static int g_withheld_blocks = 0;
+
+// SM clock cycles corresponding to the wait limit (at the device's maximum SM clock, so the limit is never shorter
+// than asked for).
+long long wait_limit_cycles() {
+  static int khz[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (khz[dev] == 0) {
+    int value = 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrClockRate, dev) != cudaSuccess || value <= 0) value = 2000000;
+    khz[dev] = value;
+  }
+  const long long us = __atomic_load_n(&g_wait_limit_us, __ATOMIC_RELAXED);
+  return us * (long long)(khz[dev] / 1000);
+}
+
+int take_withheld_blocks() { return __atomic_exchange_n(&g_withheld_blocks, 0, __ATOMIC_RELAXED); }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -97,7 +118,15 @@ struct Arena {
 
 static int padded_rank(int rank) { return (rank + 15) / 16 * 16; }
 
-__global__ void add_bf16_kernel(const uint4* a, const uint4* b, uint4* out, long long vectors) {
+__global__ void add_bf16_kernel(const uint4* a, const uint4* b, uint4* out, long long vectors, long long count) {
+  if (blockIdx.x == 0 && threadIdx.x < 8) {   // the tail past the last whole 16-byte vector
+    const long long i = vectors * 8 + threadIdx.x;
+    if (i < count) {
+      const __nv_bfloat16* as = reinterpret_cast<const __nv_bfloat16*>(a);
+      const __nv_bfloat16* bs = reinterpret_cast<const __nv_bfloat16*>(b);
+      reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(__bfloat162float(as[i]) + __bfloat162float(bs[i]));
+    }
+  }
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < vectors;
        v += (long long)gridDim.x * blockDim.x) {
     const uint4 x = a[v], y = b[v];
@@ -111,13 +140,13 @@ __global__ void add_bf16_kernel(const uint4* a, const uint4* b, uint4* out, long
 }
 
 int add_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, long long count, cudaStream_t s) {
-  if (count % 8 != 0) return fail(MOLT_E_VALUE, "add_bf16: count must be a multiple of 8");
+  if (count == 0) return MOLT_OK;
   const long long vectors = count / 8;
-  if (vectors == 0) return MOLT_OK;
   long long blocks = (vectors + 255) / 256;
   const long long cap = (long long)sm_count() * 16;
   if (blocks > cap) blocks = cap;
-  add_bf16_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint4*)a, (const uint4*)b, (uint4*)out, vectors);
+  if (blocks < 1) blocks = 1;
+  add_bf16_kernel<<<(unsigned)blocks, 256, 0, s>>>((const uint4*)a, (const uint4*)b, (uint4*)out, vectors, count);
   return launch_status("add_bf16_kernel");
 }
 
@@ -126,11 +155,18 @@ static bool aligned_case(const molt_nf4_desc* w, int rank) {
          (reinterpret_cast<uintptr_t>(w->packed) & 15) == 0;
 }
 
-static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m, bool forward, int* chosen) {
+// `requested` may carry MOLT_PATH_NO_SPLIT / MOLT_PATH_FORCE_SPLIT above the kernel path; *gemm_flags receives them.
+static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m, bool forward, int* chosen,
+                     int* gemm_flags = nullptr) {
   const bool aligned = aligned_case(w, rank);
+  MOLT_REQUIRE((requested & ~(0xff | MOLT_PATH_NO_SPLIT | MOLT_PATH_FORCE_SPLIT)) == 0, MOLT_E_VALUE,
+               "unknown kernel path flags 0x%x", requested);
+  if (gemm_flags != nullptr)
+    *gemm_flags = ((requested & MOLT_PATH_NO_SPLIT) ? kGemmNoSplit : 0) | ((requested & MOLT_PATH_FORCE_SPLIT) ? kGemmForceSplit : 0);
+  requested &= 0xff;
   if (requested == MOLT_PATH_AUTO) {
     if (!aligned) *chosen = MOLT_PATH_GENERAL;
-    else if (forward && m <= 16 && w->k <= 16384) *chosen = MOLT_PATH_GEMV;
+    else if (forward && m <= 16) *chosen = MOLT_PATH_GEMV;
     else *chosen = MOLT_PATH_TCGEN05;
     return MOLT_OK;
   }
@@ -173,7 +209,7 @@ static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s,
 // ---- forward ---------------------------------------------------------------------------------------
 static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
                          float scaling, int rank, void* y, int64_t m, void* t_out, Arena& arena, int path,
-                         cudaStream_t s) {
+                         cudaStream_t s, int flags = 0) {
   const WeightView view = make_view(w);
   const int rp = padded_rank(rank);
   auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -182,10 +218,6 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
     void* ws = arena.take(gemv_workspace_bytes(w->n, w->k));
     if (arena.dry) return MOLT_OK;
     MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
-    if (t_out != nullptr) {  // keep the contract of t_out also on this path
-      if (int rc = general_rowsum(true, xb, lora_a, 1.0f, m, w->k, rank, reinterpret_cast<__nv_bfloat16*>(t_out), 64, s))
-        return rc;
-    }
     WeightView gview = view;
     if (w->absmax_kind == MOLT_ABSMAX_NESTED && !gemv_reads_nested(view)) {
       // a nested layout the kernel cannot stage with 4-byte copies: resolve it to fp32 once per call
@@ -194,7 +226,8 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
       gview.absmax = resolved;
       gview.absmax_kind = MOLT_ABSMAX_F32;
     }
-    return gemv_forward(gview, xb, lora_a, lora_b, scaling, rank, yb, (int)m, ws, gemv_workspace_bytes(w->n, w->k), s);
+    return gemv_forward(gview, xb, lora_a, lora_b, scaling, rank, yb, (int)m, reinterpret_cast<__nv_bfloat16*>(t_out), ws,
+                        gemv_workspace_bytes(w->n, w->k), s);
   }
   __nv_bfloat16* t = t_out != nullptr ? reinterpret_cast<__nv_bfloat16*>(t_out)
                                       : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));
@@ -218,13 +251,13 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
                "molt_nf4_lora_fwd: lora_a must start on a 16-byte boundary for the tensor-core path");
   if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, bs, nullptr, &view, to_resolve, s)) return rc;
   if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t, s)) return rc;
-  return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, split, s);
+  return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, split, flags, s);
 }
 
 // ---- backward --------------------------------------------------------------------------------------
 static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, const float* lora_a,
                          const float* lora_b, float scaling, int rank, void* dx, float* da, float* db, int64_t m,
-                         const void* t_in, int accumulate, Arena& arena, int path, cudaStream_t s) {
+                         const void* t_in, int accumulate, Arena& arena, int path, cudaStream_t s, int flags = 0) {
   const WeightView view = make_view(w);
   const int rp = padded_rank(rank);
   auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -274,7 +307,7 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
   if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, nullptr, bt, &view, to_resolve, s)) return rc;
   if (int rc = rowsum_mma(gb, bt, rp, m, w->n, u, s)) return rc;  // U = dY . (sB)
   if (dxb != nullptr)
-    if (int rc = sm100_gemm(true, view, absmax, gb, u, a16, rp, dxb, m, split, s)) return rc;
+    if (int rc = sm100_gemm(true, view, absmax, gb, u, a16, rp, dxb, m, split, flags, s)) return rc;
   if (want_grads) {
     if (t_own != nullptr)
       if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t_own, s)) return rc;
@@ -286,22 +319,33 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
 
 static int dx_impl(const molt_nf4_desc* w, const void* dy, const void* lora_grad, const void* lora_a,
                    int lora_a_dtype, float scaling, int rank, void* dx, int64_t m, Arena& arena, int path,
-                   cudaStream_t s) {
+                   cudaStream_t s, int flags = 0) {
   const WeightView view = make_view(w);
   auto* gb = reinterpret_cast<const __nv_bfloat16*>(dy);
   auto* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
-  // The caller's lora_grad is [m, rank] (unpadded); both kernel families read it with its own leading dimension
-  // on the general path.  The tcgen05 path needs the padded [m, 64] layout and a bf16 A scaled by `scaling`,
-  // which only exists for the fused linear backward; the standalone op therefore always runs the general kernels
-  // when a low-rank term is present and the tcgen05 kernel otherwise.
-  if (path == MOLT_PATH_TCGEN05 && lora_grad == nullptr) {
+  if (path == MOLT_PATH_TCGEN05) {
+    // The low-rank term rides as one more contraction block: low = lora_grad zero-padded to [m, 64] and
+    // ext = bf16(scaling * A) [rp, k].  Base and low-rank term are summed in fp32 and rounded once (the reference
+    // rounds the base to bf16 first, methods/nf4_backward.py:127-136; the fused form is the more accurate one).
+    const bool has_low = lora_grad != nullptr;
+    const int rp = has_low ? padded_rank(rank) : 0;
+    __nv_bfloat16* low = nullptr;
+    __nv_bfloat16* a16 = nullptr;
+    if (has_low) {
+      low = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));
+      a16 = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
+    }
     const float* absmax = nullptr;
     if (int rc = resolved_absmax(w, arena, s, &absmax)) return rc;
     const bool fits = arena.fits();
     void* split = arena.take_optional(sm100_split_bytes());
     if (arena.dry) return MOLT_OK;
     MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_dx: workspace too small");
-    return sm100_gemm(true, view, absmax, gb, nullptr, nullptr, 0, dxb, m, split, s);
+    if (has_low)
+      if (int rc = dx_lora_prep(reinterpret_cast<const __nv_bfloat16*>(lora_grad), rank, m, lora_a, lora_a_dtype, scaling,
+                                rp, w->k, low, a16, s))
+        return rc;
+    return sm100_gemm(true, view, absmax, gb, low, a16, rp, dxb, m, split, flags, s);
   }
   if (arena.dry) return MOLT_OK;
   return general_backward_input(view, gb, reinterpret_cast<const __nv_bfloat16*>(lora_grad), rank, lora_a,
@@ -315,6 +359,21 @@ using namespace molt;
 extern "C" int molt_version(void) { return 100; }
 extern "C" const char* molt_last_error(void) { return error_buffer(); }
 extern "C" uint64_t molt_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
+
+extern "C" int molt_set_option(int option, int64_t value) {
+  switch (option) {
+    case MOLT_OPT_WAIT_LIMIT_US:
+      MOLT_REQUIRE(value >= 100 && value <= 60000000, MOLT_E_VALUE, "wait limit must lie in [100 us, 60 s]");
+      __atomic_store_n(&g_wait_limit_us, (long long)value, __ATOMIC_RELAXED);
+      return MOLT_OK;
+    case MOLT_OPT_WITHHOLD_BLOCKS:
+      MOLT_REQUIRE(value >= 0 && value <= 4, MOLT_E_VALUE, "withheld block count must lie in [0, 4]");
+      __atomic_store_n(&g_withheld_blocks, (int)value, __ATOMIC_RELAXED);
+      return MOLT_OK;
+    default:
+      return fail(MOLT_E_VALUE, "unknown option %d", option);
+  }
+}
 
 extern "C" int molt_read_status(uintptr_t stream, int32_t* status_out) {
   MOLT_REQUIRE(status_out != nullptr, MOLT_E_VALUE, "molt_read_status: status_out is NULL");
@@ -360,7 +419,8 @@ size_t molt::workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank, 
       lora_bwd_impl(&fake, nullptr, nullptr, nullptr, nullptr, 1.f, rank, reinterpret_cast<void*>(uintptr_t(256)),
                     reinterpret_cast<float*>(uintptr_t(256)), reinterpret_cast<float*>(uintptr_t(256)), m, nullptr, 0,
                     arena, path, 0);
-    else if (op == MOLT_OP_DX) dx_impl(&fake, nullptr, nullptr, nullptr, 0, 1.f, rank, nullptr, m, arena, path, 0);
+    else if (op == MOLT_OP_DX)   // sized for a call with a low-rank term of this rank
+      dx_impl(&fake, nullptr, reinterpret_cast<const void*>(uintptr_t(256)), nullptr, 0, 1.f, rank, nullptr, m, arena, path, 0);
     else return 0;
     if (arena.used > best) best = arena.used;
   }
@@ -380,12 +440,12 @@ extern "C" int molt_nf4_lora_fwd(const molt_nf4_desc* w, const void* x, const fl
   MOLT_REQUIRE(aligned16(x) && aligned16(y) && aligned16(w->packed) && (t_out == nullptr || aligned16(t_out)),
                MOLT_E_VALUE, "molt_nf4_lora_fwd: tensors must be 16-byte aligned");
   if (m == 0) return MOLT_OK;
-  int chosen = 0;
-  if (int rc = pick_path(path, w, rank, m, true, &chosen)) return rc;
+  int chosen = 0, flags = 0;
+  if (int rc = pick_path(path, w, rank, m, true, &chosen, &flags)) return rc;
   MOLT_REQUIRE(workspace != nullptr, MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace is NULL");
   Arena arena(workspace, workspace_bytes);
   return lora_fwd_impl(w, x, lora_a, lora_b, scaling, rank, y, m, t_out, arena, chosen,
-                       reinterpret_cast<cudaStream_t>(stream));
+                       reinterpret_cast<cudaStream_t>(stream), flags);
 }
 
 extern "C" int molt_nf4_gemv(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
@@ -416,12 +476,12 @@ extern "C" int molt_nf4_lora_bwd(const molt_nf4_desc* w, const void* x, const vo
     }
     return MOLT_OK;
   }
-  int chosen = 0;
-  if (int rc = pick_path(path, w, rank, m, false, &chosen)) return rc;
+  int chosen = 0, flags = 0;
+  if (int rc = pick_path(path, w, rank, m, false, &chosen, &flags)) return rc;
   MOLT_REQUIRE(workspace != nullptr, MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace is NULL");
   Arena arena(workspace, workspace_bytes);
   return lora_bwd_impl(w, x, dy, lora_a, lora_b, scaling, rank, dx, da, db, m, t_in, accumulate, arena, chosen,
-                       reinterpret_cast<cudaStream_t>(stream));
+                       reinterpret_cast<cudaStream_t>(stream), flags);
 }
 
 extern "C" int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* lora_grad, const void* lora_a,
@@ -440,17 +500,20 @@ extern "C" int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* l
                  "molt_nf4_dx: LoRA A must be bf16 or fp32");
   }
   if (m == 0) return MOLT_OK;
-  int chosen = 0;
+  int chosen = 0, flags = 0;
   const int rank_for_path = lora_grad != nullptr ? rank : 1;
-  if (path == MOLT_PATH_AUTO) {
-    chosen = (aligned_case(w, rank_for_path <= 64 ? rank_for_path : 1) && lora_grad == nullptr) ? MOLT_PATH_TCGEN05
-                                                                                               : MOLT_PATH_GENERAL;
-  } else {
-    if (int rc = pick_path(path, w, rank_for_path, m, false, &chosen)) return rc;
+  if (lora_grad != nullptr)
+    MOLT_REQUIRE(rank <= 64, MOLT_E_CAPABILITY, "molt_nf4_dx: LoRA rank %d exceeds the supported maximum of 64", rank);
+  if (int rc = pick_path(path, w, rank_for_path, m, false, &chosen, &flags)) return rc;
+  if (chosen == MOLT_PATH_TCGEN05 && lora_grad != nullptr && !aligned16(lora_a)) {
+    MOLT_REQUIRE((path & 0xff) == MOLT_PATH_AUTO, MOLT_E_CAPABILITY,
+                 "molt_nf4_dx: lora_a must start on a 16-byte boundary for the tensor-core path");
+    chosen = MOLT_PATH_GENERAL;
   }
+  MOLT_REQUIRE(chosen == MOLT_PATH_GENERAL || workspace != nullptr, MOLT_E_VALUE, "molt_nf4_dx: workspace is NULL");
   Arena arena(workspace, workspace_bytes);
   return dx_impl(w, dy, lora_grad, lora_a, lora_a_dtype, scaling, rank, dx, m, arena, chosen,
-                 reinterpret_cast<cudaStream_t>(stream));
+                 reinterpret_cast<cudaStream_t>(stream), flags);
 }
 
 // ---- gated MLP block -------------------------------------------------------------------------------

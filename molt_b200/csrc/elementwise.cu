@@ -1,5 +1,7 @@
 // HBM-bound kernels: NF4 dequantisation, absmax resolution, SwiGLU forward/backward, RMSNorm replay.
 // Each thread moves 16-byte vectors; grids are sized in multiples of the SM count.
+#include <math.h>
+
 #include "common.cuh"
 
 namespace molt {
@@ -180,29 +182,137 @@ __global__ void swiglu_scalar_kernel(const T* __restrict__ gate, const T* __rest
 }
 
 // ------------------------------------------------------------------------------------------------
-// RMSNorm (norm-replay recipe): one warp per row, fp32 reduction, bf16 out.
+// Frozen RMSNorm, forward and backward: one warp per row, 16-byte loads, fp32 reduction, bf16 in and out.
+//   forward : out = bf16(x * rsqrt(mean(x^2) + eps) * (w + offset))
+//   backward: dx  = bf16(inv * (dy (w + offset) - x inv * mean(dy (w + offset) * x inv)))   (weight frozen: no dw)
+// The row is read twice; the second pass finds it in L1.  Rows whose width is not a multiple of 8 (or unaligned
+// tensors) take the scalar loops.
 // ------------------------------------------------------------------------------------------------
 template <typename WT>
+__device__ __forceinline__ void load_weight8(const WT* w, long long c, float offset, float (&out)[8]);
+template <>
+__device__ __forceinline__ void load_weight8<float>(const float* w, long long c, float offset, float (&out)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(w + c)), b = __ldg(reinterpret_cast<const float4*>(w + c + 4));
+  out[0] = a.x + offset; out[1] = a.y + offset; out[2] = a.z + offset; out[3] = a.w + offset;
+  out[4] = b.x + offset; out[5] = b.y + offset; out[6] = b.z + offset; out[7] = b.w + offset;
+}
+template <>
+__device__ __forceinline__ void load_weight8<__nv_bfloat16>(const __nv_bfloat16* w, long long c, float offset,
+                                                            float (&out)[8]) {
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(w + c));
+  const uint32_t v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = bf16_lo(v[i]) + offset;
+    out[2 * i + 1] = bf16_hi(v[i]) + offset;
+  }
+}
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&out)[8]) {
+  const uint32_t v[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = bf16_lo(v[i]);
+    out[2 * i + 1] = bf16_hi(v[i]);
+  }
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename WT, bool VEC, bool BACKWARD>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const WT* __restrict__ weight,
-                                                      float eps, float weight_offset, __nv_bfloat16* __restrict__ out,
+                                                      const __nv_bfloat16* __restrict__ grad, float eps,
+                                                      float weight_offset, __nv_bfloat16* __restrict__ out,
                                                       long long rows, long long width) {
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long row = warp; row < rows; row += warps) {
     const __nv_bfloat16* src = x + row * width;
-    float sum = 0.f;
-    for (long long c = lane; c < width; c += 32) {
-      const float v = __bfloat162float(src[c]);
-      sum += v * v;
-    }
+    const __nv_bfloat16* gsrc = BACKWARD ? grad + row * width : nullptr;
+    __nv_bfloat16* dst = out + row * width;
+    float sum = 0.f, dot = 0.f;   // sum of x^2; backward: sum of dy (w + offset) x
+    if (VEC) {
+      for (long long c = lane * 8LL; c < width; c += 256) {
+        float xv[8];
+        unpack8(*reinterpret_cast<const uint4*>(src + c), xv);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float inv = rsqrtf(sum / (float)width + eps);
-    for (long long c = lane; c < width; c += 32) {
-      const float v = __bfloat162float(src[c]);
-      out[row * width + c] = __float2bfloat16_rn(v * inv * (to_f32<WT>(weight[c]) + weight_offset));
+        for (int i = 0; i < 8; ++i) sum += xv[i] * xv[i];
+        if (BACKWARD) {
+          float gv[8], wv[8];
+          unpack8(__ldcs(reinterpret_cast<const uint4*>(gsrc + c)), gv);
+          load_weight8<WT>(weight, c, weight_offset, wv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dot += gv[i] * wv[i] * xv[i];
+        }
+      }
+    } else {
+      for (long long c = lane; c < width; c += 32) {
+        const float v = __bfloat162float(src[c]);
+        sum += v * v;
+        if (BACKWARD) dot += __bfloat162float(gsrc[c]) * (to_f32<WT>(weight[c]) + weight_offset) * v;
+      }
     }
+    sum = warp_sum(sum);
+    const float inv = rsqrtf(sum / (float)width + eps);
+    float correction = 0.f;
+    if (BACKWARD) correction = warp_sum(dot) * inv / (float)width;   // mean(weighted * normalized)
+    if (VEC) {
+      for (long long c = lane * 8LL; c < width; c += 256) {
+        float xv[8], wv[8], res[8];
+        unpack8(*reinterpret_cast<const uint4*>(src + c), xv);
+        load_weight8<WT>(weight, c, weight_offset, wv);
+        if (!BACKWARD) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) res[i] = xv[i] * inv * wv[i];
+        } else {
+          float gv[8];
+          unpack8(*reinterpret_cast<const uint4*>(gsrc + c), gv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) res[i] = inv * (gv[i] * wv[i] - xv[i] * inv * correction);
+        }
+        __stcs(reinterpret_cast<uint4*>(dst + c), make_uint4(pack_bf16x2(res[0], res[1]), pack_bf16x2(res[2], res[3]),
+                                                              pack_bf16x2(res[4], res[5]), pack_bf16x2(res[6], res[7])));
+      }
+    } else {
+      for (long long c = lane; c < width; c += 32) {
+        const float v = __bfloat162float(src[c]);
+        const float w = to_f32<WT>(weight[c]) + weight_offset;
+        dst[c] = __float2bfloat16_rn(!BACKWARD ? v * inv * w
+                                               : inv * (__bfloat162float(gsrc[c]) * w - v * inv * correction));
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// AdamW over flat fp32 arrays (decoupled weight decay, bias correction as torch.optim.AdamW computes it).
+// All adapter parameters, their gradients and both moments live in flat arenas, so one launch steps every adapter.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) adamw_kernel(float4* __restrict__ param, const float4* __restrict__ grad,
+                                                    float4* __restrict__ exp_avg, float4* __restrict__ exp_avg_sq,
+                                                    long long vectors, float lr, float beta1, float beta2, float eps,
+                                                    float weight_decay, float bias1, float bias2_sqrt, float grad_scale) {
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < vectors;
+       v += (long long)gridDim.x * blockDim.x) {
+    const float4 g4 = __ldcs(grad + v);
+    float4 p4 = param[v], m4 = exp_avg[v], s4 = exp_avg_sq[v];
+    float g[4] = {g4.x, g4.y, g4.z, g4.w};
+    float p[4] = {p4.x, p4.y, p4.z, p4.w}, m[4] = {m4.x, m4.y, m4.z, m4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float gi = g[i] * grad_scale;
+      p[i] *= 1.0f - lr * weight_decay;
+      m[i] = beta1 * m[i] + (1.0f - beta1) * gi;
+      s[i] = beta2 * s[i] + (1.0f - beta2) * gi * gi;
+      const float denom = sqrtf(s[i]) / bias2_sqrt + eps;
+      p[i] -= (lr / bias1) * (m[i] / denom);
+    }
+    param[v] = make_float4(p[0], p[1], p[2], p[3]);
+    exp_avg[v] = make_float4(m[0], m[1], m[2], m[3]);
+    exp_avg_sq[v] = make_float4(s[0], s[1], s[2], s[3]);
   }
 }
 
@@ -300,22 +410,64 @@ extern "C" int molt_swiglu_bwd(const void* grad_out, const void* gate, const voi
   return swiglu_launch(gate, up, grad_out, h_out, dgate, dup, count, dtype, true, stream);
 }
 
-extern "C" int molt_rmsnorm_fwd(const void* x, const void* weight, int weight_dtype, float eps, float weight_offset,
-                                void* out, int64_t rows, int64_t width, uintptr_t stream) {
-  MOLT_REQUIRE(x && weight && out, MOLT_E_VALUE, "rmsnorm: NULL tensor pointer");
-  MOLT_REQUIRE(rows >= 0 && width > 0, MOLT_E_VALUE, "rmsnorm: bad shape");
+static int rmsnorm_launch(const char* who, const void* x, const void* weight, int weight_dtype, const void* grad, float eps,
+                          float weight_offset, void* out, int64_t rows, int64_t width, uintptr_t stream) {
+  MOLT_REQUIRE(x && weight && out, MOLT_E_VALUE, "%s: NULL tensor pointer", who);
+  MOLT_REQUIRE(rows >= 0 && width > 0, MOLT_E_VALUE, "%s: bad shape", who);
   MOLT_REQUIRE(weight_dtype == MOLT_DTYPE_BF16 || weight_dtype == MOLT_DTYPE_F32, MOLT_E_CAPABILITY,
-               "rmsnorm: weight dtype must be bf16 or fp32");
+               "%s: weight dtype must be bf16 or fp32", who);
   if (rows == 0) return MOLT_OK;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(rows * 32, 256, 8);
-  if (weight_dtype == MOLT_DTYPE_F32)
-    rmsnorm_kernel<float><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (const float*)weight, eps, weight_offset,
-                                               (__nv_bfloat16*)out, rows, width);
-  else
-    rmsnorm_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)weight, eps,
-                                                       weight_offset, (__nv_bfloat16*)out, rows, width);
+  const bool vec = width % 8 == 0 && aligned16(x) && aligned16(out) && aligned16(weight) && (grad == nullptr || aligned16(grad));
+  auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto* gb = reinterpret_cast<const __nv_bfloat16*>(grad);
+  auto* ob = reinterpret_cast<__nv_bfloat16*>(out);
+#define MOLT_RMS_LAUNCH(WT, VEC, BWD)                                                                       \
+  rmsnorm_kernel<WT, VEC, BWD><<<grid, 256, 0, s>>>(xb, reinterpret_cast<const WT*>(weight), gb, eps, weight_offset, ob, \
+                                                    rows, width)
+  const bool f32 = weight_dtype == MOLT_DTYPE_F32, bwd = grad != nullptr;
+  if (f32 && vec && !bwd) MOLT_RMS_LAUNCH(float, true, false);
+  else if (f32 && vec && bwd) MOLT_RMS_LAUNCH(float, true, true);
+  else if (f32 && !vec && !bwd) MOLT_RMS_LAUNCH(float, false, false);
+  else if (f32 && !vec && bwd) MOLT_RMS_LAUNCH(float, false, true);
+  else if (!f32 && vec && !bwd) MOLT_RMS_LAUNCH(__nv_bfloat16, true, false);
+  else if (!f32 && vec && bwd) MOLT_RMS_LAUNCH(__nv_bfloat16, true, true);
+  else if (!f32 && !vec && !bwd) MOLT_RMS_LAUNCH(__nv_bfloat16, false, false);
+  else MOLT_RMS_LAUNCH(__nv_bfloat16, false, true);
+#undef MOLT_RMS_LAUNCH
   return launch_status("rmsnorm_kernel");
+}
+
+extern "C" int molt_rmsnorm_fwd(const void* x, const void* weight, int weight_dtype, float eps, float weight_offset,
+                                void* out, int64_t rows, int64_t width, uintptr_t stream) {
+  return rmsnorm_launch("molt_rmsnorm_fwd", x, weight, weight_dtype, nullptr, eps, weight_offset, out, rows, width, stream);
+}
+
+extern "C" int molt_rmsnorm_bwd(const void* grad_out, const void* x, const void* weight, int weight_dtype, float eps,
+                                float weight_offset, void* grad_x, int64_t rows, int64_t width, uintptr_t stream) {
+  MOLT_REQUIRE(grad_out != nullptr, MOLT_E_VALUE, "molt_rmsnorm_bwd: NULL tensor pointer");
+  return rmsnorm_launch("molt_rmsnorm_bwd", x, weight, weight_dtype, grad_out, eps, weight_offset, grad_x, rows, width,
+                        stream);
+}
+
+extern "C" int molt_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, int64_t count,
+                               float lr, float beta1, float beta2, float eps, float weight_decay, int64_t step,
+                               float grad_scale, uintptr_t stream) {
+  MOLT_REQUIRE(param && grad && exp_avg && exp_avg_sq, MOLT_E_VALUE, "molt_adamw_step: NULL tensor pointer");
+  MOLT_REQUIRE(count >= 0 && count % 4 == 0, MOLT_E_VALUE, "molt_adamw_step: the element count must be a multiple of 4");
+  MOLT_REQUIRE(aligned16(param) && aligned16(grad) && aligned16(exp_avg) && aligned16(exp_avg_sq), MOLT_E_VALUE,
+               "molt_adamw_step: arrays must be 16-byte aligned");
+  MOLT_REQUIRE(step >= 1, MOLT_E_VALUE, "molt_adamw_step: step counts from 1");
+  if (count == 0) return MOLT_OK;
+  const double bias1 = 1.0 - pow((double)beta1, (double)step);
+  const double bias2 = 1.0 - pow((double)beta2, (double)step);
+  const long long vectors = count / 4;
+  adamw_kernel<<<grid_for(vectors, 256, 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<float4*>(param), reinterpret_cast<const float4*>(grad), reinterpret_cast<float4*>(exp_avg),
+      reinterpret_cast<float4*>(exp_avg_sq), vectors, lr, beta1, beta2, eps, weight_decay, (float)bias1,
+      (float)sqrt(bias2), grad_scale);
+  return launch_status("adamw_kernel");
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -377,12 +529,15 @@ __global__ void __launch_bounds__(512) ce_softmax_grad_kernel(__nv_bfloat16* __r
     for (int i = 0; i < warps; ++i) gs += red_max[i] == -INFINITY ? 0.f : red_sum[i] * __expf(red_max[i] - gm);
     row_stats[0] = gm;
     row_stats[1] = gs;
+    // labels outside [0, vocab) (an ignore index such as -100) contribute no loss and no one-hot term, as at
+    // reference kernels/frozen_linear_cross_entropy.py:42-43, 63
     const long long t = targets[row];
-    row_loss[row] = logf(gs) + gm - __bfloat162float(x[t]);
+    row_loss[row] = (t >= 0 && t < vocab) ? logf(gs) + gm - __bfloat162float(x[t]) : 0.f;
   }
   __syncthreads();
   const float gm = row_stats[0];
   const float inv = grad_scale / row_stats[1];
+  // an out-of-range label matches no column below, so nothing is subtracted (reference :94-95, 133)
   const long long t = targets[row];
   for (long long v = threadIdx.x; v < vectors; v += blockDim.x) {
     const uint4 raw = *reinterpret_cast<const uint4*>(x + v * 8);

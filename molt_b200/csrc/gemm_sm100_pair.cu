@@ -11,15 +11,20 @@
 //
 // Per CTA: two TMA rings (16 KB activation tiles; 4 KB packed-code tiles, deeper) run several blocks ahead of a
 // separate ring of decoded B half-tiles, so the global-memory latency is not serialised with the decode.
-// Decode: one 8-byte shared-memory lookup per packed byte returns both fp32 codebook values (table replicated
-// per bank pair, conflict free), multiplied by the fp32 absmax and rounded once to bf16 -- the bits of the
-// standalone dequantiser.  The leader CTA's MMA warp issues the pair MMA and signals both CTAs with
-// tcgen05.commit; decoders and epilogue warps of the second CTA signal the leader with remote mbarrier arrives.
-// All waits are bounded (status word + clean exit), and TMEM is released after a cluster barrier.
+// Decode: a decoder thread owns one 64-element segment (one absmax) per block.  It first forms the sixteen values
+// the segment can take, bf16(fp32 codebook value x fp32 absmax) -- one fp32 multiply and one rounding each, the bits
+// of the standalone dequantiser -- and keeps them in registers as two byte planes (low and high bytes of the sixteen
+// bf16 values).  Every 4-bit code then selects its value with byte permutes (prmt): the code's low three bits index
+// eight table bytes, its top bit picks between the two table halves.  No lookup table in shared memory: the L1 /
+// shared-memory data path, the busiest unit of this kernel, carries only the TMA writes, the packed codes, the
+// decoded tile and the tensor core's operand reads.  The leader CTA's MMA warp issues the pair MMA and signals
+// both CTAs with tcgen05.commit; decoders and epilogue warps of the second CTA signal the leader with remote
+// mbarrier arrives.  All waits are bounded (status word + clean exit), and TMEM is released after a cluster barrier.
 #include <cuda.h>
 #include <cudaTypedefs.h>
+#ifdef MOLT_PAIR_TRACE
 #include <stdlib.h>
-
+#endif
 #include "internal.h"
 #include "sm100_ptx.cuh"
 
@@ -31,14 +36,45 @@ constexpr int BN = 256;            // output columns per pair tile
 constexpr int BNH = 128;           // B rows decoded per CTA
 constexpr int BK = 64;
 constexpr int kEpilogueWarps = 4;
-// Decode groups: groups of four warps that take the contraction blocks in turn.  Measured on the 14336 x 4096 weight at
-// 4096 tokens with the (6, 3) rings, same box, forward / backward: 2 groups 451-457 / 439-444 us, 3 groups 478-482 /
-// 459-471 us, 4 groups 476 / 479-485 us.  Two groups also leave 128 registers per thread (no spills).
-constexpr int decode_groups(bool) { return 2; }
-constexpr int kProducerWarp = 4;
+// Decode groups: groups of four warps that take the contraction blocks in turn.
+#ifndef MOLT_PAIR_GROUPS
+#define MOLT_PAIR_GROUPS 3
+#endif
+#ifndef MOLT_PAIR_LOAD_STAGES
+#define MOLT_PAIR_LOAD_STAGES 6
+#endif
+// How many of the eight code words of a segment are decoded through the lookup table in shared memory (load/store
+// pipe) instead of byte permutes in registers (integer pipe): the two pipes work side by side.
+#ifndef MOLT_PAIR_LUT_WORDS
+#define MOLT_PAIR_LUT_WORDS 0
+#endif
+#ifndef MOLT_PAIR_B_STAGES
+#define MOLT_PAIR_B_STAGES (MOLT_PAIR_LUT_WORDS > 0 ? 3 : 5)
+#endif
+constexpr int kDecodeGroupsDefault = MOLT_PAIR_GROUPS;
+constexpr int kLoadStagesDefault = MOLT_PAIR_LOAD_STAGES;   // ring of activation tiles
+constexpr int kBStagesDefault = MOLT_PAIR_B_STAGES;         // ring of decoded B half-tiles
+// Warp roles.  An SM issues from four schedulers and warp w belongs to scheduler w % 4.  The three single-thread loops
+// that pace the pipeline (MMA issue, the two TMA producers) are long dependent instruction chains, so they get
+// scheduler 1 to themselves (next to one epilogue warp, which is idle most of the time); the decoder warps, which
+// issue thousands of instructions per block, are the warps >= 4 on the other three schedulers.
 constexpr int kMmaWarp = 5;
-constexpr int kFirstDecodeWarp = 6;
-constexpr int pair_threads(int groups) { return (kFirstDecodeWarp + 4 * groups) * 32; }
+constexpr int kActivationWarp = 9;    // TMA producer of the activation tiles
+constexpr int kCodeWarp = 13;         // TMA producer of the packed-code tiles
+__host__ __device__ constexpr bool is_decode_warp(int warp) { return warp >= 4 && (warp & 3) != 1; }
+// position of a decode warp among the decode warps (warps 4, 6, 7, 8, 10, 11, 12, 14, ...)
+__host__ __device__ constexpr int decode_warp_index(int warp) {
+  return ((warp >> 2) - 1) * 3 + ((warp & 3) == 0 ? 0 : (warp & 3) - 1);
+}
+constexpr int pair_warps(int groups) {
+  int warp = 4, found = 0;
+  while (found < 4 * groups) {
+    if (is_decode_warp(warp)) ++found;
+    ++warp;
+  }
+  return warp > kCodeWarp + 1 ? warp : kCodeWarp + 1;
+}
+constexpr int pair_threads(int groups) { return pair_warps(groups) * 32; }
 
 constexpr uint32_t kTileABytes = BM * BK * 2;          // 16384
 constexpr uint32_t kPackedBytes = BNH * BK / 2;        // 4096
@@ -46,7 +82,8 @@ constexpr uint32_t kLoadStageBytes = kTileABytes;      // activation ring stage
 constexpr int kCodeStages = 8;                         // ring of packed-code tiles; runs further ahead than the activations
 constexpr uint32_t kTileBBytes = BNH * BK * 2;         // 16384
 constexpr uint32_t kStoreBytes = BM * 64 * 2;          // 16384
-constexpr uint32_t kLutBytes = 256 * 16 * 8;           // 32768: [byte][16 copies] of float2
+constexpr int kLutWords = MOLT_PAIR_LUT_WORDS;
+constexpr uint32_t kLutBytes = kLutWords > 0 ? 256 * 16 * 8 : 0;   // [byte][16 copies] of float2 (both codebook values of a byte)
 constexpr uint32_t smem_bytes(int load_stages, int b_stages, int store_bufs) {
   return load_stages * kLoadStageBytes + kCodeStages * kPackedBytes + b_stages * kTileBBytes +
          store_bufs * kStoreBytes + kLutBytes + 512 /*barriers*/ + 1024 /*alignment*/;
@@ -63,9 +100,12 @@ struct Params {
   int full_tiles;        // tiles on the static schedule (whole waves); the tiles after them are split along the contraction
   float* split_partial;  // [pairs][2 parts][2 CTAs][128 rows][256 columns] fp32 partial accumulators of the split tiles
   int nibble_high_first;
-  unsigned long long* trace;   // optional [2 CTAs][4 roles][256 events] timestamps (ns) for pipeline analysis
-  int debug;             // timing experiments only: 1 = skip decode, 2 = skip MMA issue, 4 = skip epilogue stores,
-                         // 16 = skip writing split partials
+  long long wait_cycles; // limit of every bounded wait, in SM clock cycles
+  int withhold;          // failure injection (tests): the producers issue this many contraction blocks fewer than the
+                         // consumers expect, so that a bounded wait runs out; 0 in normal use
+#ifdef MOLT_PAIR_TRACE
+  unsigned long long* trace;   // optional [2 CTAs][12 roles][256 events] timestamps (ns) for pipeline analysis
+#endif
   float codebook[16];
 };
 
@@ -74,12 +114,17 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// role: 0 producer (TMA issued), 1 MMA (issued), 2 decoder warp 0 (waits done), 3 decoder warp 0 (arrived)
+// role: 0 producer (TMA issued), 1 MMA (issued), 2 decoder warp 0 (waits done), 3 decoder warp 0 (arrived),
+//       4 decoder warp 0 (block decoded, before the wait for the activation tile), 5 decoder warp 0 (loop entry)
+#ifdef MOLT_PAIR_TRACE
 #define MOLT_TRACE(role, index)                                                                       \
   do {                                                                                                \
     if (p.trace != nullptr && blockIdx.x < 2 && (index) < 256)                                        \
-      p.trace[(blockIdx.x * 4 + (role)) * 256 + (index)] = global_ns();                               \
+      p.trace[(blockIdx.x * 12 + (role)) * 256 + (index)] = global_ns();                               \
   } while (0)
+#else
+#define MOLT_TRACE(role, index) do {} while (0)
+#endif
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -99,10 +144,6 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 }
 // Barriers completed from the other CTA (remote arrives, tcgen05.commit of the leader) are waited on with the
 // ordinary CTA-scope try_wait.
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  int32_t* status, int where) {
-  return mbar_wait(bar, parity, abort_flag, status, where);
-}
 __device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
   uint64_t d;
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
@@ -131,6 +172,44 @@ __device__ __forceinline__ void umma_commit_both(uint32_t local_bar_addr) {
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// ---- NF4 decode in registers ---------------------------------------------------------------------------------
+// The sixteen bf16 values of one segment, split into byte planes: lo[i] / hi[i] hold the low / high bytes of entries
+// 4 i .. 4 i + 3.
+struct SegmentTable {
+  uint32_t lo[4], hi[4];
+};
+__device__ __forceinline__ SegmentTable make_segment_table(const float (&codebook)[16], float absmax) {
+  uint32_t pairs[8];   // (entry 2 i, entry 2 i + 1) as bf16x2; one fp32 multiply and one rounding per entry
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    pairs[i] = pack_bf16x2(__fmul_rn(codebook[2 * i], absmax), __fmul_rn(codebook[2 * i + 1], absmax));
+  SegmentTable t;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    t.lo[i] = __byte_perm(pairs[2 * i], pairs[2 * i + 1], 0x6420u);
+    t.hi[i] = __byte_perm(pairs[2 * i], pairs[2 * i + 1], 0x7531u);
+  }
+  return t;
+}
+// Eight codes (one 32-bit word, code i in bits 4 i .. 4 i + 3) -> eight bf16 values.  A byte permute indexes eight
+// bytes with the low three bits of a selector nibble (bit 3 would ask for sign replication, so it is masked off);
+// the code's top bit chooses between the two halves of the table through a byte mask.  pick01 / pick23 order the
+// result for the weight's nibble order.
+__device__ __forceinline__ void decode_word(uint32_t w, const SegmentTable& t, uint32_t pick01, uint32_t pick23,
+                                            uint32_t (&out)[4]) {
+  const uint32_t low3 = w & 0x77777777u;
+  const uint32_t top = (w >> 3) & 0x11111111u;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const uint32_t sel = c == 0 ? low3 : (low3 >> 16);   // prmt reads the low 16 bits of its selector
+    const uint32_t upper = __byte_perm(0x0000ff00u, 0u, c == 0 ? top : (top >> 16));   // 0xff where the code is >= 8
+    const uint32_t lo = (__byte_perm(t.lo[0], t.lo[1], sel) & ~upper) | (__byte_perm(t.lo[2], t.lo[3], sel) & upper);
+    const uint32_t hi = (__byte_perm(t.hi[0], t.hi[1], sel) & ~upper) | (__byte_perm(t.hi[2], t.hi[3], sel) & upper);
+    out[2 * c] = __byte_perm(lo, hi, pick01);
+    out[2 * c + 1] = __byte_perm(lo, hi, pick23);
+  }
 }
 
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -206,40 +285,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(kDecode
 nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_packed,
                            const __grid_constant__ CUtensorMap map_low, const __grid_constant__ CUtensorMap map_ext,
                            const __grid_constant__ CUtensorMap map_out, const __grid_constant__ Params p) {
-  constexpr int kThreads = pair_threads(kDecodeGroups);
   extern __shared__ unsigned char smem_dyn[];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag_s;
   __shared__ WorkPlan plan_s;
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  unsigned char* base_ptr = smem_dyn + (base - raw);
   const uint32_t load0 = base;
   const uint32_t codes0 = load0 + kLoadStages * kLoadStageBytes;
   const uint32_t btile0 = codes0 + kCodeStages * kPackedBytes;
   const uint32_t store0 = btile0 + kBStages * kTileBBytes;
   const uint32_t lut0 = store0 + kStoreBufs * kStoreBytes;
   const uint32_t bar0 = lut0 + kLutBytes;
-  float2* lut_ptr = reinterpret_cast<float2*>(base_ptr + (lut0 - base));
   auto bar_ldfull = [&](int s) { return bar0 + 8u * s; };
   // consumed[g % 8] completes when the MMAs of contraction block number g (counted per CTA across tiles) have
   // finished reading their operands; ONE commit per block releases both the load stage and the B stage, in both
   // CTAs.  Sixteen slots exceed every ring depth, so a waiter can never be lapped.
   constexpr int kConsumedSlots = 16;
-  static_assert(kLoadStages < kCodeStages && kCodeStages < kConsumedSlots && kBStages < kConsumedSlots,
+  static_assert(kLoadStages < kConsumedSlots && kCodeStages < kConsumedSlots && kBStages < kConsumedSlots,
                 "ring deeper than the consumed slots");
   auto bar_consumed = [&](int g) { return bar0 + 8u * (kLoadStages + (g & (kConsumedSlots - 1))); };
   auto bar_bfull = [&](int s) { return bar0 + 8u * (kLoadStages + kConsumedSlots + s); };          // used in the leader
   auto bar_accfull = [&](int b) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + b); };
   auto bar_accempty = [&](int b) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + 2 + b); };  // leader
-  const uint32_t bar_ext = bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + 4);
-  auto bar_pkfull = [&](int s) { return bar_ext + 8u * (1 + s); };
+  // one low-rank barrier per decode group: a group waits for its own load before it moves on, so a barrier never sees
+  // the expect_tx of a second load while the first is still pending (groups run several blocks apart)
+  auto bar_ext = [&](int grp) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + 4 + grp); };
+  auto bar_pkfull = [&](int s) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + 4 + kDecodeGroups + s); };
   auto consumed_parity = [&](int g) { return (uint32_t)((g / kConsumedSlots) & 1); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
   const bool leader = rank == 0;
   volatile int* abort_flag = &abort_flag_s;
+  auto wait_on = [&](uint32_t bar, uint32_t parity, int where) {
+    return mbar_wait(bar, parity, abort_flag, p.status, where, p.wait_cycles);
+  };
 
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
@@ -259,15 +340,18 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       mbar_init(bar_accfull(b), 1);
       mbar_init(bar_accempty(b), 2 * kEpilogueWarps);
     }
-    mbar_init(bar_ext, 1);
+    for (int gr = 0; gr < kDecodeGroups; ++gr) mbar_init(bar_ext(gr), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // byte -> (first element, second element) fp32 codebook values; 16 copies so that lane l reads bank pair l % 16
-  for (int i = threadIdx.x; i < 256 * 16; i += kThreads) {
-    const int byte = i >> 4;
-    const int lo = byte & 15, hi = byte >> 4;
-    lut_ptr[i] = p.nibble_high_first ? make_float2(p.codebook[hi], p.codebook[lo])
-                                     : make_float2(p.codebook[lo], p.codebook[hi]);
+  if (kLutWords > 0) {
+    // byte -> (first element, second element) fp32 codebook values; 16 copies so that lane l reads bank pair l % 16
+    float2* lut_ptr = reinterpret_cast<float2*>(smem_dyn + (lut0 - raw));
+    for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
+      const int byte = i >> 4;
+      const int lo = byte & 15, hi = byte >> 4;
+      lut_ptr[i] = p.nibble_high_first ? make_float2(p.codebook[hi], p.codebook[lo])
+                                       : make_float2(p.codebook[lo], p.codebook[hi]);
+    }
   }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
@@ -280,81 +364,66 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals across the pair
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  // Launched as a programmatic dependent of the kernel before it in the stream: everything above (barriers, the lookup
-  // table, TMEM) touches no global memory and may overlap that kernel's tail; nothing below runs before that kernel
+  // Launched as a programmatic dependent of the kernel before it in the stream: everything above (barriers, TMEM)
+  // touches no global memory and may overlap that kernel's tail; nothing below runs before that kernel
   // has completed and its writes are visible.  (Same-box A/B at 4096 tokens: +0.4 % per fwd+bwd step.  Launching the
   // small side kernels the same way was measured too and is slower, -0.7 %, so only the GEMM does it.)
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int pair_id = blockIdx.x >> 1;
-  const int blocks_per_tile = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
   const WorkPlan& plan = plan_s;   // in shared memory: read at item boundaries only, so it does not occupy registers
 
-  if (warp == kProducerWarp) {
-    // ================= TMA producer (each CTA loads its own token rows and its own half of the codes) ==========
-    // Two streams with the same block order: packed codes (small, kCodeStages deep, needed first by the decoders)
-    // and activation tiles (large, kLoadStages deep, needed last by the MMA).  Step t issues the codes of block t
-    // and the activations of block t - kLag; both ring slots are free once block t - kCodeStages is consumed.
-    constexpr int kLag = kCodeStages - kLoadStages;
-    struct Cursor {
-      WorkItem item;
-      int kb, tm, tn;
-      bool valid;
-    };
-    auto start_cursor = [&]() {
-      Cursor c;
-      c.item = first_item(plan);
-      c.valid = c.item.valid;
-      c.kb = c.item.kb0;
-      c.tm = c.tn = 0;
-      if (c.valid) pair_tile_coords(c.item.tile, p.tiles_m, p.tiles_n, c.tm, c.tn);
-      return c;
-    };
-    auto advance = [&](Cursor& c) {
-      if (++c.kb == c.item.kb1) {
-        next_item(plan, c.item);
-        c.valid = c.item.valid;
-        c.kb = c.item.kb0;
-        if (c.valid) pair_tile_coords(c.item.tile, p.tiles_m, p.tiles_n, c.tm, c.tn);
+  if (warp == kActivationWarp || warp == kCodeWarp) {
+    // ================= TMA producers (each CTA loads its own token rows and its own half of the codes) ==========
+    // Two warps, one stream each, same block order: packed codes (small, kCodeStages deep, needed first by the
+    // decoders) and activation tiles (large, kLoadStages deep, needed last by the MMA).  The slot of block t is free
+    // once block t - depth has been consumed.  One thread per warp runs the loop; it is kept short because its
+    // iteration time bounds the whole pipeline.
+    const bool codes = warp == kCodeWarp;
+    const int depth = codes ? kCodeStages : kLoadStages;
+    if (lane == 0) {
+      // Failure injection for tests: with p.withhold = w the last w blocks of this CTA are never requested, so the
+      // consumers' bounded waits run out.  total_blocks is only computed when the injection is on.
+      int total_blocks = 0x7fffffff;
+      if (p.withhold > 0) {
+        total_blocks = 0;
+        for (WorkItem it = first_item(plan); it.valid; next_item(plan, it)) total_blocks += it.kb1 - it.kb0;
+        total_blocks -= p.withhold;
       }
-    };
-    Cursor pc = start_cursor(), ac = start_cursor();
-    bool ok = true;
-    for (int t = 0; ok; ++t) {
-      if (!pc.valid && !ac.valid) break;
-      const bool do_codes = pc.valid;
-      const bool do_act = t >= kLag && ac.valid;
-      if (t >= kCodeStages)
-        ok = mbar_wait_cluster(bar_consumed(t - kCodeStages), consumed_parity(t - kCodeStages), abort_flag, p.status, 1);
-      if (!ok) break;
-      if (lane == 0) {
-        if (do_codes) {
-          const int s = t % kCodeStages;
-          if (pc.kb < p.num_kb) {
-            const uint32_t pk_dst = codes0 + (uint32_t)s * kPackedBytes;
-            mbar_expect_tx(bar_pkfull(s), kPackedBytes);
-            if (!BACKWARD) tma_load_2d(pk_dst, &map_packed, pc.kb * (BK / 2), pc.tn * BN + (int)rank * BNH, bar_pkfull(s));
-            else tma_load_2d(pk_dst, &map_packed, (pc.tn * BN + (int)rank * BNH) / 2, pc.kb * BK, bar_pkfull(s));
+      int t = 0, stage = 0;
+      for (WorkItem item = first_item(plan); item.valid && t < total_blocks; next_item(plan, item)) {
+        int tm, tn;
+        pair_tile_coords(item.tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int row0 = tm * 2 * BM + (int)rank * BM;          // first token row of this CTA
+        const int col0 = tn * BN + (int)rank * BNH;             // first B row of this CTA
+        bool ok = true;
+        for (int kb = item.kb0; kb < item.kb1 && t < total_blocks; ++kb, ++t) {
+          if (t >= depth) ok = wait_on(bar_consumed(t - depth), consumed_parity(t - depth), 1);
+          if (!ok) break;
+          if (codes) {
+            MOLT_TRACE(8, t);
+            if (kb < p.num_kb) {
+              const uint32_t pk_dst = codes0 + (uint32_t)stage * kPackedBytes;
+              mbar_expect_tx(bar_pkfull(stage), kPackedBytes);
+              if (!BACKWARD) tma_load_2d(pk_dst, &map_packed, kb * (BK / 2), col0, bar_pkfull(stage));
+              else tma_load_2d(pk_dst, &map_packed, col0 / 2, kb * BK, bar_pkfull(stage));
+            } else {
+              mbar_arrive(bar_pkfull(stage));   // the low-rank block has no codes; keep the ring's phases in step
+            }
+            MOLT_TRACE(9, t);
           } else {
-            mbar_arrive(bar_pkfull(s));   // the low-rank block has no codes; keep the ring's phases in step
+            const uint32_t a_dst = load0 + (uint32_t)stage * kLoadStageBytes;
+            mbar_expect_tx(bar_ldfull(stage), kTileABytes);
+            if (kb < p.num_kb) tma_load_2d(a_dst, &map_in, kb * BK, row0, bar_ldfull(stage));
+            else tma_load_2d(a_dst, &map_low, 0, row0, bar_ldfull(stage));
+            MOLT_TRACE(0, t);
           }
+          if (++stage == depth) stage = 0;
         }
-        if (do_act) {
-          const int s = (t - kLag) % kLoadStages;
-          const uint32_t a_dst = load0 + (uint32_t)s * kLoadStageBytes;
-          const int row0 = ac.tm * 2 * BM + (int)rank * BM;
-          mbar_expect_tx(bar_ldfull(s), kTileABytes);
-          if (ac.kb < p.num_kb) tma_load_2d(a_dst, &map_in, ac.kb * BK, row0, bar_ldfull(s));
-          else tma_load_2d(a_dst, &map_low, 0, row0, bar_ldfull(s));
-        }
-#ifdef MOLT_PAIR_TRACE
-        MOLT_TRACE(0, t);
-#endif
+        if (!ok) break;
       }
-      __syncwarp();
-      if (do_codes) advance(pc);
-      if (do_act) advance(ac);
     }
+    __syncwarp();
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer (leader CTA only) =================
     if (leader) {
@@ -372,7 +441,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         uint32_t bphase = 0, acc_phase = 0;
         bool ok = true;
         for (WorkItem item = first_item(plan); item.valid && ok; next_item(plan, item)) {
-          ok = mbar_wait_cluster(bar_accempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2);
+          ok = wait_on(bar_accempty(acc), acc_phase ^ 1u, 2);
           if (!ok) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
@@ -380,12 +449,17 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           for (int kb = item.kb0; kb < item.kb1; ++kb) {
             // The decoders of both CTAs arrive on b_full only after their own activation tile has landed, so
             // this one wait covers both operands in both CTAs.
-            ok = mbar_wait_cluster(bar_bfull(bs), bphase, abort_flag, p.status, 4);
+            ok = wait_on(bar_bfull(bs), bphase, 4);
             if (!ok) break;
+            MOLT_TRACE(6, g);
             tc_fence_after();
             const uint32_t a_lo = a_lo0 + (uint32_t)ls * (kLoadStageBytes >> 4);
             const uint32_t b_lo = b_lo0 + (uint32_t)bs * (kTileBBytes >> 4);
+#ifdef MOLT_PAIR_EXP_NO_MMA      // timing experiment: no tensor work, only the commits (results are wrong)
+            if (false) {
+#else
             if (kb < p.num_kb) {
+#endif
               umma_bf16_pair(d_tmem, desc64(a_lo, desc_hi), desc64(b_lo, desc_hi), idesc, accumulate);
 #pragma unroll
               for (int ks = 1; ks < BK / 16; ++ks)
@@ -396,12 +470,11 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
                                (accumulate | (uint32_t)(ks > 0)));
             }
             accumulate = 1u;
+            MOLT_TRACE(7, g);
             // one commit releases this block's load stage and B stage in both CTAs once the MMAs have read them
             umma_commit_both(bar_consumed(g));
             if (kb == item.kb1 - 1) umma_commit_both(bar_accfull(acc));
-#ifdef MOLT_PAIR_TRACE
             MOLT_TRACE(1, g);
-#endif
             ++g;
             if (++ls == kLoadStages) ls = 0;
             if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
@@ -411,16 +484,19 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       }
       __syncwarp();
     }
-  } else if (warp >= kFirstDecodeWarp) {
+  } else if (is_decode_warp(warp) && decode_warp_index(warp) < 4 * kDecodeGroups) {
     // ================= NF4 decoders =================
     // Groups of four warps take the contraction blocks in turn (running block number modulo the group count),
     // so the decode latency of one block overlaps the following blocks'.  Inside a group every thread expands one whole
     // 64-element segment (one absmax) per block.
-    const int dt = threadIdx.x - kFirstDecodeWarp * 32;
-    const int dwarp = dt >> 5;
-    const int grp = dwarp % kDecodeGroups;
-    const int u = (dwarp / kDecodeGroups) * 32 + lane;   // 0..127 inside the group
+    const int dwarp = decode_warp_index(warp);
+    const int dt = dwarp * 32 + lane;                    // 0 for the thread that writes the trace
+    const int grp = dwarp >> 2;                          // four consecutive decode warps form a group
+    const int u = (dwarp & 3) * 32 + lane;               // 0..127 inside the group
     const uint32_t lut_lane = lut0 + (uint32_t)(lane & 15) * 8u;
+    // which table bytes make the bf16 pairs (element 0, element 1) and (element 2, element 3) of four decoded codes
+    const uint32_t pick01 = p.nibble_high_first ? 0x4051u : 0x5140u;
+    const uint32_t pick23 = p.nibble_high_first ? 0x6273u : 0x7362u;
     const long long kblocks_per_row = p.k / 64;
     const uint32_t bfull_remote_base = map_to_cta(bar_bfull(0), 0);
     uint32_t ext_phase = 0;
@@ -479,20 +555,22 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           const int kb = kb0 + kDecodeGroups * q;
           if (kb >= item.kb1 || !ok) continue;
           const float scale = cur[q];
-          unsigned long long scale2;   // (scale, scale)
-          asm("mov.b64 %0, {%1, %1};" : "=l"(scale2) : "f"(scale));
           const int g = g_tile + (kb - item.kb0);
           const int ls = g % kLoadStages, bs = g % kBStages, cs = g % kCodeStages;
-          ok = mbar_wait(bar_pkfull(cs), (uint32_t)((g / kCodeStages) & 1), abort_flag, p.status, 5);
+          // The sixteen values this segment can take, as byte planes (needs only the absmax: done before the waits).
+          SegmentTable table;
+          if (kLutWords < 8 && kb < p.num_kb) table = make_segment_table(p.codebook, scale);
+          unsigned long long scale2;   // (scale, scale)
+          asm("mov.b64 %0, {%1, %1};" : "=l"(scale2) : "f"(scale));
+          if (dt == 0) MOLT_TRACE(5, g);
+          ok = wait_on(bar_pkfull(cs), (uint32_t)((g / kCodeStages) & 1), 5);
           if (ok && g >= kBStages)   // the block that used this B stage must have been consumed
-            ok = mbar_wait_cluster(bar_consumed(g - kBStages), consumed_parity(g - kBStages), abort_flag, p.status, 6);
+            ok = wait_on(bar_consumed(g - kBStages), consumed_parity(g - kBStages), 6);
           if (!ok) continue;
-#ifdef MOLT_PAIR_TRACE
-          if (dt == 0 && !(p.debug & 64)) MOLT_TRACE(2, g);
-#endif
+          if (dt == 0) MOLT_TRACE(2, g);
           const uint32_t bt = btile0 + bs * kTileBBytes;
-          if (kb < p.num_kb && (p.debug & 1)) {
-          } else if (kb < p.num_kb) {
+          if (kb < p.num_kb) {
+#ifndef MOLT_PAIR_EXP_NO_DECODE   // (timing experiment: the decoders only do their waits and arrivals; results are wrong)
             const uint32_t pk = codes0 + (uint32_t)cs * kPackedBytes;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -501,62 +579,66 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
                            : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3])
                            : "r"(pk + (half == 0 ? src_off0 : src_off1))
                            : "memory");
-              // 16 table lookups (independent, issued back to back), then 16 two-wide multiplies (mul.rn.f32x2 rounds
-              // each lane like a scalar multiply), 16 roundings, 4 stores
-              unsigned long long codes[16];
 #pragma unroll
-              for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                  const uint32_t byte = __byte_perm(words[c], 0u, 0x4440u + (uint32_t)b);
-                  asm("ld.shared.b64 %0, [%1];" : "=l"(codes[c * 4 + b]) : "r"(lut_lane + byte * 128u));
-                }
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
+              for (int c = 0; c < 4; ++c) {   // one word = 8 codes = 16 bytes of bf16 = one swizzled chunk of the row
                 uint32_t out[4];
+                if (4 * half + c < kLutWords) {
+                  // table path: one 8-byte lookup per byte gives both fp32 codebook values; two-wide multiply
+                  // (mul.rn.f32x2 rounds each lane like a scalar multiply) and one rounding to bf16
 #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                  unsigned long long prod;
-                  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(prod) : "l"(codes[c * 4 + b]), "l"(scale2));
-                  asm("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.bf16x2.f32 %0, hi, lo;\n\t}" : "=r"(out[b]) : "l"(prod));
+                  for (int b = 0; b < 4; ++b) {
+                    const uint32_t byte = __byte_perm(words[c], 0u, 0x4440u + (uint32_t)b);
+                    unsigned long long pair, prod;
+                    asm("ld.shared.b64 %0, [%1];" : "=l"(pair) : "r"(lut_lane + byte * 128u));
+                    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(prod) : "l"(pair), "l"(scale2));
+                    asm("{\n\t.reg .f32 lo, hi;\n\tmov.b64 {lo, hi}, %1;\n\tcvt.rn.bf16x2.f32 %0, hi, lo;\n\t}" : "=r"(out[b]) : "l"(prod));
+                  }
+                } else {
+#ifdef MOLT_PAIR_EXP_NO_ALU      // timing experiment: loads and stores as usual, no decode arithmetic (results are wrong)
+                  out[0] = words[c]; out[1] = words[c] ^ 1u; out[2] = words[c] ^ 2u; out[3] = words[c] ^ 3u;
+#else
+                  decode_word(words[c], table, pick01, pick23, out);
+#endif
                 }
+#ifdef MOLT_PAIR_EXP_NO_STS      // timing experiment: decode, but store only when a value that never occurs shows up
+                if (out[0] == 0x12345678u)
+#endif
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bt + dst_off + ((((uint32_t)(4 * half + c)) ^ swz) << 4)),
                              "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3])
                              : "memory");
               }
             }
+#endif
             fence_proxy_async();
+            if (dt == 0) MOLT_TRACE(4, g);
           } else {
             // low-rank block: this CTA's half of the ready-made B operand comes by TMA into the B stage
             if (u == 0) {
               if (!BACKWARD) {
-                mbar_expect_tx(bar_ext, kTileBBytes);
-                tma_load_2d(bt, &map_ext, 0, col0, bar_ext);
+                mbar_expect_tx(bar_ext(grp), kTileBBytes);
+                tma_load_2d(bt, &map_ext, 0, col0, bar_ext(grp));
               } else {
-                mbar_expect_tx(bar_ext, 2u * (uint32_t)p.ext_steps * 16u * 128u);
-                tma_load_2d(bt, &map_ext, col0, 0, bar_ext);
-                tma_load_2d(bt + 8192u, &map_ext, col0 + 64, 0, bar_ext);
+                mbar_expect_tx(bar_ext(grp), 2u * (uint32_t)p.ext_steps * 16u * 128u);
+                tma_load_2d(bt, &map_ext, col0, 0, bar_ext(grp));
+                tma_load_2d(bt + 8192u, &map_ext, col0 + 64, 0, bar_ext(grp));
               }
             }
-            ok = mbar_wait(bar_ext, ext_phase, abort_flag, p.status, 7);
+            ok = wait_on(bar_ext(grp), ext_phase, 7);
             if (!ok) continue;
+            ext_phase ^= 1u;   // this group's barrier has completed once more
           }
           // this CTA's activation tile must have landed before the block is announced to the MMA thread
-          ok = mbar_wait(bar_ldfull(ls), (uint32_t)((g / kLoadStages) & 1), abort_flag, p.status, 9);
+          ok = wait_on(bar_ldfull(ls), (uint32_t)((g / kLoadStages) & 1), 9);
           if (!ok) continue;
           __syncwarp();
           if (lane == 0) mbar_arrive_remote(bfull_remote_base + 8u * (uint32_t)bs);
-#ifdef MOLT_PAIR_TRACE
-          if (dt == 0 && !(p.debug & 64)) MOLT_TRACE(3, g);
-#endif
+          if (dt == 0) MOLT_TRACE(3, g);
         }
 #pragma unroll
         for (int q = 0; q < kPrefetch; ++q) cur[q] = nxt[q];
       }
-      // the low-rank barrier completes once per item that holds the low-rank block, whichever group handled it
-      if (p.ext_steps > 0 && item.kb1 == blocks_per_tile) ext_phase ^= 1u;
     }
-  } else {
+  } else if (warp < kEpilogueWarps) {
     // ================= epilogue: TMEM -> bf16 -> shared -> TMA store (own 128 token rows) =================
     const int row = warp * 32 + lane;
     const uint32_t accempty_remote_base = map_to_cta(bar_accempty(0), 0);
@@ -568,7 +650,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       int tm, tn;
       pair_tile_coords(item.tile, p.tiles_m, p.tiles_n, tm, tn);
       const int row0 = tm * 2 * BM + (int)rank * BM;
-      ok = mbar_wait_cluster(bar_accfull(acc), acc_phase, abort_flag, p.status, 8);
+      ok = wait_on(bar_accfull(acc), acc_phase, 8);
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)acc * BN;
@@ -576,7 +658,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         // ---- part of a split tile: the fp32 accumulator goes to this pair's slot, row-major ----
         float* part = p.split_partial + split_slot_offset(pair_id, item.kb0 == 0 ? 1 : 0, (int)rank) + (size_t)row * BN;
         const bool row_valid = (long long)row0 + row < p.m;   // the fix-up kernel never reads rows past the end
-        for (int cg = 0; cg < BN / 32 && !(p.debug & 16); ++cg) {
+        for (int cg = 0; cg < BN / 32; ++cg) {
           uint32_t v[32];
           tmem_ld32(t_row + (uint32_t)cg * 32u, v);
           tmem_ld_wait();
@@ -593,7 +675,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         continue;
       }
-      for (int cg = 0; cg < BN / 64 && !(p.debug & 4); ++cg) {
+      for (int cg = 0; cg < BN / 64; ++cg) {
         const uint32_t stage_addr = store0 + (uint32_t)store_buf * kStoreBytes;
         // the store that last read this staging buffer must have finished reading it
         if (threadIdx.x == 0) {
@@ -688,18 +770,47 @@ __global__ void __launch_bounds__(256) split_fixup_kernel(const float* __restric
 }  // namespace pair
 
 // ---- host side -----------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
 int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* ptr, uint64_t inner, uint64_t outer,
                     uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
-                    const char* what);
+                    const char* what) {
+  auto fn = encode_fn();
+  if (fn == nullptr) return fail(MOLT_E_RUNTIME, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = fn(map, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return fail(MOLT_E_RUNTIME, "cuTensorMapEncodeTiled(%s) failed with code %d", what, (int)rc);
+  return MOLT_OK;
+}
+
+bool sm100_gemm_supported(const WeightView& w, int rank) {
+  return w.blocksize == 64 && w.k % 64 == 0 && w.n % 64 == 0 && rank <= 64;
+}
 
 // Scratch for splitting the last wave: two fp32 partial tiles per CTA pair.
 size_t sm100_split_bytes() {
   return pair::split_slot_offset(sm_count() / 2, 0, 0) * sizeof(float);
 }
 
-int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
-                    const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
-                    void* split_ws, cudaStream_t s) {
+int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
+               const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
+               void* split_ws, int flags, cudaStream_t s) {
   using namespace pair;
   if (!sm100_gemm_supported(w, rp)) return fail(MOLT_E_CAPABILITY, "tcgen05 GEMM: unsupported shape");
   const long long contraction = backward ? w.n : w.k;
@@ -752,20 +863,16 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
   p.tiles_m = (int)((m + 2 * BM - 1) / (2 * BM));
   p.tiles_n = (int)((out_cols + BN - 1) / BN);
   p.nibble_high_first = w.nibble_order == MOLT_NIBBLE_HIGH_FIRST ? 1 : 0;
+  p.wait_cycles = wait_limit_cycles();
+  p.withhold = take_withheld_blocks();
+#ifdef MOLT_PAIR_TRACE
   {
-    const char* dbg = getenv("MOLT_B200_DEBUG");
-    p.debug = dbg != nullptr ? atoi(dbg) : 0;
     const char* tr = getenv("MOLT_B200_TRACE_PTR");   // device pointer (decimal) of a 16 KB trace buffer
     p.trace = tr != nullptr ? reinterpret_cast<unsigned long long*>(strtoull(tr, nullptr, 10)) : nullptr;
   }
+#endif
   for (int i = 0; i < 16; ++i) p.codebook[i] = w.codebook[i];
 
-  int variant = 0;
-  {
-    const char* env = getenv("MOLT_B200_PAIR_STAGES");   // timing experiments: 0 = activation/B stages (6,3), the default; 1 = (4,4), 2 = (4,5), 3 = (3,6), 4 = (5,4); 5, 6, 7, 8 = (6,3) with 2, 3, 4, 1 decode groups; 9 = (5,3) with two store buffers
-    variant = env != nullptr ? atoi(env) : 0;
-    if (variant < 0 || variant > 9) variant = 0;
-  }
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   const long long all_pairs = sm_count() / 2;
   long long pairs = all_pairs;
@@ -774,10 +881,8 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
   p.full_tiles = (int)tiles;
   p.split_partial = nullptr;
   {
-    const char* env = getenv("MOLT_B200_NO_SPLIT");   // tests and timing experiments: 1 = keep the plain schedule
-    const char* force = getenv("MOLT_B200_FORCE_SPLIT");   // 1 = split whenever the shape allows it
-    const bool allowed = split_ws != nullptr && !(env != nullptr && atoi(env) != 0);
-    const bool forced = force != nullptr && atoi(force) != 0;
+    const bool allowed = split_ws != nullptr && !(flags & kGemmNoSplit);
+    const bool forced = (flags & kGemmForceSplit) != 0;
     const long long blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
     if (tiles < all_pairs) {
       // Fewer tiles than CTA pairs (few tokens): cutting all tiles along the contraction so that every pair of the device
@@ -796,47 +901,35 @@ int sm100_gemm_pair(bool backward, const WeightView& w, const float* absmax_f32,
     }
   }
   const int grid = (int)pairs * 2;
-  static thread_local bool configured[64][2][10] = {};
+  constexpr int LS = kLoadStagesDefault, BS = kBStagesDefault, SB = 1, GR = kDecodeGroupsDefault;
+  static thread_local bool configured[64][2] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));
-  const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0][variant];
-#define MOLT_PAIR_LAUNCH(BWD, LS, BS, SB, GR)                                                              \
-  do {                                                                                                     \
-    if (need_config)                                                                                       \
-      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB, GR>,                      \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,                          \
-                                     (int)smem_bytes(LS, BS, SB)));                                        \
-    cudaLaunchConfig_t cfg = {};                                                                           \
-    cfg.gridDim = dim3((unsigned)grid);                                                                    \
-    cfg.blockDim = dim3((unsigned)pair_threads(GR));                                                       \
-    cfg.dynamicSmemBytes = smem_bytes(LS, BS, SB);                                                         \
-    cfg.stream = s;                                                                                        \
-    cudaLaunchAttribute attr[1];                                                                           \
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                       \
-    attr[0].val.programmaticStreamSerializationAllowed = 1;                                                \
-    cfg.attrs = attr;                                                                                      \
-    cfg.numAttrs = 1;                                                                                      \
-    MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemm_sm100_pair_kernel<BWD, LS, BS, SB, GR>, map_in, map_packed, map_low, \
-                                 map_ext, map_out, p));                                                    \
-  } while (0)
-#define MOLT_PAIR_DISPATCH(BWD)                                                  \
-  do {                                                                           \
-    if (variant == 1) MOLT_PAIR_LAUNCH(BWD, 4, 4, 2, decode_groups(BWD));        \
-    else if (variant == 2) MOLT_PAIR_LAUNCH(BWD, 4, 5, 1, decode_groups(BWD));   \
-    else if (variant == 3) MOLT_PAIR_LAUNCH(BWD, 3, 6, 1, decode_groups(BWD));   \
-    else if (variant == 4) MOLT_PAIR_LAUNCH(BWD, 5, 4, 1, decode_groups(BWD));   \
-    else if (variant == 5) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 2);                    \
-    else if (variant == 6) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 3);                    \
-    else if (variant == 7) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 4);                    \
-    else if (variant == 8) MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, 1);                    \
-    else if (variant == 9) MOLT_PAIR_LAUNCH(BWD, 5, 3, 2, 2);                    \
-    else MOLT_PAIR_LAUNCH(BWD, 6, 3, 1, decode_groups(BWD));                     \
-  } while (0)
-  if (backward) MOLT_PAIR_DISPATCH(true);
-  else MOLT_PAIR_DISPATCH(false);
-#undef MOLT_PAIR_DISPATCH
-#undef MOLT_PAIR_LAUNCH
-  if (need_config) configured[dev][backward ? 1 : 0][variant] = true;
+  const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)pair_threads(GR));
+  cfg.dynamicSmemBytes = smem_bytes(LS, BS, SB);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (backward) {
+    if (need_config)
+      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<true, LS, BS, SB, GR>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(LS, BS, SB)));
+    MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemm_sm100_pair_kernel<true, LS, BS, SB, GR>, map_in, map_packed, map_low,
+                                 map_ext, map_out, p));
+  } else {
+    if (need_config)
+      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<false, LS, BS, SB, GR>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(LS, BS, SB)));
+    MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemm_sm100_pair_kernel<false, LS, BS, SB, GR>, map_in, map_packed, map_low,
+                                 map_ext, map_out, p));
+  }
+  if (need_config) configured[dev][backward ? 1 : 0] = true;
   if (int rc = launch_status("nf4_gemm_sm100_pair_kernel")) return rc;
   if (p.full_tiles < tiles) {
     WorkPlan plan;

@@ -1,549 +1,430 @@
-// Small-token (M <= 16) NF4 + LoRA forward.  The packed weight is streamed from HBM exactly once.
+// Small-token (M <= 16) NF4 + LoRA forward: y = x . deq(W)^T + s (x A^T) B^T with the packed weight streamed from
+// HBM exactly once, straight into registers.
 //
-// Work split: the grid is (CTAs per K-group, K-groups); a K-group is up to 32 absmax blocks (2048 columns) and
-// a CTA walks over 16-row chunks of W inside its K-group.  Up to sixteen streaming warps each own a fixed K-slice
-// of 2 absmax blocks (128 columns) and keep the matching X fragments in registers for their whole life.  Every
-// streaming warp runs its own load pipeline: per chunk it copies its 16 x 64 bytes of packed codes and its 32
-// absmax values into a private ring of shared-memory stages with cp.async (several chunks ahead, completion by
-// cp.async groups), so the load path needs no barrier between warps and the warps drift apart instead of
-// alternating between a load phase and a compute phase in lockstep.  Codes are expanded two at a time through a
-// byte-indexed table of bf16 pairs that is replicated once per lane (256 bytes per entry, bank = lane, so
-// lookups never conflict; one byte-permute builds the table offset from a code byte and the lane) and fed to
-// mma.sync m16n8k16 with the tokens as the M dimension.  The MMA runs on the unscaled code values; each absmax
-// block's partial sum is multiplied by its fp32 absmax afterwards (nested absmax: each lane resolves one value
-// per chunk and the quads fetch theirs by shuffle), so no per-element multiply is needed.  The streaming warps
-// drop their K-slice sums into a ring of buffers and two reducing warps add them in warp order (deterministic)
-// and write an fp32 partial per K-group.  The low-rank input T = X . A^T rides along: the X fragments are
-// already in registers, so the first CTAs of every K-group run a few more MMAs against bf16(A) and write their
-// K-group's part of T.  A small second kernel adds the K-groups, rounds T to bf16, adds the low-rank term and
-// rounds to bf16.  The only waits between warps are mbarrier waits of the sum ring; they have a time limit that
-// reports to the device status word.
-#include <cstdlib>
-
-#include "sm100_ptx.cuh"
+// One kernel does the whole product.  A CTA owns a contiguous range of 8-row groups of W with their FULL rows, so
+// nothing leaves the SM as a partial sum.  Inside the CTA the warps split the contraction: a warp owns a K-slice of
+// up to four absmax blocks (64 columns each) per pass, keeps the matching X fragments in registers, and walks over
+// the CTA's row groups two at a time (16 weight rows = the M dimension of mma.sync m16n8k16; the tokens are the N
+// dimension, eight per MMA).  Per 16 x 64 tile a lane issues two 8-byte loads of packed codes (the four lanes of a
+// quad cover the 32 contiguous bytes of one row's block, so every 32-byte sector fetched is used in full) a few
+// tiles ahead of their use, expands every byte into a bf16 pair of codebook values with one byte-permute (table
+// offset) and one shared-memory lookup (table replicated per lane, conflict-free), and runs four MMAs on the UNSCALED
+// values; the fp32 absmax of the row's block scales the block's partial sum afterwards (one FMA per accumulator), so
+// no per-element multiply is needed.  The accumulators of all row groups stay in registers for the whole kernel;
+// the warps' K-slice sums meet once, at the end, through shared memory (the table's space is reused), in warp order
+// (deterministic).  The summing threads add the low-rank term s T B^T and round once to bf16.
+//
+// T = bf16(x . bf16(A)^T) is produced by a small companion kernel launched in front.  The streaming kernel is launched
+// as its programmatic dependent: it starts at once and only waits for T (griddepcontrol.wait) after its own stream
+// is done, so the two run concurrently and the caller sees one kernel's latency.
+//
+// No thread waits on another except at __syncthreads, so there is no bounded-wait machinery here.
+#include "internal.h"
 
 namespace molt {
 
-constexpr int kGemvMaxWarps = 16;
-constexpr int kGemvBlocksPerWarp = 2;   // absmax blocks (of 64 columns) per warp
-constexpr int kGemvChunkRows = 16;
-constexpr int kGemvRing = 2;            // buffers between the streaming warps and the reducing warps
-constexpr int kGemvLutBytes = 256 * 256;   // [256 entries][64 lane positions, 32 used] bf16x2
-constexpr int kGemvStageBytes = 1024 + 128 + 64;   // codes [16 rows][64 B] | 32 absmax words | 16 raw words (nested)
-constexpr int kGemvStages = 6;   // depth of every warp's private ring (chunks in flight + the one being read)
-constexpr int kGemvSmemLimit = 227 * 1024;
+constexpr int kGemvWarps = 16;
+constexpr int kGemvMaxPairs = 7;            // row-group pairs (16 weight rows) per CTA whose sums stay in registers
+constexpr int kGemvLutStride = 256;         // bytes per table entry: 32 lanes x 4 bytes used, so that (byte << 8) | (lane * 4)
+constexpr int kGemvLutBytes = 256 * kGemvLutStride;   // is the offset and one byte-permute builds it
 
 struct GemvParams {
   WeightView w;
-  const __nv_bfloat16* x;   // [m, k]
-  const float* lora_a;      // [rank, k] fp32
-  float* t_partial;         // [kgroups][16][64] fp32: every K-group's part of x . bf16(A)^T
+  const __nv_bfloat16* x;    // [m, k]
+  const float* lora_b;       // [n, rank] fp32
+  const float* t;            // [16][64] fp32: x . A^T rounded to bf16 values (written by the companion kernel)
+  __nv_bfloat16* y;          // [m, n]
+  float scaling;
   int rank;
   int m;
-  int nblk;                 // k / 64
-  int kgroups;
-  int warps_per_cta;        // streaming warps
-  int32_t* status;
-  float* partial;           // [kgroups][16][n] fp32
-  int debug;                // with -DMOLT_GEMV_TRACE: bit 0 skips the decode + MMA work
-  long long* trace;         // optional [8 roles][64] clock64 stamps of one CTA; only with -DMOLT_GEMV_TRACE
+  int nblk;                  // k / 64
+  int warps;                 // streaming warps that own a K-slice (<= kGemvWarps)
+  int passes;                // K passes: pass p covers blocks [p * warps * BPW, (p + 1) * warps * BPW)
+  int groups_total;          // n / 8
+  int ctas;
 };
 
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// d = a . b + c with c given separately (used with c = 0 for the first MMA of an absmax block)
-__device__ __forceinline__ void mma_16816_c(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
-                                            const float (&c)[4]) {
+__device__ __forceinline__ void gemv_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1, const float (&c)[4]) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
-#ifdef MOLT_GEMV_TRACE
-#define GEMV_TRACE(role, index)                                                                  \
-  do {                                                                                           \
-    if (p.trace != nullptr && blockIdx.x == 3 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (index) < 64) \
-      p.trace[(role) * 64 + (index)] = clock64();                                                \
-  } while (0)
-#else
-#define GEMV_TRACE(role, index) do {} while (0)
-#endif
+__device__ __forceinline__ uint2 ldg_stream8(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
 
-__device__ __forceinline__ void named_sync(int id, int count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// Waits until at most N of this thread's most recent cp.async groups are still in flight.
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Ring of tiles in flight per warp: R = BPW * U tiles (U row-group pairs), refilled as tiles are consumed.
+constexpr int gemv_unroll_pairs(int bpw) { return bpw == 1 ? 4 : bpw == 2 ? 2 : 1; }
 
-template <bool NESTED>
-__global__ void __launch_bounds__((kGemvMaxWarps + 2) * 32, 1) nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  // pair table | [ring][warps][2 n-tiles][32 lanes][4] K-slice sums | [warps][32 lanes][4] low-rank sums | code2 |
-  // barriers | [warps][stages] private load stages
-  const int warps = p.warps_per_cta;   // streaming warps; the two warps after them reduce
-  unsigned char* lut_bytes = smem_raw;
-  float* red = reinterpret_cast<float*>(smem_raw + kGemvLutBytes);
-  float* t_red = red + kGemvRing * warps * 256;     // [warps][32][4]
-  float* code2_s = t_red + warps * 128;             // [256]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(code2_s + 256);
-  const uint32_t bar0 = smem_u32(bars);
-  auto red_full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto red_empty_bar = [&](int s) { return bar0 + 8u * (kGemvRing + s); };
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kGemvRing);
-  unsigned char* stage_mem = reinterpret_cast<unsigned char*>(bars + 8);   // 64 bytes hold the barriers and the flag
+// BPW: absmax blocks per warp per pass.  TT: token tiles of eight (1 for m <= 8, 2 for m <= 16).
+template <bool NESTED, int BPW, int TT>
+__global__ void __launch_bounds__(kGemvWarps * 32, 1) nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
+  constexpr int U = gemv_unroll_pairs(BPW);
+  constexpr int R = BPW * U;
+  extern __shared__ __align__(256) unsigned char smem_raw[];
+  unsigned char* lut_bytes = smem_raw;                                          // [256 entries][256 bytes]
+  float4* sums = reinterpret_cast<float4*>(smem_raw + kGemvLutBytes);           // [warp][pair][tt][lane]
+  __shared__ float code2_s[NESTED ? 256 : 1];
+  __shared__ float t_s[16 * 64];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int kgroup = blockIdx.y;
-  const int blk_first = kgroup * warps * kGemvBlocksPerWarp;                      // first absmax block of this K-group
+
+  // ---- this CTA's row groups: [group0, group1), walked in pairs ----
+  const int group0 = (int)(((long long)p.groups_total * blockIdx.x) / p.ctas);
+  const int group1 = (int)(((long long)p.groups_total * (blockIdx.x + 1)) / p.ctas);
+  const int ngroups = group1 - group0;
+  const int npairs = (ngroups + 1) >> 1;
   const long long row_bytes = p.w.k / 2;
-  const int chunks = (int)(p.w.n / kGemvChunkRows);
-  const int stride = gridDim.x;
-  const int total = (chunks - (int)blockIdx.x + stride - 1) / stride;             // chunks of this CTA
 
-  if (warp == 0) GEMV_TRACE(7, 0);
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kGemvRing; ++s) {
-      mbar_init(red_full_bar(s), warps);
-      mbar_init(red_empty_bar(s), 2);
-    }
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  // ---- table: byte -> bf16 pair (first element, second element) of codebook values, one copy per lane ----
+  for (int i = threadIdx.x; i < 256 * 8; i += kGemvWarps * 32) {
+    const int byte = i >> 3;
+    const int first = p.w.nibble_order == MOLT_NIBBLE_LOW_FIRST ? (byte & 15) : (byte >> 4);
+    const int second = p.w.nibble_order == MOLT_NIBBLE_LOW_FIRST ? (byte >> 4) : (byte & 15);
+    const uint32_t pair = pack_bf16x2(p.w.codebook[first], p.w.codebook[second]);
+    *reinterpret_cast<uint4*>(lut_bytes + byte * kGemvLutStride + (i & 7) * 16) = make_uint4(pair, pair, pair, pair);
   }
+  if (NESTED)
+    for (int i = threadIdx.x; i < 256; i += kGemvWarps * 32) code2_s[i] = p.w.code2[i];
+  __syncthreads();
 
-  // ---- this warp's K-slice ----
-  const int blk0 = blk_first + warp * kGemvBlocksPerWarp;
-  int nb = p.nblk - blk0;
-  if (nb < 0 || warp >= warps) nb = 0;
-  if (nb > kGemvBlocksPerWarp) nb = kGemvBlocksPerWarp;
-  // A warp whose K-slice has fewer than two blocks reads a valid block in place of the missing one; its X fragments
-  // for the missing block are zero, so that block adds zero.  Nothing is predicated inside the loop.
-  const int blkc = nb > 0 ? blk0 : 0;               // first block actually read
-  const int b1 = nb == kGemvBlocksPerWarp ? 1 : 0;  // offset of the second block, in blocks
-
-  // ---- private load pipeline (streaming warps) ----
-  // codes: lane copies 16-byte granule c = lane % 4 of rows lane / 4 and lane / 4 + 8; a granule of row r sits at
-  // position c ^ (2 * ((r / 2) % 2)) of the row's 64 bytes, which makes the 8-byte fragment reads conflict-free
-  const uint32_t my_stages = smem_u32(stage_mem) + (uint32_t)(warp * kGemvStages) * kGemvStageBytes;
-  const int cp_row = lane >> 2, cp_gran = lane & 3;
-  const bool cp_on = warp < warps && cp_gran < 2 * (b1 + 1);    // granules of blocks this warp really reads
-  const uint32_t cp_dst = (uint32_t)(cp_row * 64 + ((cp_gran ^ (((cp_row >> 1) & 1) << 1)) * 16));
-  const long long chunk_bytes = (long long)kGemvChunkRows * row_bytes;
-  const uint8_t* code_src = p.w.packed + ((long long)blockIdx.x * kGemvChunkRows + cp_row) * row_bytes +
-                            (long long)blkc * 32 + cp_gran * 16;
-  // absmax: lane copies the value of (row lane / 2, block lane % 2)
-  const int sc_row = lane >> 1, sc_b = (lane & 1) * b1;
-  const long long sc_index0 = ((long long)blockIdx.x * kGemvChunkRows + sc_row) * p.nblk + blkc + sc_b;
-  const long long sc_chunk = (long long)kGemvChunkRows * p.nblk;
-  const long long code_step = (long long)stride * chunk_bytes, sc_step = (long long)stride * sc_chunk;
-  const uint8_t* code_next = code_src;   // this lane's sources for the next chunk to request
-  long long sc_next = sc_index0;
-  // for the nested form, lanes 0..15 also copy the aligned word that holds row `lane`'s two codes; the rows' segments
-  // start on 2-byte boundaries of words because nblk % 4 == 0 (host-checked)
-  long long raw_next = (((long long)blockIdx.x * kGemvChunkRows + (lane & 15)) * p.nblk + blkc) & ~3LL;
-  int requested = 0;
-  auto issue = [&](int stage) {   // requests this CTA's next chunk into `stage`
-    if (requested < total) {
-      const uint32_t base = my_stages + (uint32_t)stage * kGemvStageBytes;
-      if (cp_on) {
-        cp_async_16(base + cp_dst, code_next);
-        cp_async_16(base + cp_dst + 512, code_next + 8 * row_bytes);
-      }
-      if (!NESTED) {
-        cp_async_4(base + 1024 + lane * 4, reinterpret_cast<const float*>(p.w.absmax) + sc_next);
-      } else {
-        cp_async_4(base + 1024 + lane * 4, p.w.absmax2 + (sc_next >> p.w.block2_shift));
-        if (lane < kGemvChunkRows)
-          cp_async_4(base + 1024 + 128 + lane * 4, reinterpret_cast<const uint8_t*>(p.w.absmax) + raw_next);
-      }
-      code_next += code_step;
-      sc_next += sc_step;
-      raw_next += sc_step;
-      ++requested;
-    }
-    cp_async_commit();
-  };
-
-  // ---- X fragments ----
-  uint32_t xa[kGemvBlocksPerWarp][4][4];
-#pragma unroll
-  for (int b = 0; b < kGemvBlocksPerWarp; ++b)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const long long col = (long long)(blk0 + b) * 64 + 16 * t + 4 * j;
-      uint2 lo = make_uint2(0, 0), hi = make_uint2(0, 0);
-      if (b < nb) {
-        if (g < p.m) lo = __ldg(reinterpret_cast<const uint2*>(p.x + (long long)g * p.w.k + col));
-        if (g + 8 < p.m) hi = __ldg(reinterpret_cast<const uint2*>(p.x + (long long)(g + 8) * p.w.k + col));
-      }
-      xa[b][j][0] = lo.x; xa[b][j][1] = hi.x; xa[b][j][2] = lo.y; xa[b][j][3] = hi.y;
-    }
-
-  // the first chunks are requested behind the X loads, so that X (L2 hits) does not queue behind them
-  if (warp < warps)
-    for (int j = 0; j < kGemvStages - 1; ++j) issue(j);
-
-  // ---- tables: one (byte, 8 lanes) item per step ----
-  {
-    const int builders = (warps + 2) * 32;
-    for (int i = threadIdx.x; i < 256 * 4; i += builders) {
-      const int byte = i >> 2;
-      const int first = p.w.nibble_order == MOLT_NIBBLE_LOW_FIRST ? (byte & 15) : (byte >> 4);
-      const int second = p.w.nibble_order == MOLT_NIBBLE_LOW_FIRST ? (byte >> 4) : (byte & 15);
-      const uint32_t pair = pack_bf16x2(p.w.codebook[first], p.w.codebook[second]);
-      uint4* dst = reinterpret_cast<uint4*>(lut_bytes + byte * 256 + (i & 3) * 32);
-      dst[0] = make_uint4(pair, pair, pair, pair);
-      dst[1] = make_uint4(pair, pair, pair, pair);
-    }
-    if (NESTED)
-      for (int i = threadIdx.x; i < 256; i += builders) code2_s[i] = p.w.code2[i];
-  }
-
-  // ---- low-rank input: CTA x of a K-group computes rows 8x .. 8x+7 of A against this K-group's columns ----
-  const int t_tile = blockIdx.x;                      // 8-row tile of A handled by this CTA (if any)
-  const bool t_owner = t_tile * 8 < p.rank;
-  if (t_owner && warp < warps) {
-    float tacc[4] = {0.f, 0.f, 0.f, 0.f};
-    const int r = t_tile * 8 + g;
-#pragma unroll
-    for (int b = 0; b < kGemvBlocksPerWarp; ++b)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float4 av = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (b < nb && r < p.rank)
-          av = __ldg(reinterpret_cast<const float4*>(p.lora_a + (long long)r * p.w.k + (long long)(blk0 + b) * 64 + 16 * t + 4 * j));
-        mma_16816(tacc, xa[b][j], pack_bf16x2(av.x, av.y), pack_bf16x2(av.z, av.w));
-      }
-    *reinterpret_cast<float4*>(t_red + (warp * 32 + lane) * 4) = make_float4(tacc[0], tacc[1], tacc[2], tacc[3]);
-  }
-  __syncthreads();   // tables, barriers and the low-rank sums are in place
-
-  if (warp >= warps) {
-    // ---- reducing warps (one per 8-row tile): add the K-slices of each chunk in warp order, write the fp32 partial ----
-    const int nt = warp - warps;
-    if (t_owner && nt == 0) {
-      // lane (g, t) holds tokens g, g + 8 and rows 2t, 2t + 1 of the tile: add the warps' K-slices in warp order
-      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int wv = 0; wv < warps; ++wv) {
-        const float4 v = *reinterpret_cast<const float4*>(t_red + (wv * 32 + lane) * 4);
-        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-      }
-      float* dst = p.t_partial + (long long)kgroup * 16 * 64 + t_tile * 8 + 2 * t;
-      *reinterpret_cast<float2*>(dst + g * 64) = make_float2(sum.x, sum.y);
-      *reinterpret_cast<float2*>(dst + (g + 8) * 64) = make_float2(sum.z, sum.w);
-    }
-    int buf = 0, phase = 0, tr_it = 0;
-    for (int chunk = blockIdx.x; chunk < chunks; chunk += stride) {
-      if (!mbar_wait(red_full_bar(buf), phase, abort_flag, p.status, 42)) return;
-      if (nt == 0) GEMV_TRACE(5, tr_it + 1);
-      const float* src = red + (size_t)buf * warps * 256 + (nt * 32 + lane) * 4;
-      float4 v[kGemvMaxWarps];
-#pragma unroll
-      for (int wv = 0; wv < kGemvMaxWarps; ++wv)
-        v[wv] = wv < warps ? *reinterpret_cast<const float4*>(src + wv * 256) : make_float4(0.f, 0.f, 0.f, 0.f);
-      float4 sum = v[0];
-#pragma unroll
-      for (int wv = 1; wv < kGemvMaxWarps; ++wv) {
-        sum.x += v[wv].x; sum.y += v[wv].y; sum.z += v[wv].z; sum.w += v[wv].w;
-      }
-      __syncwarp();                                     // every lane's loads have been consumed by its sums
-      if (lane == 0) mbar_arrive(red_empty_bar(buf));   // the buffer may be overwritten
-      // lane (g, t) holds tokens g and g + 8, rows 2t and 2t + 1 of the 8-row tile
-      float* dst = p.partial + (long long)kgroup * 16 * p.w.n + (long long)chunk * kGemvChunkRows + 2 * t + nt * 8;
-      *reinterpret_cast<float2*>(dst + (long long)g * p.w.n) = make_float2(sum.x, sum.y);
-      *reinterpret_cast<float2*>(dst + (long long)(g + 8) * p.w.n) = make_float2(sum.z, sum.w);
-      if (nt == 0) GEMV_TRACE(6, tr_it + 1);
-      ++tr_it;
-      if (++buf == kGemvRing) { buf = 0; phase ^= 1; }
-    }
-    return;
-  }
-
-  // ---- streaming warps ----
-  // fragment reads: lane (g, t) takes bytes 8 * (t % 2) .. + 7 of granule 2b + t / 2 of rows g and g + 8
-  uint32_t frag_off[kGemvBlocksPerWarp];
-#pragma unroll
-  for (int b = 0; b < kGemvBlocksPerWarp; ++b)
-    frag_off[b] = (uint32_t)(g * 64 + (((2 * b * b1 + (t >> 1)) ^ (((g >> 1) & 1) << 1)) * 16) + (t & 1) * 8);
   const uint32_t lane4 = (uint32_t)lane * 4u;
-  const int raw_off = 1024 + 128 + sc_row * 4 + (blkc & 3) + sc_b;   // this lane's code in the raw words (nested)
-  // table offset of code byte `which` of q: (byte << 8) | (lane * 4), built by one byte permute
-  auto lookup = [&](uint32_t q, uint32_t selector) -> uint32_t {
+  auto lookup = [&](uint32_t q, uint32_t selector) -> uint32_t {   // table entry of one code byte of q
     return *reinterpret_cast<const uint32_t*>(lut_bytes + __byte_perm(q, lane4, selector));
   };
   const float zero[4] = {0.f, 0.f, 0.f, 0.f};
-  const unsigned char* my_stage_ptr = stage_mem + (size_t)(warp * kGemvStages) * kGemvStageBytes;
-  int stage = 0, fill = kGemvStages - 1, buf = 0, red_phase = 0, red_wrapped = 0;
-  if (warp == 0) GEMV_TRACE(2, 0);
-  for (int it = 0; it < total; ++it) {
-    issue(fill);                          // into the stage the previous iteration read
-    if (++fill == kGemvStages) fill = 0;
-    cp_async_wait<kGemvStages - 1>();     // this lane's copies of chunk `it` have landed ...
-    __syncwarp();                         // ... and so have the other lanes'
-    if (warp == 0) GEMV_TRACE(2, it + 1);
-    const unsigned char* base = my_stage_ptr + stage * kGemvStageBytes;
-    uint2 cq[2][kGemvBlocksPerWarp];
-    float sc[2][2][kGemvBlocksPerWarp];   // absmax of (n-tile, row 2t + r, block)
+
+  if (warp < p.warps) {
+    for (int pass = 0; pass < p.passes; ++pass) {
+      const int blk0 = (pass * p.warps + warp) * BPW;         // first absmax block of this warp's K-slice
+      int nb = p.nblk - blk0;
+      if (nb > BPW) nb = BPW;
+      if (nb <= 0) continue;                                  // (its sums from earlier passes stay as they are)
+      // ---- X fragments of the K-slice: lane (g, t) holds token g's (and g + 8's) columns 64 b + 16 t .. + 15 ----
+      // A missing block (b >= nb) keeps zero fragments; its codes are read from block blk0 instead.
+      uint32_t xf[BPW][TT][8];
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+      for (int b = 0; b < BPW; ++b)
 #pragma unroll
-      for (int b = 0; b < kGemvBlocksPerWarp; ++b)
-        cq[nt][b] = *reinterpret_cast<const uint2*>(base + frag_off[b] + nt * 512);
-    if (!NESTED) {
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const float2 v = *reinterpret_cast<const float2*>(base + 1024 + (nt * 8 + 2 * t + r) * 8);
-          sc[nt][r][0] = v.x;
-          sc[nt][r][1] = v.y;
+        for (int tt = 0; tt < TT; ++tt) {
+          uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+          const int tok = tt * 8 + g;
+          if (b < nb && tok < p.m) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)tok * p.w.k + (long long)(blk0 + b) * 64 + 16 * t);
+            lo = __ldg(src);
+            hi = __ldg(src + 1);
+          }
+          xf[b][tt][0] = lo.x; xf[b][tt][1] = lo.y; xf[b][tt][2] = lo.z; xf[b][tt][3] = lo.w;
+          xf[b][tt][4] = hi.x; xf[b][tt][5] = hi.y; xf[b][tt][6] = hi.z; xf[b][tt][7] = hi.w;
         }
-    } else {
-      // lane L resolves the absmax of (row L / 2, block L % 2) of this warp's K-slice -- code2[u8] * absmax2 + offset
-      // with a separate multiply and add, the bits the dequantiser produces -- and the quads fetch theirs by shuffle
-      const float second = *reinterpret_cast<const float*>(base + 1024 + lane * 4);
-      const float mine = __fadd_rn(__fmul_rn(code2_s[base[raw_off]], second), p.w.offset);
+      // ---- the ring of tiles in flight: codes of rows g (first group of the pair) and g (second group), and the
+      // two absmax values (nested form: the 8-bit code and its second-level absmax), R tiles ahead of their use ----
+      const uint8_t* code_base = p.w.packed + ((long long)group0 * 8 + g) * row_bytes + (long long)blk0 * 32 + 8 * t;
+      const long long scale_base = ((long long)group0 * 8 + g) * p.nblk + blk0;
+      uint2 q0[R], q1[R];
+      float s0[R], s1[R];
+      uint32_t n0[NESTED ? R : 1], n1[NESTED ? R : 1];   // nested: raw 8-bit codes (s0/s1 then hold the second level)
+      auto request = [&](int slot, int pr, int b) {
+        if (pr >= npairs) pr = npairs - 1;                     // past the end: re-read the last tile (never used)
+        const int bb = b < nb ? b : 0;
+        const long long second_group = (2 * pr + 1 < ngroups) ? 8 : 0;   // odd group count: the last pair reads its first group twice
+        const uint8_t* src = code_base + (long long)pr * 16 * row_bytes + bb * 32;
+        q0[slot] = ldg_stream8(src);
+        q1[slot] = ldg_stream8(src + second_group * row_bytes);
+        const long long blk = scale_base + (long long)pr * 16 * p.nblk + bb;
+        const long long blk_second = blk + second_group * p.nblk;
+        if (!NESTED) {
+          s0[slot] = __ldg(reinterpret_cast<const float*>(p.w.absmax) + blk);
+          s1[slot] = __ldg(reinterpret_cast<const float*>(p.w.absmax) + blk_second);
+        } else {
+          n0[NESTED ? slot : 0] = __ldg(reinterpret_cast<const uint8_t*>(p.w.absmax) + blk);
+          n1[NESTED ? slot : 0] = __ldg(reinterpret_cast<const uint8_t*>(p.w.absmax) + blk_second);
+          s0[slot] = __ldg(p.w.absmax2 + (blk >> p.w.block2_shift));
+          s1[slot] = __ldg(p.w.absmax2 + (blk_second >> p.w.block2_shift));
+        }
+      };
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int b = 0; b < BPW; ++b) request(u * BPW + b, u, b);
+
+      for (int pr0 = 0; pr0 < npairs; pr0 += U) {
 #pragma unroll
-          for (int b = 0; b < kGemvBlocksPerWarp; ++b)
-            sc[nt][r][b] = __shfl_sync(0xffffffffu, mine, ((nt * 8 + 2 * t + r) << 1) | b);
-    }
-    float acc[2][4];
-#ifdef MOLT_GEMV_TRACE
-    if (p.debug & 1) {
+        for (int u = 0; u < U; ++u) {
+          const int pr = pr0 + u;
+          if (pr < npairs) {                                   // warp-uniform
+            float acc[TT][4];
+            float4* mine = sums + ((warp * kGemvMaxPairs + pr) * TT) * 32 + lane;
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+            for (int tt = 0; tt < TT; ++tt) {
+              if (pass == 0) {
+                acc[tt][0] = acc[tt][1] = acc[tt][2] = acc[tt][3] = 0.f;
+              } else {
+                const float4 v = mine[tt * 32];
+                acc[tt][0] = v.x; acc[tt][1] = v.y; acc[tt][2] = v.z; acc[tt][3] = v.w;
+              }
+            }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = __uint_as_float(cq[nt][0].x + cq[nt][1].y) * sc[nt][i & 1][i >> 1];
-    } else
-#endif
+            for (int b = 0; b < BPW; ++b) {
+              constexpr int kNone = 0;
+              const int slot = u * BPW + b;                      // compile-time
+              const uint2 c0 = q0[slot], c1 = q1[slot];
+              float sc0, sc1;
+              if (!NESTED) {
+                sc0 = s0[slot];
+                sc1 = s1[slot];
+              } else {
+                // code2[u8] * absmax2 + offset with a separate multiply and add: the dequantiser's bits
+                sc0 = __fadd_rn(__fmul_rn(code2_s[n0[NESTED ? slot : kNone]], s0[slot]), p.w.offset);
+                sc1 = __fadd_rn(__fmul_rn(code2_s[n1[NESTED ? slot : kNone]], s1[slot]), p.w.offset);
+              }
+              if (b >= nb) sc0 = sc1 = 0.f;
+              request(slot, pr + U, b);                          // refill the slot, U pairs ahead
+              // eight table lookups per row: bytes 2 s, 2 s + 1 of the lane's eight feed k-step s
+              uint32_t a_lo[8], a_hi[8];
+              a_lo[0] = lookup(c0.x, 0x5504); a_lo[1] = lookup(c0.x, 0x5514); a_lo[2] = lookup(c0.x, 0x5524); a_lo[3] = lookup(c0.x, 0x5534);
+              a_lo[4] = lookup(c0.y, 0x5504); a_lo[5] = lookup(c0.y, 0x5514); a_lo[6] = lookup(c0.y, 0x5524); a_lo[7] = lookup(c0.y, 0x5534);
+              a_hi[0] = lookup(c1.x, 0x5504); a_hi[1] = lookup(c1.x, 0x5514); a_hi[2] = lookup(c1.x, 0x5524); a_hi[3] = lookup(c1.x, 0x5534);
+              a_hi[4] = lookup(c1.y, 0x5504); a_hi[5] = lookup(c1.y, 0x5514); a_hi[6] = lookup(c1.y, 0x5524); a_hi[7] = lookup(c1.y, 0x5534);
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      float part[kGemvBlocksPerWarp][4];
-      uint32_t pr[kGemvBlocksPerWarp][8];
+              for (int tt = 0; tt < TT; ++tt) {
+                float part[4];
+                gemv_mma(part, a_lo[0], a_hi[0], a_lo[1], a_hi[1], xf[b][tt][0], xf[b][tt][1], zero);
 #pragma unroll
-      for (int b = 0; b < kGemvBlocksPerWarp; ++b) {
-        const uint2 q = cq[nt][b];
-        pr[b][0] = lookup(q.x, 0x5504); pr[b][1] = lookup(q.x, 0x5514); pr[b][2] = lookup(q.x, 0x5524); pr[b][3] = lookup(q.x, 0x5534);
-        pr[b][4] = lookup(q.y, 0x5504); pr[b][5] = lookup(q.y, 0x5514); pr[b][6] = lookup(q.y, 0x5524); pr[b][7] = lookup(q.y, 0x5534);
+                for (int s = 1; s < 4; ++s)
+                  gemv_mma(part, a_lo[2 * s], a_hi[2 * s], a_lo[2 * s + 1], a_hi[2 * s + 1], xf[b][tt][2 * s],
+                           xf[b][tt][2 * s + 1], part);
+                // accumulator rows: c0, c1 belong to weight row g of the first group, c2, c3 to row g of the second
+                acc[tt][0] = fmaf(part[0], sc0, acc[tt][0]);
+                acc[tt][1] = fmaf(part[1], sc0, acc[tt][1]);
+                acc[tt][2] = fmaf(part[2], sc1, acc[tt][2]);
+                acc[tt][3] = fmaf(part[3], sc1, acc[tt][3]);
+              }
+            }
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) mine[tt * 32] = make_float4(acc[tt][0], acc[tt][1], acc[tt][2], acc[tt][3]);
+          }
+        }
       }
-#pragma unroll
-      for (int b = 0; b < kGemvBlocksPerWarp; ++b) mma_16816_c(part[b], xa[b][0], pr[b][0], pr[b][1], zero);
-#pragma unroll
-      for (int j = 1; j < 4; ++j)
-#pragma unroll
-        for (int b = 0; b < kGemvBlocksPerWarp; ++b) mma_16816(part[b], xa[b][j], pr[b][2 * j], pr[b][2 * j + 1]);
-      // accumulator columns: c0, c2 belong to row 2t (r = 0), c1, c3 to row 2t + 1 (r = 1)
-      acc[nt][0] = part[0][0] * sc[nt][0][0];
-      acc[nt][1] = part[0][1] * sc[nt][1][0];
-      acc[nt][2] = part[0][2] * sc[nt][0][0];
-      acc[nt][3] = part[0][3] * sc[nt][1][0];
-#pragma unroll
-      for (int b = 1; b < kGemvBlocksPerWarp; ++b) {
-        acc[nt][0] = fmaf(part[b][0], sc[nt][0][b], acc[nt][0]);
-        acc[nt][1] = fmaf(part[b][1], sc[nt][1][b], acc[nt][1]);
-        acc[nt][2] = fmaf(part[b][2], sc[nt][0][b], acc[nt][2]);
-        acc[nt][3] = fmaf(part[b][3], sc[nt][1][b], acc[nt][3]);
-      }
     }
-    if (warp == 0) GEMV_TRACE(3, it + 1);
-    if (++stage == kGemvStages) stage = 0;
-    // hand the K-slice sums to the reducing warps through a ring of buffers
-    if (red_wrapped && !mbar_wait(red_empty_bar(buf), red_phase ^ 1, abort_flag, p.status, 44)) return;
-    if (warp == 0) GEMV_TRACE(4, it + 1);
-    float* my_red = red + ((size_t)buf * warps + warp) * 256;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-      *reinterpret_cast<float4*>(my_red + (nt * 32 + lane) * 4) =
-          make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
-    __syncwarp();   // also orders this iteration's stage reads before the next iteration's copies into that stage
-    if (lane == 0) mbar_arrive(red_full_bar(buf));
-    if (++buf == kGemvRing) { buf = 0; red_wrapped = 1; red_phase ^= 1; }
   }
-  cp_async_wait<0>();
+
+  // the low-rank input comes from the companion kernel: wait for it only now
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int i = threadIdx.x; i < 16 * 64; i += kGemvWarps * 32) t_s[i] = __ldcg(p.t + i);
+  __syncthreads();   // all K-slice sums and the low-rank input are in shared memory
+
+  // ---- one thread per (pair, token tile, lane slot): add the K-slices in warp order, the low-rank term, round ----
+  const int active = p.nblk < p.warps * BPW ? (p.nblk + BPW - 1) / BPW : p.warps;   // warps that own at least one block
+  for (int item = threadIdx.x; item < npairs * TT * 32; item += kGemvWarps * 32) {
+    const int slot = item & 31, tt = (item >> 5) % TT, pr = (item >> 5) / TT;
+    float4 sum = sums[((0 * kGemvMaxPairs + pr) * TT + tt) * 32 + slot];
+    for (int wv = 1; wv < active; ++wv) {
+      const float4 v = sums[((wv * kGemvMaxPairs + pr) * TT + tt) * 32 + slot];
+      sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    const int sg = slot >> 2, st = slot & 3;
+    const int tok0 = tt * 8 + 2 * st;
+    const float base[2][2] = {{sum.x, sum.y}, {sum.z, sum.w}};   // [group of the pair][token]
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int grp = group0 + 2 * pr + half;
+      if (grp >= group1) continue;
+      const long long row = (long long)grp * 8 + sg;
+      float lora[2] = {0.f, 0.f};
+      for (int r = 0; r < p.rank; ++r) {
+        const float bs = __bfloat162float(__float2bfloat16_rn(p.scaling * __ldg(p.lora_b + row * p.rank + r)));
+        lora[0] = fmaf(t_s[tok0 * 64 + r], bs, lora[0]);
+        lora[1] = fmaf(t_s[(tok0 + 1) * 64 + r], bs, lora[1]);
+      }
+      if (tok0 < p.m) p.y[(long long)tok0 * p.w.n + row] = __float2bfloat16_rn(base[half][0] + lora[0]);
+      if (tok0 + 1 < p.m) p.y[(long long)(tok0 + 1) * p.w.n + row] = __float2bfloat16_rn(base[half][1] + lora[1]);
+    }
+  }
 }
 
-// y[tok, n] = bf16(sum over K-groups of partial + low-rank term).  One thread per output column: it keeps its row of
-// bf16(scaling * B) in registers and handles all tokens; T = bf16(sum over K-groups of its parts) sits in shared memory.
-constexpr int kGemvFinishThreads = 128;
-constexpr int kGemvMaxKGroups = 8;   // K up to 16384 columns
-template <int RP>   // rank rounded up to a multiple of 16
-__global__ void __launch_bounds__(kGemvFinishThreads) gemv_finish_kernel(const float* __restrict__ partial, int kgroups,
-                                                                         const float* __restrict__ t_partial,
-                                                                         const float* __restrict__ lora_b, float scaling,
-                                                                         int rank, int m, long long n,
-                                                                         __nv_bfloat16* __restrict__ y) {
-  __shared__ float t_s[16 * 64];
-  float tv[16 * 64 / kGemvFinishThreads];
+// T[tok][r] = bf16(sum_k x[tok][k] * bf16(A[r][k])) for tok < m, r < rank, as fp32 values in t [16][64] (zero elsewhere)
+// and, when t_out is given, as bf16 in t_out [m][64].  One CTA per adapter row.
+__global__ void __launch_bounds__(256) gemv_lowrank_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ a,
+                                                           int m, long long k, int rank, float* __restrict__ t,
+                                                           __nv_bfloat16* __restrict__ t_out) {
+  // the streaming kernel behind this one may start now; it waits for this grid only before it reads t
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ float red[8][16];
+  const int r = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float sums[16];
 #pragma unroll
-  for (int j = 0; j < 16 * 64 / kGemvFinishThreads; ++j) {   // all requested before any is used
-    const int i = threadIdx.x + j * kGemvFinishThreads;
-    tv[j] = 0.f;
-    if ((i & 63) < rank && (i >> 6) < m) {
+  for (int i = 0; i < 16; ++i) sums[i] = 0.f;
+  if (r < rank) {
+    for (long long c = threadIdx.x * 8LL; c < k; c += 256 * 8) {
+      const float4 a0 = __ldg(reinterpret_cast<const float4*>(a + r * k + c));
+      const float4 a1 = __ldg(reinterpret_cast<const float4*>(a + r * k + c + 4));
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      float ab[8];
 #pragma unroll
-      for (int kg = 0; kg < kGemvMaxKGroups; ++kg)
-        if (kg < kgroups) tv[j] += __ldg(t_partial + kg * 16 * 64 + i);
+      for (int j = 0; j < 8; ++j) ab[j] = __bfloat162float(__float2bfloat16_rn(av[j]));
+#pragma unroll
+      for (int tok = 0; tok < 16; ++tok) {
+        if (tok < m) {
+          const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (long long)tok * k + c));
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            sums[tok] = fmaf(bf16_lo(xw[j]), ab[2 * j], sums[tok]);
+            sums[tok] = fmaf(bf16_hi(xw[j]), ab[2 * j + 1], sums[tok]);
+          }
+        }
+      }
     }
   }
 #pragma unroll
-  for (int j = 0; j < 16 * 64 / kGemvFinishThreads; ++j)
-    t_s[threadIdx.x + j * kGemvFinishThreads] = __bfloat162float(__float2bfloat16_rn(tv[j]));
+  for (int tok = 0; tok < 16; ++tok) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sums[tok] += __shfl_xor_sync(0xffffffffu, sums[tok], o);
+    if (lane == 0) red[warp][tok] = sums[tok];
+  }
   __syncthreads();
-  const long long col = blockIdx.x * (long long)kGemvFinishThreads + threadIdx.x;
-  if (col >= n) return;
-  float bs[RP];
+  if (threadIdx.x < 16) {
+    const int tok = threadIdx.x;
+    float total = 0.f;
 #pragma unroll
-  for (int rk = 0; rk < RP; ++rk)
-    bs[rk] = rk < rank ? __bfloat162float(__float2bfloat16_rn(scaling * __ldg(lora_b + col * rank + rk))) : 0.f;
-  // eight tokens at a time; all loads of a batch are requested before any is used (kgroups and m only predicate them)
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    float part[8][kGemvMaxKGroups];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-      for (int kg = 0; kg < kGemvMaxKGroups; ++kg)
-        part[i][kg] = (half * 8 + i < m && kg < kgroups) ? __ldg(partial + ((long long)kg * 16 + half * 8 + i) * n + col) : 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int tok = half * 8 + i;
-      if (tok < m) {
-        float lora = 0.f;
-#pragma unroll
-        for (int rk = 0; rk < RP; ++rk) lora += t_s[tok * 64 + rk] * bs[rk];   // entries past the rank are zero
-        float base = part[i][0];
-#pragma unroll
-        for (int kg = 1; kg < kGemvMaxKGroups; ++kg) base += part[i][kg];
-        y[(long long)tok * n + col] = __float2bfloat16_rn(base + lora);
-      }
-    }
+    for (int wv = 0; wv < 8; ++wv) total += red[wv][tok];
+    const __nv_bfloat16 rounded = __float2bfloat16_rn((r < rank && tok < m) ? total : 0.f);
+    t[tok * 64 + r] = __bfloat162float(rounded);
+    if (t_out != nullptr && tok < m) t_out[(long long)tok * 64 + r] = rounded;
   }
 }
 
 namespace {
 
 struct GemvPlan {
-  int nblk, warps_needed, kgroups, warps;
+  int nblk, warps, bpw, passes, ctas, tt;
   size_t smem_bytes;
 };
 
-GemvPlan gemv_plan(long long k) {
+// K-slices: `warps` warps x `bpw` blocks per pass; chosen to waste as few warp-passes as possible.
+GemvPlan gemv_plan(long long n, long long k, int m) {
   GemvPlan g;
   g.nblk = (int)(k / 64);
-  g.warps_needed = (g.nblk + kGemvBlocksPerWarp - 1) / kGemvBlocksPerWarp;
-  g.kgroups = (g.warps_needed + kGemvMaxWarps - 1) / kGemvMaxWarps;
-  g.warps = (g.warps_needed + g.kgroups - 1) / g.kgroups;
-  // pair table, sum ring, low-rank sums, code2, barriers; the rest goes to the warps' private load stages
-  const size_t fixed = kGemvLutBytes + (size_t)kGemvRing * g.warps * 1024 + (size_t)g.warps * 512 + 1024 + 64;
-  g.smem_bytes = fixed + (size_t)kGemvStages * g.warps * kGemvStageBytes;
+  g.tt = m > 8 ? 2 : 1;
+  const int max_bpw = g.tt == 2 ? 2 : 4;   // X fragments in registers: 8 per block and token tile
+  long long best_cost = -1;
+  g.warps = kGemvWarps; g.bpw = 1; g.passes = g.nblk;
+  for (int bpw = 1; bpw <= max_bpw; ++bpw)
+    for (int warps = kGemvWarps; warps >= 8; --warps) {
+      const int per_pass = warps * bpw;
+      const int passes = (g.nblk + per_pass - 1) / per_pass;
+      // time ~ passes x bpw tile-rows per warp, plus a fixed cost per pass (X fragments) and idle warps
+      const long long cost = (long long)passes * bpw * 16 + passes * 4 + (kGemvWarps - warps);
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        g.warps = warps; g.bpw = bpw; g.passes = passes;
+      }
+    }
+  const long long groups = n / 8;
+  const int sms = sm_count();
+  const long long per_wave = (long long)sms * 2 * kGemvMaxPairs;   // row groups one wave of CTAs can hold in registers
+  const long long waves = (groups + per_wave - 1) / per_wave;
+  long long ctas = waves * sms;
+  if (ctas > groups) ctas = groups;
+  g.ctas = (int)ctas;
+  g.smem_bytes = (size_t)kGemvLutBytes + (size_t)kGemvWarps * kGemvMaxPairs * g.tt * 32 * sizeof(float4);
   return g;
 }
 
 }  // namespace
 
-// Whether the kernel can read this weight's nested absmax itself; otherwise the caller resolves it to fp32 first.
-// It copies the u8 codes as aligned 4-byte words, which needs K / 64 to be a multiple of 4 and an aligned array.
+// The kernel reads a nested absmax itself when the second-level block size is a power of two and rows hold whole
+// second-level... (a K-slice never crosses a row, and rows of k / 64 codes must not straddle a second-level block inside
+// a slice: guaranteed when block2 is a multiple of the slice or k / 64 divides block2).  Otherwise the caller resolves
+// the absmax to fp32 first.
 bool gemv_reads_nested(const WeightView& w) {
   if (w.block2_shift < 0) return false;
-  if ((w.k / 64) % 4 != 0) return false;
-  return (reinterpret_cast<uintptr_t>(w.absmax) & 3) == 0;
+  const long long nblk = w.k / 64;
+  return nblk > 0 && (w.block2 % nblk == 0 || nblk % w.block2 == 0) && (w.block2 % 4 == 0);
 }
 
-// Workspace layout: [kgroups][16][64] fp32 parts of T | [kgroups][16][n] fp32 partial outputs | n * k / 64 fp32 resolved
-// absmax (used by the caller for nested forms the kernel cannot read), each region starting on a 256-byte boundary.
-static size_t gemv_partial_offset(const GemvPlan& g) { return ((size_t)g.kgroups * 16 * 64 * sizeof(float) + 255) & ~size_t(255); }
-static size_t gemv_resolved_offset(const GemvPlan& g, long long n) {
-  return (gemv_partial_offset(g) + (size_t)g.kgroups * 16 * n * sizeof(float) + 255) & ~size_t(255);
-}
+// Workspace layout: [16][64] fp32 low-rank input | n * k / 64 fp32 resolved absmax (used by the caller for nested forms
+// the kernel cannot read), each region starting on a 256-byte boundary.
+static size_t gemv_resolved_offset() { return 16 * 64 * sizeof(float); }
 
 size_t gemv_workspace_bytes(long long n, long long k) {
-  const GemvPlan g = gemv_plan(k);
-  return gemv_resolved_offset(g, n) + (size_t)n * g.nblk * sizeof(float) + 256;
+  return gemv_resolved_offset() + (size_t)n * (k / 64) * sizeof(float) + 256;
 }
 
-// Where in the workspace a caller puts the resolved absmax.
-float* gemv_resolved_absmax_slot(void* workspace, long long n, long long k) {
-  return reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + gemv_resolved_offset(gemv_plan(k), n));
+float* gemv_resolved_absmax_slot(void* workspace, long long, long long) {
+  return reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + gemv_resolved_offset());
+}
+
+template <bool NESTED, int BPW, int TT>
+static int gemv_launch(const GemvParams& p, const GemvPlan& g, cudaStream_t s) {
+  static thread_local bool configured[64] = {};
+  int dev = 0;
+  MOLT_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    MOLT_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<NESTED, BPW, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(kGemvLutBytes + kGemvWarps * kGemvMaxPairs * TT * 32 * sizeof(float4))));
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)g.ctas);
+  cfg.blockDim = dim3(kGemvWarps * 32);
+  cfg.dynamicSmemBytes = g.smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemv_kernel<NESTED, BPW, TT>, p));
+  return launch_status("nf4_gemv_kernel");
 }
 
 int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_a, const float* lora_b, float scaling,
-                 int rank, __nv_bfloat16* y, int m, void* workspace, size_t workspace_bytes, cudaStream_t s) {
-  if (workspace_bytes < gemv_workspace_bytes(w.n, w.k))
+                 int rank, __nv_bfloat16* y, int m, __nv_bfloat16* t_out, void* workspace, size_t workspace_bytes,
+                 cudaStream_t s) {
+  if (workspace_bytes < 16 * 64 * sizeof(float))
     return fail(MOLT_E_VALUE, "molt_nf4_gemv: workspace too small (%zu < %zu bytes)", workspace_bytes,
-                gemv_workspace_bytes(w.n, w.k));
+                16 * 64 * sizeof(float));
   const bool nested = w.absmax_kind == MOLT_ABSMAX_NESTED;
   if (nested && !gemv_reads_nested(w))
     return fail(MOLT_E_RUNTIME, "molt_nf4_gemv: this nested absmax layout must be resolved to fp32 before the call");
   if ((reinterpret_cast<uintptr_t>(w.packed) & 15) != 0 || (reinterpret_cast<uintptr_t>(lora_a) & 15) != 0 ||
-      (reinterpret_cast<uintptr_t>(x) & 7) != 0)
-    return fail(MOLT_E_CAPABILITY, "molt_nf4_gemv: the packed weight and lora_a must start on 16-byte boundaries, x on 8");
-  const GemvPlan g = gemv_plan(w.k);
-  if (g.kgroups > kGemvMaxKGroups) return fail(MOLT_E_CAPABILITY, "molt_nf4_gemv: K is limited to %d columns", kGemvMaxKGroups * 2048);
-  if (g.smem_bytes > (size_t)kGemvSmemLimit) return fail(MOLT_E_CAPABILITY, "molt_nf4_gemv: no room for the load stages");
+      (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    return fail(MOLT_E_CAPABILITY, "molt_nf4_gemv: the packed weight, lora_a and x must start on 16-byte boundaries");
+  if (m < 1 || m > 16) return fail(MOLT_E_CAPABILITY, "molt_nf4_gemv: 1 to 16 tokens");
+  const GemvPlan g = gemv_plan(w.n, w.k, m);
   GemvParams p;
   p.w = w;
   p.x = x;
-  p.lora_a = lora_a;
+  p.lora_b = lora_b;
+  p.t = reinterpret_cast<const float*>(workspace);
+  p.y = y;
+  p.scaling = scaling;
   p.rank = rank;
   p.m = m;
   p.nblk = g.nblk;
-  p.kgroups = g.kgroups;
-  p.warps_per_cta = g.warps;
-  p.status = device_status_word();
-  if (p.status == nullptr) return fail(MOLT_E_RUNTIME, "molt_nf4_gemv: no device status word");
-  unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
-  p.t_partial = reinterpret_cast<float*>(ws);
-  p.partial = reinterpret_cast<float*>(ws + gemv_partial_offset(g));
-  p.trace = nullptr;
-  p.debug = 0;
-#ifdef MOLT_GEMV_TRACE
-  if (const char* dbg = getenv("MOLT_B200_DEBUG")) p.debug = atoi(dbg);
-  if (const char* tr = getenv("MOLT_B200_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 10));
-#endif
-
-  static thread_local bool configured[64][2] = {};
-  int dev = 0;
-  MOLT_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !configured[dev][nested ? 1 : 0]) {
-    if (nested) MOLT_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit));
-    else MOLT_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit));
-    configured[dev][nested ? 1 : 0] = true;
-  }
-  const int chunks = (int)(w.n / kGemvChunkRows);
-  int gx = sm_count() / p.kgroups;
-  if (gx < 1) gx = 1;
-  if (gx > chunks) gx = chunks;
-  if (gx * 8 < rank) return fail(MOLT_E_CAPABILITY, "molt_nf4_gemv: too few row chunks for this rank");
-  dim3 grid((unsigned)gx, (unsigned)p.kgroups);
-  const int threads = (p.warps_per_cta + 2) * 32;   // streaming warps + two reducing warps
-  if (nested) nf4_gemv_kernel<true><<<grid, threads, g.smem_bytes, s>>>(p);
-  else nf4_gemv_kernel<false><<<grid, threads, g.smem_bytes, s>>>(p);
-  if (int rc = launch_status("nf4_gemv_kernel")) return rc;
-  const unsigned fgrid = (unsigned)((w.n + kGemvFinishThreads - 1) / kGemvFinishThreads);
-  switch ((rank + 15) / 16) {
-    case 1: gemv_finish_kernel<16><<<fgrid, kGemvFinishThreads, 0, s>>>(p.partial, p.kgroups, p.t_partial, lora_b, scaling, rank, m, w.n, y); break;
-    case 2: gemv_finish_kernel<32><<<fgrid, kGemvFinishThreads, 0, s>>>(p.partial, p.kgroups, p.t_partial, lora_b, scaling, rank, m, w.n, y); break;
-    case 3: gemv_finish_kernel<48><<<fgrid, kGemvFinishThreads, 0, s>>>(p.partial, p.kgroups, p.t_partial, lora_b, scaling, rank, m, w.n, y); break;
-    default: gemv_finish_kernel<64><<<fgrid, kGemvFinishThreads, 0, s>>>(p.partial, p.kgroups, p.t_partial, lora_b, scaling, rank, m, w.n, y); break;
-  }
-  return launch_status("gemv_finish_kernel");
+  p.warps = g.warps;
+  p.passes = g.passes;
+  p.groups_total = (int)(w.n / 8);
+  p.ctas = g.ctas;
+  gemv_lowrank_kernel<<<64, 256, 0, s>>>(x, lora_a, m, w.k, rank, reinterpret_cast<float*>(workspace), t_out);
+  if (int rc = launch_status("gemv_lowrank_kernel")) return rc;
+#define MOLT_GEMV_CASE(NE, BP, T)                                            \
+  if (nested == NE && g.bpw == BP && g.tt == T) return gemv_launch<NE, BP, T>(p, g, s)
+  MOLT_GEMV_CASE(false, 1, 1); MOLT_GEMV_CASE(false, 2, 1); MOLT_GEMV_CASE(false, 3, 1); MOLT_GEMV_CASE(false, 4, 1);
+  MOLT_GEMV_CASE(false, 1, 2); MOLT_GEMV_CASE(false, 2, 2);
+  MOLT_GEMV_CASE(true, 1, 1); MOLT_GEMV_CASE(true, 2, 1); MOLT_GEMV_CASE(true, 3, 1); MOLT_GEMV_CASE(true, 4, 1);
+  MOLT_GEMV_CASE(true, 1, 2); MOLT_GEMV_CASE(true, 2, 2);
+#undef MOLT_GEMV_CASE
+  return fail(MOLT_E_RUNTIME, "molt_nf4_gemv: no kernel for this plan");
 }
 
 }  // namespace molt

@@ -297,6 +297,47 @@ __global__ void colsum_reduce_kernel(ReduceProblem first, ReduceProblem second, 
   pr.grad[idx] = accumulate ? pr.grad[idx] + sum : sum;
 }
 
+// Operands of the low-rank block of the standalone input-gradient op: one thread per 8 output elements of either list.
+__global__ void dx_lora_prep_kernel(const __nv_bfloat16* __restrict__ lora_grad, int rank, long long m,
+                                    const void* __restrict__ lora_a, int a_is_f32, float scaling, int rp, long long k,
+                                    __nv_bfloat16* __restrict__ low, __nv_bfloat16* __restrict__ a16) {
+  const long long items_low = m * 8;            // [m, 64] in groups of 8
+  const long long items_a = (long long)rp * k / 8;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  uint32_t out[4] = {0u, 0u, 0u, 0u};
+  if (i < items_low) {
+    const long long row = i >> 3;
+    const int c0 = (int)(i & 7) * 8;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = c0 + j < rank ? __bfloat162float(lora_grad[row * rank + c0 + j]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) out[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    *reinterpret_cast<uint4*>(low + row * 64 + c0) = make_uint4(out[0], out[1], out[2], out[3]);
+    return;
+  }
+  i -= items_low;
+  if (i < items_a) {
+    const long long e = i * 8;
+    const int r = (int)(e / k);
+    if (r < rank) {
+      float v[8];
+      if (a_is_f32) {
+        const float* a = reinterpret_cast<const float*>(lora_a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = scaling * __ldg(a + e + j);
+      } else {
+        const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(lora_a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = scaling * __bfloat162float(a[e + j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) out[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    }
+    *reinterpret_cast<uint4*>(a16 + e) = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
 // ---- host wrappers --------------------------------------------------------------------------------
 int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, long long n, long long k,
               __nv_bfloat16* a16, __nv_bfloat16* bs, __nv_bfloat16* bt, const WeightView* w, float* resolved,
@@ -311,6 +352,16 @@ int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, l
   lora_prep_kernel<<<(unsigned)((items + 255) / 256), 256, 0, s>>>(a, b, scaling, rank, rp, n, k, a16, bs, bt, view,
                                                                     absmax_blocks > 0 ? resolved : nullptr, absmax_blocks);
   return launch_status("lora_prep_kernel");
+}
+
+int dx_lora_prep(const __nv_bfloat16* lora_grad, int rank, long long m, const void* lora_a, int lora_a_dtype,
+                 float scaling, int rp, long long k, __nv_bfloat16* low, __nv_bfloat16* a16, cudaStream_t s) {
+  const long long items = m * 8 + (long long)rp * k / 8;   // k is a multiple of 64 on this path
+  if (items == 0) return MOLT_OK;
+  dx_lora_prep_kernel<<<(unsigned)((items + 255) / 256), 256, 0, s>>>(lora_grad, rank, m, lora_a,
+                                                                      lora_a_dtype == MOLT_DTYPE_F32 ? 1 : 0, scaling, rp, k,
+                                                                      low, a16);
+  return launch_status("dx_lora_prep_kernel");
 }
 
 int rowsum_mma(const __nv_bfloat16* in, const __nv_bfloat16* wt, int rp, long long m, long long cols,

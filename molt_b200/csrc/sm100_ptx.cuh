@@ -8,7 +8,7 @@
 
 namespace molt {
 
-constexpr int kStatusTimeout = 1;
+constexpr int kStatusTimeout = MOLT_E_TIMEOUT;   // code in the top byte of the device status word
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -34,15 +34,16 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
-// Bounded wait.  Returns false when the wait expired or another role already gave up.
+// Bounded wait: gives up after limit_cycles SM clock cycles.  Returns false when the wait expired or another role
+// of the CTA already gave up; the first to give up records (code, where, block) in the device status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int where) {
+                                          int where, long long limit_cycles) {
   if (mbar_try(bar, parity)) return true;
   const long long start = clock64();
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
-    if ((spin & 63u) == 63u && clock64() - start > 2000000000LL) {  // about one second
+    if ((spin & 63u) == 63u && clock64() - start > limit_cycles) {
       *abort_flag = 1;
       atomicCAS(status, 0, (kStatusTimeout << 24) | (where << 16) | (int)(blockIdx.x & 0xffff));
       return false;

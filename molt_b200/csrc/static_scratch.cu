@@ -57,6 +57,8 @@ extern "C" int molt_nf4_lora_fwd_static(const molt_nf4_desc* w, const void* x, c
                                         const float* lora_b, float scaling, int rank, void* y, int64_t m, int path,
                                         uintptr_t stream) {
   MOLT_REQUIRE(w != nullptr, MOLT_E_VALUE, "molt_nf4_lora_fwd_static: weight descriptor is NULL");
+  MOLT_REQUIRE(rank <= 64, MOLT_E_CAPABILITY, "molt_nf4_lora_fwd_static: LoRA rank %d exceeds the supported maximum of 64",
+               rank);
   // the smallest workspace the forward accepts (without the optional scratch of the tensor-core kernel's split schedule)
   const size_t need = workspace_bytes(MOLT_OP_LORA_FWD, m, w->n, w->k, rank, false);
   MOLT_REQUIRE(need != 0, MOLT_E_VALUE, "molt_nf4_lora_fwd_static: invalid sizes (m=%lld n=%lld k=%lld rank=%d)",

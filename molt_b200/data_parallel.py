@@ -62,8 +62,19 @@ class GradArena:
             end = begin
         return buckets
 
+    def rebind(self) -> None:
+        """Point every parameter's ``.grad`` at its arena slice again.  ``optimizer.zero_grad()`` with its default
+        ``set_to_none=True`` drops ``.grad`` while the kernels keep accumulating into the arena; without this the
+        optimiser would silently skip every adapter."""
+        for p, view in zip(self.params, self.views):
+            if p.grad is not view:
+                p.grad = view
+
     def zero(self) -> None:
+        """Clear the arena for the next step (use this, or ``zero_grad(set_to_none=False)``, between steps: the
+        backward kernels ADD into the slices)."""
         self.flat.zero_()
+        self.rebind()
 
     def bucket_of_param(self, index: int) -> int:
         off = self.offsets[index]
@@ -88,6 +99,7 @@ class GradArena:
 
     def all_reduce(self, group=None, average: bool = False) -> None:
         """Sum (or average) the whole arena over the group, bucket by bucket, then rejoin the main stream."""
+        self.rebind()
         if not dist.is_initialized() or dist.get_world_size(group) == 1:
             return
         for b in range(len(self.buckets)):

@@ -32,8 +32,7 @@ def resolved_nf4_scales(quant_state: Any) -> torch.Tensor:
         scales = torch.empty(absmax.numel(), dtype=torch.float32, device=absmax.device)
         from molt_b200.methods.quant_state import describe
 
-        # only the absmax fields of the descriptor are read here; the packed pointer is a placeholder
-        desc = describe(absmax, quant_state)
+        desc = describe(None, quant_state)   # only the absmax fields of the descriptor are read here
         with torch.cuda.device(absmax.device):
             _native.check(_native.library().molt_nf4_resolve_absmax(
                 ctypes.byref(desc), scales.data_ptr(), _native.stream_handle(absmax.device)))

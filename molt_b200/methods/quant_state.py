@@ -110,37 +110,74 @@ def quantize_nf4(weight: torch.Tensor, blocksize: int = 64, compress_statistics:
     return packed, state
 
 
-def describe(packed: torch.Tensor, quant_state: Any) -> _native.NF4Desc:
+def _require_buffer(tensor: Any, what: str, dtype: torch.dtype, min_numel: int, device: torch.device) -> None:
+    """The C side only sees raw pointers: every buffer must be what the declared shape says it is."""
+    if not isinstance(tensor, torch.Tensor):
+        raise ValueError(f"{what} must be a tensor")
+    if tensor.dtype != dtype:
+        raise CapabilityError(f"{what} must be {dtype}, got {tensor.dtype}")
+    if tensor.device != device:
+        raise ValueError(f"{what} must be on the same device as the packed weight ({tensor.device} != {device})")
+    if not tensor.is_contiguous():
+        raise ValueError(f"{what} must be contiguous")
+    if tensor.numel() < min_numel:
+        raise ValueError(f"{what} holds {tensor.numel()} elements but the declared weight shape needs {min_numel}")
+
+
+def describe(packed: Optional[torch.Tensor], quant_state: Any) -> _native.NF4Desc:
     """Build the C descriptor for a ``(packed, quant_state)`` pair.  The returned struct borrows the tensors'
-    memory; callers keep the tensors alive for the duration of the native call."""
+    memory; callers keep the tensors alive for the duration of the native call.
+
+    Every buffer is checked against the declared weight shape (dtype, device, contiguity, element count) because
+    the native side cannot: a state whose shape disagrees with its tensors would make the kernels read out of
+    bounds.  ``packed=None`` builds a descriptor for calls that read only the absmax fields
+    (``resolved_nf4_scales``); its packed pointer aliases the absmax and must not be dereferenced."""
     if getattr(quant_state, "quant_type", None) != "nf4":
         raise CapabilityError("the packed NF4 kernels require NF4 quantization")
     shape = tuple(int(v) for v in quant_state.shape)
-    if len(shape) != 2:
-        raise ValueError("the NF4 weight must be a matrix")
+    if len(shape) != 2 or shape[0] <= 0 or shape[1] <= 0:
+        raise ValueError("the NF4 weight must be a non-empty matrix")
     order = getattr(quant_state, "nibble_order", "high-first")
     if order not in NIBBLE_ORDERS:
         raise ValueError(f"unknown nibble order {order!r}")
+    blocksize = int(quant_state.blocksize)
+    if blocksize < 16 or blocksize % 2:
+        raise ValueError(f"invalid NF4 block size {blocksize}")
     absmax = quant_state.absmax
-    if absmax.device != packed.device:
-        raise ValueError("absmax and packed weight must be on the same device")
+    if not isinstance(absmax, torch.Tensor):
+        raise ValueError("absmax must be a tensor")
+    device = absmax.device if packed is None else packed.device
+    blocks = -(-(shape[0] * shape[1]) // blocksize)
+    if packed is not None:
+        _require_buffer(packed, "the packed weight", torch.uint8, -(-(shape[0] * shape[1]) // 2), device)
     nested = bool(getattr(quant_state, "nested", False))
     code = quant_state.code
     codebook = code.detach().float().cpu().tolist() if isinstance(code, torch.Tensor) else list(code)
     if len(codebook) != 16:
         raise CapabilityError("the NF4 codebook must have 16 entries")
+    packed_arg = absmax if packed is None else packed
     if nested:
         state2 = quant_state.state2
+        if state2 is None:
+            raise ValueError("a nested quant state needs state2")
+        block2 = int(state2.blocksize)
+        if block2 <= 0:
+            raise ValueError(f"invalid nested block size {block2}")
         if absmax.dtype != torch.uint8:
             raise CapabilityError("nested absmax must be stored as uint8 codes")
+        _require_buffer(absmax, "the nested absmax codes", torch.uint8, blocks, device)
         if state2.absmax.dtype != torch.float32 or state2.code.dtype != torch.float32:
             raise CapabilityError("the nested absmax scale and its 256-entry table must be float32")
+        _require_buffer(state2.absmax, "the second-level absmax", torch.float32, -(-blocks // block2), device)
+        _require_buffer(state2.code, "the second-level table", torch.float32, 256, device)
+        if state2.code.numel() != 256:
+            raise ValueError("the second-level table must have exactly 256 entries")
         offset = quant_state.offset
         offset_value = float(offset.item()) if isinstance(offset, torch.Tensor) else float(offset)
-        return _native.make_desc(packed, absmax, shape[0], shape[1], int(quant_state.blocksize), NIBBLE_ORDERS[order],
+        return _native.make_desc(packed_arg, absmax, shape[0], shape[1], blocksize, NIBBLE_ORDERS[order],
                                  codebook, absmax2=state2.absmax, code2=state2.code,
-                                 offset=offset_value, block2=int(state2.blocksize))
+                                 offset=offset_value, block2=block2)
     if absmax.dtype != torch.float32:
         raise CapabilityError("absmax must be float32 (or uint8 codes with a nested state)")
-    return _native.make_desc(packed, absmax, shape[0], shape[1], int(quant_state.blocksize), NIBBLE_ORDERS[order],
-                             codebook)
+    _require_buffer(absmax, "absmax", torch.float32, blocks, device)
+    return _native.make_desc(packed_arg, absmax, shape[0], shape[1], blocksize, NIBBLE_ORDERS[order], codebook)

@@ -99,18 +99,6 @@ def test_dimension_tails_use_the_general_kernels(native_library):
         run_forward(case, _native.PATH_TCGEN05)
 
 
-def test_single_cta_variant_still_matches(native_library, monkeypatch):
-    """The single-CTA tcgen05 kernel (selectable variant) against the oracle and against the default pair kernel."""
-    case = make_case(512, 320, 200, 16, seed=31)
-    y_pair, _ = run_forward(case, PATHS["tcgen05"])
-    monkeypatch.setenv("MOLT_B200_GEMM_VARIANT", "1")
-    errors = _check_all(case, PATHS["tcgen05"])
-    y_single, _ = run_forward(case, PATHS["tcgen05"])
-    monkeypatch.delenv("MOLT_B200_GEMM_VARIANT")
-    assert max(errors.values()) <= TOL
-    assert oracle.rel_frobenius(y_single, y_pair.float()) < 2e-3
-
-
 @pytest.mark.parametrize("n,k,m", [(64, 64, 256), (64, 128, 300), (128, 64, 40), (192, 64, 513)])
 def test_short_contractions(native_library, n, k, m):
     """One or two contraction blocks per tile: shorter than the pipeline's lead of codes over activations."""
@@ -119,20 +107,18 @@ def test_short_contractions(native_library, n, k, m):
 
 
 @pytest.mark.parametrize("n,k", [(2560, 1024), (1024, 2560)])
-def test_split_last_wave(native_library, monkeypatch, n, k):
+def test_split_last_wave(native_library, n, k):
     """80 output tiles on 74 CTA pairs (forward for the first shape, backward for the second): the six tiles of the
     last wave are cut along the contraction, leave the GEMM as fp32 partial tiles and are summed by the fix-up kernel
     (forced here: for tiles this short the library would keep the plain schedule).  Results must match the oracle
     and, up to the order of fp32 additions, the plain schedule."""
-    monkeypatch.setenv("MOLT_B200_FORCE_SPLIT", "1")
     case = make_case(n, k, 2048, 16, seed=n + k, nested=True, order="high-first")
-    _check_all(case, PATHS["tcgen05"])
-    y_split, _ = run_forward(case, PATHS["tcgen05"])
-    dx_split, da_split, db_split = run_backward(case, PATHS["tcgen05"])
-    monkeypatch.delenv("MOLT_B200_FORCE_SPLIT")
-    monkeypatch.setenv("MOLT_B200_NO_SPLIT", "1")
-    y_plain, _ = run_forward(case, PATHS["tcgen05"])
-    dx_plain, da_plain, db_plain = run_backward(case, PATHS["tcgen05"])
+    split, plain = PATHS["tcgen05"] | _native.PATH_FORCE_SPLIT, PATHS["tcgen05"] | _native.PATH_NO_SPLIT
+    _check_all(case, split)
+    y_split, _ = run_forward(case, split)
+    dx_split, da_split, db_split = run_backward(case, split)
+    y_plain, _ = run_forward(case, plain)
+    dx_plain, da_plain, db_plain = run_backward(case, plain)
     assert oracle.rel_frobenius(y_split, y_plain.float()) < 1e-3
     assert oracle.rel_frobenius(dx_split, dx_plain.float()) < 1e-3
     assert not (torch.equal(y_split, y_plain) and torch.equal(dx_split, dx_plain))   # the split schedule really ran
@@ -155,7 +141,7 @@ def test_tcgen05_forward_equals_general_forward_closely(native_library):
     assert oracle.rel_frobenius(y_fast, y_slow.float()) < 4e-3
 
 
-def test_forward_linearity_at_full_size(native_library, monkeypatch):
+def test_forward_linearity_at_full_size(native_library):
     """Size-independent property at BASELINE config 2's weight (14336 x 4096, nested absmax), M = 4096:
     rows are independent, so the forward of a row subset equals the subset of the forward -- bit for bit on the plain
     tile schedule, and up to the order of two fp32 additions where the tiles of the last wave are split."""
@@ -171,9 +157,9 @@ def test_forward_linearity_at_full_size(native_library, monkeypatch):
     assert_clean_status()
     differing = (full[1024:1536] != part).float().mean().item()
     assert differing < 0.02 and oracle.rel_frobenius(full[1024:1536], part.float()) < 1e-3
-    monkeypatch.setenv("MOLT_B200_NO_SPLIT", "1")
-    full_plain, _ = linear_forward(desc, x, a, b, 2.0, False, _native.PATH_TCGEN05)
-    part_plain, _ = linear_forward(desc, x[1024:1536].contiguous(), a, b, 2.0, False, _native.PATH_TCGEN05)
+    plain = _native.PATH_TCGEN05 | _native.PATH_NO_SPLIT
+    full_plain, _ = linear_forward(desc, x, a, b, 2.0, False, plain)
+    part_plain, _ = linear_forward(desc, x[1024:1536].contiguous(), a, b, 2.0, False, plain)
     assert_clean_status()
     assert torch.equal(full_plain[1024:1536], part_plain)
     # and a 64-row slice against the oracle
@@ -193,19 +179,32 @@ def test_gemv_path(native_library, m, n, k, nested):
     assert torch.equal(y, y_again)  # deterministic, tickets left clean
 
 
-def test_gemv_widest_rows_and_the_fallback_beyond(native_library):
-    """K = 16384 is the widest row the streaming kernel takes (8 K-groups); one block more and AUTO hands a 4-token
-    call to the tensor-core kernels instead.  Both must match the oracle."""
+def test_gemv_wide_and_ragged_rows(native_library):
+    """Rows wider than one pass of the streaming kernel's K-slices (K = 16384: 256 absmax blocks) and a block count that
+    no slice layout divides evenly (K = 16448: 257 blocks); both must match the oracle."""
     case = make_case(128, 16384, 4, 16, seed=77, nested=True, order="high-first")
     y, _ = run_forward(case, _native.PATH_GEMV)
     y_ref = oracle.nf4_lora_forward(case.x, case.weight, case.a, case.b, case.scaling)
     assert oracle.rel_frobenius(y, y_ref) <= TOL
-    wide = make_case(128, 16448, 4, 16, seed=78)
-    y_wide, _ = run_forward(wide, _native.PATH_AUTO)
+    wide = make_case(128, 16448, 11, 16, seed=78)
+    y_wide, _ = run_forward(wide, _native.PATH_GEMV)
     y_wide_ref = oracle.nf4_lora_forward(wide.x, wide.weight, wide.a, wide.b, wide.scaling)
     assert oracle.rel_frobenius(y_wide, y_wide_ref) <= TOL
-    with pytest.raises(Exception):
-        run_forward(wide, _native.PATH_GEMV)
+    assert torch.equal(run_forward(wide, _native.PATH_AUTO)[0], y_wide)
+    assert_clean_status()
+
+
+@pytest.mark.parametrize("n,k,m,rank", [(64, 64, 1, 1), (192, 1536, 9, 64), (8960, 1536, 16, 16), (1536, 8960, 5, 16),
+                                        (24 * 8 * 148, 128, 7, 8)])
+def test_gemv_plans(native_library, n, k, m, rank):
+    """Shapes that exercise the streaming kernel's plans: a single row group per CTA, rank 64, 24 and 140 absmax blocks
+    per row (slices of 2 and 3 blocks, several passes), more row groups than one wave of CTAs holds, and t_out."""
+    case = make_case(n, k, m, rank, seed=n + k + m, nested=(k % 256 == 0), order="high-first")
+    y, t = run_forward(case, _native.PATH_GEMV, keep_t=True)
+    y_ref = oracle.nf4_lora_forward(case.x, case.weight, case.a, case.b, case.scaling)
+    assert oracle.rel_frobenius(y, y_ref) <= TOL
+    t_ref = case.x @ case.a.bfloat16().float().t()
+    assert oracle.rel_frobenius(t[:, :rank], t_ref) <= TOL and torch.count_nonzero(t[:, rank:]) == 0
     assert_clean_status()
 
 

@@ -47,3 +47,32 @@ def test_ce_softmax_grad_kernel(native_library, rows, vocab):
     torch.testing.assert_close(loss.cpu(), ref_loss.detach(), rtol=1e-4, atol=1e-4)
     got = dev_logits.float().cpu()
     assert (got - ref_logits.grad).abs().max() <= 2e-3 * 0.25 + 1e-6   # bf16 rounding of values in [-0.25, 0.25]
+
+
+def test_ce_softmax_grad_ignores_out_of_range_labels(native_library):
+    """Labels outside [0, vocab) -- the usual ignore index -100, or an id past the vocabulary -- give zero loss and a
+    plain softmax gradient with no one-hot term (reference kernels/frozen_linear_cross_entropy.py:42-43, 63, 94-95,
+    133); the row before the first must not be touched."""
+    from molt_b200 import _native
+
+    rows, vocab = 6, 1000
+    gen = torch.Generator().manual_seed(9)
+    logits = (torch.randn(rows + 1, vocab, generator=gen) * 3).bfloat16()
+    targets = torch.tensor([-100, 3, vocab, 999, -1, vocab + 7])
+    buffer = logits.cuda()
+    dev_logits = buffer[1:]                      # row 0 of the buffer sits in front of the kernel's first row
+    loss = torch.full((rows,), 7.0, device="cuda")
+    _native.check(_native.library().molt_ce_softmax_grad(dev_logits.data_ptr(), targets.cuda().data_ptr(), loss.data_ptr(),
+                                                         rows, vocab, 0.5, _native.stream_handle()))
+    torch.cuda.synchronize()
+    assert torch.equal(buffer[0].cpu(), logits[0])
+    ref = logits[1:].float()
+    valid = (targets >= 0) & (targets < vocab)
+    probs = torch.softmax(ref, dim=-1) * 0.5
+    onehot = torch.zeros_like(probs)
+    onehot[valid, targets[valid]] = 0.5
+    want_grad = probs - onehot
+    want_loss = torch.where(valid, torch.logsumexp(ref, -1) - ref[torch.arange(rows), targets.clamp(0, vocab - 1)],
+                            torch.zeros(rows))
+    torch.testing.assert_close(loss.cpu(), want_loss, rtol=1e-4, atol=1e-4)
+    assert (dev_logits.float().cpu() - want_grad).abs().max() <= 2e-3 * 0.5 + 1e-6

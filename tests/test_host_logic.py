@@ -184,3 +184,59 @@ def test_grad_arena_layout_and_buckets():
     assert arena.flat.sum() == 2.0 * 256 * 16
     arena.zero()
     assert arena.flat.abs().sum() == 0
+
+
+def test_describe_checks_every_buffer_against_the_declared_shape():
+    """The native side sees raw pointers only, so the descriptor builder refuses tensors that do not cover the
+    declared weight: wrong dtype, sliced (non-contiguous) or short buffers, a second-level table of the wrong size."""
+    from molt_b200.methods.quant_state import NestedState, describe
+
+    n, k = 8, 128
+    packed = torch.zeros(n * k // 2, 1, dtype=torch.uint8)
+    good = QuantState(absmax=torch.ones(n * k // 64), shape=(n, k))
+    desc = describe(packed, good)
+    assert (desc.n, desc.k, desc.blocksize) == (n, k, 64)
+    with pytest.raises(ValueError, match="declared weight shape"):
+        describe(packed[:-1], good)                                   # packed too short
+    with pytest.raises(CapabilityError):
+        describe(packed.float(), good)                                # packed not uint8
+    with pytest.raises(ValueError, match="declared weight shape"):
+        describe(packed, QuantState(absmax=torch.ones(n * k // 64 - 1), shape=(n, k)))
+    with pytest.raises(ValueError, match="contiguous"):
+        describe(packed, QuantState(absmax=torch.ones(2 * n * k // 64)[::2], shape=(n, k)))
+    with pytest.raises(ValueError, match="non-empty matrix"):
+        describe(packed, QuantState(absmax=torch.ones(16), shape=(n, k, 1)))
+    codes = torch.zeros(n * k // 64, dtype=torch.uint8)
+    table = torch.linspace(-1, 1, 256)
+    nested = QuantState(absmax=codes, shape=(n, k), nested=True, state2=NestedState(torch.ones(1), table, 256), offset=0.5)
+    assert describe(packed, nested).absmax_kind == 1
+    nested.state2 = NestedState(torch.ones(1), table[:255], 256)
+    with pytest.raises(ValueError):
+        describe(packed, nested)                                      # second-level table too short
+    nested.state2 = NestedState(torch.ones(0), table, 256)
+    with pytest.raises(ValueError, match="declared weight shape"):
+        describe(packed, nested)                                      # second-level absmax too short
+    nested.state2 = None
+    with pytest.raises(ValueError, match="state2"):
+        describe(packed, nested)
+    # absmax-only descriptor (what resolved_nf4_scales builds): no packed tensor to check
+    assert describe(None, good).n == n
+
+
+def test_grad_arena_survives_zero_grad_set_to_none():
+    """optimizer.zero_grad() drops .grad by default; the arena rebinds its slices so the optimiser still sees the
+    gradients the kernels accumulate there."""
+    a = torch.nn.Parameter(torch.zeros(4, 8))
+    b = torch.nn.Parameter(torch.zeros(8, 4))
+    arena = GradArena([a, b])
+    opt = torch.optim.SGD([a, b], lr=1.0)
+    opt.zero_grad()                       # set_to_none=True
+    assert a.grad is None
+    arena.zero()
+    assert a.grad is arena.views[0] and b.grad is arena.views[1]
+    arena.flat.fill_(1.0)
+    opt.step()
+    assert torch.all(a == -1.0) and torch.all(b == -1.0)
+    opt.zero_grad()
+    arena.all_reduce()                    # single process: no collective, but the slices are bound again
+    assert a.grad is arena.views[0]
