@@ -8,7 +8,9 @@ One "step" is one forward + backward of a frozen NF4 linear with its LoRA adapte
 Workload (BASELINE config 2's weight, at the M the targets are quoted for): W [14336, 4096] ~ N(0, 0.02),
 NF4 blocksize 64 with the absmax double-quantised to 8 bit in blocks of 256, LoRA r=16 alpha=32,
 M = 4096 tokens per GPU, X and dY ~ N(0, 1) in bf16, seeded synthetic data.  With N > 1 GPUs the token batch is
-sharded (4096 tokens per GPU, weak scaling) and the LoRA gradients are all-reduced over NCCL every step.
+sharded (4096 tokens per GPU, weak scaling) and the LoRA gradients are all-reduced over NCCL every step, on a side
+stream that overlaps the next step.  The same line also carries, at every N, the second half of the metric: training
+targets per second of a full QLoRA step at BASELINE config 4's shapes (``extra.qlora_step_c4``).
 Prints exactly one JSON line on rank 0.
 """
 from __future__ import annotations
@@ -157,23 +159,45 @@ def time_cpu_reference(sample_rows: int, steps: int, warmup: int, q=None, scales
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     seconds = sum(times) / len(times)
+    what = "the full workload" if sample_rows == M_PER_GPU else f"{sample_rows} of {M_PER_GPU} token rows per step"
     return {"value": linear_flops(sample_rows) / seconds / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-            "sample": f"{sample_rows} of {M_PER_GPU} token rows per step, full weight, fp32, torch {torch.__version__} "
+            "sample": f"{what}: {sample_rows} token rows, full weight, fp32, torch {torch.__version__} "
                       f"on {cores} host threads; {steps} timed steps",
             "ms_per_step": seconds * 1e3}
+
+
+def time_cpu_config1(steps: int = 10, warmup: int = 3):
+    """BASELINE config 1 on the host cores through the oracle's statement of the reference's eager path
+    (NF4Tensor.quantize once, untimed; then dequantise + forward + backward, which dequantises again)."""
+    from oracle import molt_oracle as oracle
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n, k, m, r = 4864, 896, 512, 16
+    w, a, b, x, dy = oracle.seeded_linear_case(n, k, m, r, seed=1337)
+    q = oracle.nf4_quantize(w, 64)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        oracle.nf4_lora_fwd_bwd(q, x, dy, a, b, 2.0)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    seconds = sum(times) / len(times)
+    return {"workload": "BASELINE config 1: W[4864,896] NF4 bs64 fp32 absmax, r=16, M=512, fp32 on CPU",
+            "ms_per_step": seconds * 1e3, "gflops": linear_flops(m, n, k, r) / seconds / 1e9, "cores": cores,
+            "kind": "port"}
 
 
 def run_reference_arm(args) -> int:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    sample_rows = 1024
-    base = time_cpu_reference(sample_rows, max(1, args.steps), max(1, args.warmup))
+    base = time_cpu_reference(M_PER_GPU, max(1, args.steps), max(1, min(args.warmup, 2)))
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample_rows_per_step": sample_rows},
+        "config": {"workload": WORKLOAD, "tokens_per_gpu": M_PER_GPU, "n": N_OUT, "k": K_IN, "rank": RANK},
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -264,21 +288,48 @@ def run_ours(args) -> int:
     ws = torch.empty(ws_bytes, device=device, dtype=torch.uint8)
     stream = _native.stream_handle(device)
 
+    # Two gradient buffers: the all-reduce of step i runs on a side stream while step i + 1 computes into the other one.
+    grad_sets = [(grads, da, db)]
+    if world > 1:
+        more = torch.zeros_like(grads)
+        grad_sets.append((more, more[: RANK * K_IN].view(RANK, K_IN), more[RANK * K_IN:].view(N_OUT, RANK)))
+    comm_stream = torch.cuda.Stream(device=device) if world > 1 else None
+    reduced = [torch.cuda.Event() for _ in grad_sets]
+    main = torch.cuda.current_stream(device)
+    counter = [0]
+
     def step_device():
+        flat, ga, gb = grad_sets[counter[0] % len(grad_sets)]
+        slot = counter[0] % len(grad_sets)
+        counter[0] += 1
+        if world > 1:
+            main.wait_event(reduced[slot])          # the collective that last read this buffer is done
         _native.check(lib.molt_nf4_lora_fwd(ctypes.byref(desc), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
                                             SCALING, RANK, y.data_ptr(), m, t_buf.data_ptr(), ws.data_ptr(), ws_bytes,
                                             _native.PATH_AUTO, stream))
         _native.check(lib.molt_nf4_lora_bwd(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), lora_a.data_ptr(),
-                                            lora_b.data_ptr(), SCALING, RANK, dx.data_ptr(), da.data_ptr(),
-                                            db.data_ptr(), m, t_buf.data_ptr(), 0, ws.data_ptr(), ws_bytes,
+                                            lora_b.data_ptr(), SCALING, RANK, dx.data_ptr(), ga.data_ptr(),
+                                            gb.data_ptr(), m, t_buf.data_ptr(), 0, ws.data_ptr(), ws_bytes,
                                             _native.PATH_AUTO, stream))
         if world > 1:
-            dist.all_reduce(grads, op=dist.ReduceOp.SUM)
+            comm_stream.wait_stream(main)
+            with torch.cuda.stream(comm_stream):
+                dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+                reduced[slot].record(comm_stream)
+
+    def drain():
+        if world > 1:
+            main.wait_stream(comm_stream)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def check_status(where):
+        status = _native.read_status(device)
+        if status:
+            raise SystemExit(f"a bounded device wait expired during {where} (status 0x{status:08x})")
 
     if args.profile:
         return profile_case(args.profile, lib, device, desc, packed, state, lora_a, lora_b, x, dy, y, dx, ws, ws_bytes)
@@ -286,6 +337,7 @@ def run_ours(args) -> int:
     # ---- timed region: device-resident inputs -------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
         step_device()
+    drain()
     barrier()
     launches_before = lib.molt_launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -294,6 +346,7 @@ def run_ours(args) -> int:
         start.record()
         for _ in range(args.steps):
             step_device()
+        drain()
         stop.record()
         barrier()
     elapsed_ms = torch.tensor([start.elapsed_time(stop)], device=device)
@@ -301,12 +354,32 @@ def run_ours(args) -> int:
         dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
     elapsed_ms = float(elapsed_ms.item())
     launches = int(lib.molt_launch_count() - launches_before)
-    status = _native.read_status(device)
-    if status:
-        raise SystemExit(f"a bounded device wait expired during the timed region (status 0x{status:08x})")
+    check_status("the timed region")
     clocks = sampler.summary()
     ms_per_step = elapsed_ms / args.steps
     value = world * linear_flops(m) / (ms_per_step * 1e-3) / 1e12
+
+    # ---- the same step for about 1.5 s without a pause: what the chip sustains under its power cap ----------
+    sustained_steps = max(args.steps, int(1500.0 / ms_per_step))
+    with ClockSampler(local_rank) as sustained_sampler:
+        barrier()
+        start.record()
+        for _ in range(sustained_steps):
+            step_device()
+        drain()
+        stop.record()
+        barrier()
+    sustained_ms = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(sustained_ms, op=dist.ReduceOp.MAX)
+    sustained_ms = float(sustained_ms.item())
+    check_status("the sustained run")
+    sustained_value = world * linear_flops(m) * sustained_steps / (sustained_ms * 1e-3) / 1e12
+    sustained = {"steps": sustained_steps, "seconds": sustained_ms * 1e-3, "value": sustained_value, "unit": "TFLOP/s",
+                 "ms_per_step": sustained_ms / sustained_steps,
+                 "frac_of_bf16_burst_peak": sustained_value / world / peaks["bf16_tflops"],
+                 "frac_of_bf16_sustained_peak": sustained_value / world / peaks["bf16_tflops_sustained"],
+                 "clocks": sustained_sampler.summary()}
 
     # ---- end to end through the Python API, host buffers, copies inside the timed region -------------
     x_host = x.cpu().pin_memory()
@@ -359,20 +432,40 @@ def run_ours(args) -> int:
     e2e_ms = torch.tensor([start.elapsed_time(stop) / e2e_steps], device=device)
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    check_status("the end-to-end run")
+    # what bounds it: the same host-to-device copies alone, all ranks at once (they share the host's memory and PCIe fabric)
+    h2d_bytes = x_host.numel() * 2 + dy_host.numel() * 2
+    barrier()
+    start.record()
+    for i in range(e2e_steps):
+        x_dev[i & 1].copy_(x_host, non_blocking=True)
+        dy_dev[i & 1].copy_(dy_host, non_blocking=True)
+    stop.record()
+    barrier()
+    copy_ms = torch.tensor([start.elapsed_time(stop) / e2e_steps], device=device)
+    if world > 1:
+        dist.all_reduce(copy_ms, op=dist.ReduceOp.MAX)
+    copy_ms = float(copy_ms.item())
     e2e_value = world * linear_flops(m) / (float(e2e_ms.item()) * 1e-3) / 1e12
     e2e = {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": float(e2e_ms.item()),
-           "h2d_bytes_per_step": x_host.numel() * 2 + dy_host.numel() * 2, "d2h_bytes_per_step": grads_host.numel() * 4,
-           "pipelining": "inputs of step i+1 are copied on a second stream while step i computes"}
+           "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": grads_host.numel() * 4,
+           "pipelining": "inputs of step i+1 are copied on a second stream while step i computes",
+           "h2d_copies_alone_ms_per_step": copy_ms, "h2d_gbs_per_gpu_alone": h2d_bytes / copy_ms / 1e6,
+           "bound": ("host-to-device copies: alone, with all ranks copying at once, they take "
+                     f"{copy_ms:.2f} ms per step against {ms_per_step:.2f} ms of kernels"
+                     if copy_ms > ms_per_step else "kernels")}
+    del x_dev, dy_dev, x_host, dy_host
 
     # ---- roofline of the dominant kernel: the tcgen05 GEMM, timed alone with CUDA events ---------------
     plain_state = QuantState(absmax=resolved_nf4_scales(state), shape=(N_OUT, K_IN), nibble_order=state.nibble_order)
     plain_desc = weight_desc(packed, plain_state)
 
-    def gemm_only():  # exactly one launch of nf4_gemm_sm100_kernel<backward>: dx = dy . deq(W)
+    def gemm_only():  # exactly one launch of the backward GEMM (+ its fix-up): dx = dy . deq(W)
         _native.check(lib.molt_nf4_dx(ctypes.byref(plain_desc), dy.data_ptr(), None, None, 0, 0.0, 0, dx.data_ptr(), m,
                                       ws.data_ptr(), ws_bytes, _native.PATH_TCGEN05, stream))
 
     gemm_ms = event_time_ms(gemm_only, iters=max(5, args.steps), warmup=3)
+    check_status("the roofline run")
     achieved = 2.0 * m * N_OUT * K_IN / (gemm_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": "nf4_gemm_sm100_pair_kernel<backward> (dX = dY . deq(W), M=4096)",
                 "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
@@ -385,16 +478,40 @@ def run_ours(args) -> int:
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens_per_gpu": m, "n": N_OUT, "k": K_IN, "rank": RANK,
-                   "parallelism": f"dp{world}", "l2": "per-step working set (X, dY, Y, dX = 300 MB) exceeds the 126 MB L2"},
+                   "parallelism": f"dp{world}", "l2": "per-step working set (X, dY, Y, dX = 300 MB) exceeds the 126 MB L2",
+                   "allreduce": "LoRA gradients (1.18 MB) all-reduced every step on a side stream, overlapping the next step"},
         "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
+        "frac_of_bf16_sustained_peak": value / world / peaks["bf16_tflops_sustained"],
+        "sustained": sustained,
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
     }
+    del x, dy, y, dx, ws
 
-    if rank == 0 and not args.no_extras:
-        line["extra"] = extras(lib, device, desc, packed, state, lora_a, lora_b, peaks)
+    extra = {}
+    if rank == 0 and world == 1 and not args.no_extras:
+        extra = extras(lib, device, desc, packed, state, lora_a, lora_b, peaks)
+        check_status("the secondary measurements")
+    if not args.no_extras:
+        # the metric's second half, at every N: a full QLoRA step at BASELINE config 4's shapes
+        torch.cuda.empty_cache()
+        from molt_b200.qlora_step import QWEN25_1P5B
+
+        step_line = measure_step(QWEN25_1P5B, "step4", steps=max(3, min(args.steps, 8)), warmup=3, layers=None,
+                                 use_graph=True, world=world, rank=rank, local_rank=local_rank, device=device)
+        extra["qlora_step_c4"] = {
+            "targets_per_s": step_line["value"], "ms_per_step": step_line["ms_per_step"], "n_gpus": world,
+            "hot_path_tflops_per_gpu": step_line["hot_path_tflops_per_gpu"],
+            "hot_path_frac_of_bf16_peak": step_line["hot_path_frac_of_bf16_peak"],
+            "lora_allreduce_bytes": step_line["config"]["lora_parameters"] * 4, "loss": step_line["loss"],
+            "gpu_launches": step_line["gpu_launches"], "workload": step_line["config"]["workload"],
+            "allreduce": step_line["config"]["allreduce"], "clocks": step_line["clocks"],
+        }
+    if extra:
+        line["extra"] = extra
     if rank == 0 and world == 1:
-        base = time_cpu_reference(1024, steps=5, warmup=1)
+        base = time_cpu_reference(M_PER_GPU, steps=5, warmup=1)
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        line["cpu_baseline"]["config1"] = time_cpu_config1()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -437,23 +554,16 @@ def profile_case(which, lib, device, desc, packed, state, lora_a, lora_b, x, dy,
     return 0
 
 
-def run_step_workload(args) -> int:
-    """BASELINE configs 4 / 5: a full QLoRA step of a synthetic-weight decoder; metric = training targets per second."""
+def measure_step(shape, workload_name, steps, warmup, layers, use_graph, world, rank, local_rank, device):
+    """Times a full QLoRA step of a synthetic-weight decoder (the process group, if any, is already up).
+    Returns the JSON line of the step workload as a dict."""
     import torch.distributed as dist
 
     from molt_b200 import _native
-    from molt_b200.qlora_step import LLAMA3_8B, QWEN25_1P5B, QLoRAStep, hot_path_flops_per_token
+    from molt_b200.qlora_step import QLoRAStep, hot_path_flops_per_token
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    shape = QWEN25_1P5B if args.workload == "step4" else LLAMA3_8B
     lib = _native.library()
-    step = QLoRAStep(shape, device, layers=args.layers, cuda_graph=not args.no_graph)
+    step = QLoRAStep(shape, device, layers=layers, cuda_graph=use_graph, status_interval=0)
     gen = torch.Generator(device=device).manual_seed(1337 + rank)
     tokens = torch.randint(0, shape.vocab, (shape.micro_batch, shape.seq_len), device=device, generator=gen)
     targets = torch.randint(0, shape.vocab, (shape.micro_batch, shape.seq_len), device=device, generator=gen)
@@ -464,7 +574,7 @@ def run_step_workload(args) -> int:
         torch.cuda.synchronize()
 
     with torch.autocast("cuda", dtype=torch.bfloat16):
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(max(warmup, 3)):
             step.run(tokens, targets)
         barrier()
         launches_before = lib.molt_launch_count() + step.replayed_launches   # eager launches + graph-replayed ones
@@ -472,34 +582,54 @@ def run_step_workload(args) -> int:
         with ClockSampler(local_rank) as sampler:
             barrier()
             start.record()
-            for _ in range(args.steps):
+            for _ in range(steps):
                 loss = step.run(tokens, targets)
             stop.record()
             barrier()
     elapsed = torch.tensor([start.elapsed_time(stop)], device=device)
     if world > 1:
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-    ms_per_step = float(elapsed.item()) / args.steps
-    status = _native.read_status(device)
-    if status:
-        raise SystemExit(f"a bounded device wait expired (status 0x{status:08x})")
+    ms_per_step = float(elapsed.item()) / steps
+    step.check_status()
     peaks = measured_peaks()
-    layers = len(step.model.layers)
+    n_layers = len(step.model.layers)
     targets_per_s = world * shape.tokens / (ms_per_step * 1e-3)
-    hot_flops = hot_path_flops_per_token(shape) * layers / shape.layers
+    hot_flops = hot_path_flops_per_token(shape) * n_layers / shape.layers
     line = {
         "metric": "qlora_step_targets_per_s", "value": targets_per_s, "unit": "targets/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"QLoRA step, {'Qwen2.5-1.5B' if args.workload == 'step4' else 'Llama-3-8B'} architecture, "
-                               f"{layers} layers, random-init NF4 weights, LoRA r={shape.rank}, seq {shape.seq_len}, "
+        "config": {"workload": f"QLoRA step, {'Qwen2.5-1.5B' if workload_name == 'step4' else 'Llama-3-8B'} architecture, "
+                               f"{n_layers} layers, random-init NF4 weights, LoRA r={shape.rank}, seq {shape.seq_len}, "
                                f"micro-batch {shape.micro_batch} per GPU", "parallelism": f"dp{world}",
-                   "lora_parameters": step.lora_parameter_count(), "cuda_graph": not args.no_graph},
+                   "lora_parameters": step.lora_parameter_count(), "cuda_graph": use_graph,
+                   "allreduce": "one bucket per decoder layer, issued from the backward on a side stream, NCCL sum"},
         "hot_path_tflops_per_gpu": hot_flops * shape.tokens / (ms_per_step * 1e-3) / 1e12,
         "hot_path_frac_of_bf16_peak": hot_flops * shape.tokens / (ms_per_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
         "loss": float(loss), "gpu_launches": int(lib.molt_launch_count() + step.replayed_launches - launches_before),
         "clocks": sampler.summary(),
     }
+    del step
+    torch.cuda.empty_cache()
+    return line
+
+
+def run_step_workload(args) -> int:
+    """BASELINE configs 4 / 5: a full QLoRA step of a synthetic-weight decoder; metric = training targets per second."""
+    import torch.distributed as dist
+
+    from molt_b200.qlora_step import LLAMA3_8B, QWEN25_1P5B
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    shape = QWEN25_1P5B if args.workload == "step4" else LLAMA3_8B
+    line = measure_step(shape, args.workload, args.steps, args.warmup, args.layers, not args.no_graph, world, rank,
+                        local_rank, device)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -24,7 +24,11 @@ from molt_b200.methods._linear import GRAD_SLOT
 class GradArena:
     """One flat fp32 gradient buffer shared by a list of parameters."""
 
-    def __init__(self, params: Iterable[torch.nn.Parameter], bucket_bytes: int = 32 << 20):
+    def __init__(self, params: Iterable[torch.nn.Parameter], bucket_bytes: int = 32 << 20,
+                 bucket_starts: Optional[Sequence[int]] = None):
+        """``bucket_starts``: indices (into the trainable parameters, ascending, first one 0) at which a new bucket
+        begins -- e.g. the first adapter of every decoder layer, so that a layer's gradients can be reduced as soon as
+        its backward has run.  Without it buckets are cut by size."""
         self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
         if not self.params:
             raise ValueError("GradArena needs at least one trainable parameter")
@@ -44,8 +48,17 @@ class GradArena:
             self.views.append(view)
             p.grad = view
             setattr(p, GRAD_SLOT, view)
-        self.buckets = self._make_buckets(bucket_bytes)
+        self.buckets = self._make_buckets(bucket_bytes) if bucket_starts is None else self._buckets_from(bucket_starts)
         self._comm_stream: Optional[torch.cuda.Stream] = None
+
+    def _buckets_from(self, starts: Sequence[int]) -> List[Tuple[int, int]]:
+        """Buckets that begin at the given parameter indices, listed from the last to the first like the size-cut ones."""
+        starts = sorted(set(int(i) for i in starts))
+        if not starts or starts[0] != 0 or starts[-1] >= len(self.params):
+            raise ValueError("bucket_starts must begin with 0 and stay inside the parameter list")
+        bounds = self.offsets + [self.flat.numel()]
+        edges = starts + [len(self.params)]
+        return [(bounds[edges[i]], bounds[edges[i + 1]]) for i in range(len(starts) - 1, -1, -1)]
 
     def _make_buckets(self, bucket_bytes: int) -> List[Tuple[int, int]]:
         """Contiguous [begin, end) element ranges, cut at parameter boundaries, walked from the LAST
@@ -112,6 +125,102 @@ class GradArena:
         """Make the current stream wait for the collectives issued so far."""
         if self._comm_stream is not None:
             torch.cuda.current_stream(self.flat.device).wait_stream(self._comm_stream)
+
+
+class ParamArena:
+    """The parameters themselves in one flat fp32 buffer, laid out exactly like a :class:`GradArena` over the same list
+    (same offsets), with the two AdamW moments beside it: one fused kernel (``molt_adamw_step``) then steps every
+    adapter of the model.  Takes the place of the per-parameter optimizer the reference builds
+    (reference training/qlora.py:218-243) and steps (:982-986)."""
+
+    def __init__(self, grads: GradArena, lr: float = 1e-4, betas: Tuple[float, float] = (0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.0):
+        self.grads = grads
+        self.flat = torch.empty_like(grads.flat)
+        self.flat.zero_()
+        for p, off in zip(grads.params, grads.offsets):
+            view = self.flat[off:off + p.numel()].view_as(p)
+            view.copy_(p.data)
+            p.data = view                      # the module keeps its Parameter object; its storage is now the arena
+        self.exp_avg = torch.zeros_like(self.flat)
+        self.exp_avg_sq = torch.zeros_like(self.flat)
+        self.lr, self.betas, self.eps, self.weight_decay = float(lr), betas, float(eps), float(weight_decay)
+        self.steps = 0
+
+    def step(self, grad_scale: float = 1.0) -> None:
+        """One AdamW step over every parameter, on the current stream."""
+        import ctypes  # noqa: F401  (the native binding passes raw pointers)
+
+        from molt_b200 import _native
+
+        self.steps += 1
+        flat = self.flat
+        with torch.cuda.device(flat.device):
+            _native.check(_native.library().molt_adamw_step(
+                flat.data_ptr(), self.grads.flat.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                flat.numel(), self.lr, self.betas[0], self.betas[1], self.eps, self.weight_decay, self.steps,
+                float(grad_scale), _native.stream_handle(flat.device)))
+
+
+class RankLeftError(RuntimeError):
+    """A peer announced that it left, or stopped announcing steps, before a collective was launched."""
+
+
+class StepGuard:
+    """Host-side watchdog in front of the collectives of a step.
+
+    Every rank announces each step it is about to run through the process group's key-value store, and checks that
+    every peer has announced the same step before it launches kernels or collectives for it.  A rank that leaves
+    (between steps, with nothing in flight) says so; a rank that died silently simply stops announcing.  Either way
+    the survivors get :class:`RankLeftError` within ``timeout`` seconds on the host instead of a collective that
+    never completes.  (The reference is single-GPU and has no counterpart.)"""
+
+    def __init__(self, store=None, rank: Optional[int] = None, world_size: Optional[int] = None, timeout: float = 30.0,
+                 poll: float = 0.02, prefix: str = "molt_step_guard"):
+        if store is None:
+            from torch.distributed import distributed_c10d
+
+            store = distributed_c10d._get_default_store()
+        self.store = store
+        self.rank = dist.get_rank() if rank is None else int(rank)
+        self.world = dist.get_world_size() if world_size is None else int(world_size)
+        self.timeout, self.poll, self.prefix = float(timeout), float(poll), prefix
+
+    def _key(self, rank: int) -> str:
+        return f"{self.prefix}/{rank}"
+
+    def announce(self, step: int) -> None:
+        self.store.set(self._key(self.rank), str(int(step)))
+
+    def leave(self) -> None:
+        """Tell the peers that this rank is gone; call it only between steps."""
+        self.store.set(self._key(self.rank), "left")
+
+    def check(self, step: int) -> None:
+        """Announce ``step`` and wait until every peer has announced it too."""
+        import time
+
+        self.announce(step)
+        deadline = time.monotonic() + self.timeout
+        pending = [r for r in range(self.world) if r != self.rank]
+        while pending:
+            still = []
+            for r in pending:
+                value = None
+                try:
+                    if self.store.check([self._key(r)]):
+                        value = self.store.get(self._key(r)).decode()
+                except Exception as exc:  # the store itself is gone (its host rank died)
+                    raise RankLeftError(f"lost the rendezvous store while waiting for rank {r}: {exc}") from exc
+                if value == "left":
+                    raise RankLeftError(f"rank {r} left before step {step}")
+                if value is None or int(value) < step:
+                    still.append(r)
+            pending = still
+            if pending:
+                if time.monotonic() > deadline:
+                    raise RankLeftError(f"ranks {pending} did not reach step {step} within {self.timeout:.1f} s")
+                time.sleep(self.poll)
 
 
 def shard_rows(total_rows: int, rank: int, world_size: int) -> Tuple[int, int]:

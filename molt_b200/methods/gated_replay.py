@@ -21,7 +21,8 @@ import torch
 from molt_b200 import _native
 from molt_b200.core.errors import CapabilityError
 from molt_b200.kernels.gated_activation import swiglu_backward, swiglu_forward
-from molt_b200.methods._linear import GRAD_SLOT, check_linear_inputs, linear_backward, linear_forward, weight_desc
+from molt_b200.methods._linear import (GRAD_SLOT, check_linear_inputs, linear_backward, linear_forward,
+                                       weight_desc_for_tokens)
 from molt_b200.methods.nf4_lora import _adapter_of, _bf16_autocast_active, is_lora_4bit_linear
 
 
@@ -62,9 +63,10 @@ class _AsymmetricGatedNF4LoRA(torch.autograd.Function):
                 raise CapabilityError("gated activation host storage must match the gate result")
         gate2, up2 = _as_rows(gate), _as_rows(up)
         hidden = swiglu_forward(gate2, up2)
-        down_desc = weight_desc(down_packed_weight, down_quant_state)
+        tokens = int(hidden.shape[0])
+        down_desc = weight_desc_for_tokens(down_packed_weight, down_quant_state, tokens)
         result, t_down = linear_forward(down_desc, hidden, down_lora_a, down_lora_b, float(down_scaling), True)
-        ctx.up_desc = weight_desc(up_packed_weight, up_quant_state)
+        ctx.up_desc = weight_desc_for_tokens(up_packed_weight, up_quant_state, tokens)
         ctx.down_desc = down_desc
         ctx.states = (up_quant_state, down_quant_state)
         ctx.up_scaling = float(up_scaling)
@@ -186,9 +188,10 @@ class _GatedMLPNF4LoRA(torch.autograd.Function):
                 norm_weight_offset):
         for w, a, b in ((gate_w, gate_a, gate_b), (up_w, up_a, up_b), (down_w, down_a, down_b)):
             check_linear_inputs(x, w, a, b, "gated NF4-LoRA MLP")
-        descs = (weight_desc(gate_w, gate_state), weight_desc(up_w, up_state), weight_desc(down_w, down_state))
         x2 = _as_rows(x)
         m = x2.shape[0]
+        descs = tuple(weight_desc_for_tokens(w, st, int(m)) for w, st in ((gate_w, gate_state), (up_w, up_state),
+                                                                          (down_w, down_state)))
         inter, hidden_width = int(descs[0].n), int(descs[0].k)
         if x2.shape[1] != hidden_width:
             raise ValueError("input width must match the gate/up projection in_features")

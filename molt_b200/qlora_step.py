@@ -3,10 +3,11 @@ NF4-LoRA kernels: the caller-side harness for BASELINE configs 4 (Qwen2.5-1.5B s
 
 The reference drives this path from its trainer (reference training/qlora.py:485-1109) with Hugging Face
 checkpoints; checkpoints and datasets are not available here, so the decoder is random-initialised with the same
-architecture and fed uniform random token ids.  Attention (torch SDPA), RoPE, RMSNorm, the frozen bf16 embedding /
-LM head with a chunked exact cross-entropy, and AdamW are plain PyTorch -- they are callers of the hot path, not
-part of it.  Data parallelism: one process per GPU, the LoRA gradients live in one flat arena that is all-reduced
-over NCCL (``molt_b200.data_parallel``).
+architecture and fed uniform random token ids.  Attention (torch SDPA) and RoPE are plain PyTorch -- they are callers of the hot path, not part of it.  The frozen
+RMSNorm (forward and backward), the in-place softmax gradient of the frozen-head cross-entropy and the AdamW step over
+the flat adapter arena are this library's kernels.  Data parallelism: one process per GPU; the LoRA gradients live in
+one flat arena whose per-layer buckets are all-reduced over NCCL on a side stream while the backward of the earlier
+layers is still running (``molt_b200.data_parallel``).
 """
 from __future__ import annotations
 
@@ -20,7 +21,7 @@ from torch import nn
 from torch.nn import functional as F
 
 from molt_b200 import _native
-from molt_b200.data_parallel import GradArena, lora_parameters
+from molt_b200.data_parallel import GradArena, ParamArena, StepGuard, lora_parameters
 from molt_b200.methods.quant_state import NestedState, QuantState
 from molt_b200.modules import GatedMLP, NF4LoRALinear
 from molt_b200.streaming.nf4 import NF4_CODEBOOK
@@ -87,6 +88,42 @@ def _projection(out_features: int, in_features: int, shape: DecoderShape, gen: t
     return lin
 
 
+class _FrozenRMSNorm(torch.autograd.Function):
+    """RMSNorm with a frozen weight: fp32 reduction, bf16 in and out, gradient for the input only (the contract of
+    reference kernels/frozen_rmsnorm.py:9-37)."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, eps):
+        rows = hidden.reshape(-1, hidden.shape[-1])
+        if not rows.is_contiguous():
+            rows = rows.contiguous()
+        out = torch.empty_like(rows)
+        dtype = _native.DTYPE_F32 if weight.dtype == torch.float32 else _native.DTYPE_BF16
+        with torch.cuda.device(rows.device):
+            _native.check(_native.library().molt_rmsnorm_fwd(rows.data_ptr(), weight.data_ptr(), dtype, float(eps), 0.0,
+                                                             out.data_ptr(), rows.shape[0], rows.shape[1],
+                                                             _native.stream_handle(rows.device)))
+        ctx.save_for_backward(rows, weight)
+        ctx.eps, ctx.weight_dtype, ctx.shape = float(eps), dtype, hidden.shape
+        return out.reshape(hidden.shape)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_output):
+        rows, weight = ctx.saved_tensors
+        grad = grad_output.reshape(rows.shape)
+        if grad.dtype != torch.bfloat16:
+            grad = grad.to(torch.bfloat16)
+        if not grad.is_contiguous():
+            grad = grad.contiguous()
+        out = torch.empty_like(rows)
+        with torch.cuda.device(rows.device):
+            _native.check(_native.library().molt_rmsnorm_bwd(grad.data_ptr(), rows.data_ptr(), weight.data_ptr(),
+                                                             ctx.weight_dtype, ctx.eps, 0.0, out.data_ptr(), rows.shape[0],
+                                                             rows.shape[1], _native.stream_handle(rows.device)))
+        return out.reshape(ctx.shape), None, None
+
+
 class RMSNorm(nn.Module):
     def __init__(self, width: int, device, eps: float = 1e-6):
         super().__init__()
@@ -94,6 +131,8 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            return _FrozenRMSNorm.apply(x, self.weight, self.eps)
         return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
 
 
@@ -135,7 +174,11 @@ class DecoderLayer(nn.Module):
                             _projection(shape.intermediate, shape.hidden, shape, gen, device),
                             _projection(shape.hidden, shape.intermediate, shape, gen, device))
 
-    def forward(self, x, cos, sin, replay_up: bool):
+    def forward(self, x, cos, sin, replay_up: bool, on_backward_done=None):
+        if on_backward_done is not None and x.requires_grad:
+            # fires when the gradient of this layer's input exists, i.e. when every adapter gradient of the layer has
+            # been written: the moment its bucket can go to the all-reduce
+            x.register_hook(on_backward_done)
         x = x + self.attn(self.input_norm(x), cos, sin)
         normed = self.post_norm(x)
         b, s, w = normed.shape
@@ -191,41 +234,70 @@ class SyntheticDecoder(nn.Module):
         self.register_buffer("cos", angles.cos().bfloat16()[None, None], persistent=False)
         self.register_buffer("sin", angles.sin().bfloat16()[None, None], persistent=False)
 
-    def loss(self, tokens: torch.Tensor, targets: torch.Tensor, global_tokens: int, replay_up: bool = True) -> torch.Tensor:
+    def loss(self, tokens: torch.Tensor, targets: torch.Tensor, global_tokens: int, replay_up: bool = True,
+             layer_done=None) -> torch.Tensor:
+        """``layer_done(index)``, when given, is called during backward as soon as layer ``index`` has produced all of
+        its adapter gradients (layers finish from the last to the first)."""
         x = F.embedding(tokens, self.embed).requires_grad_()
-        for layer in self.layers:
-            x = layer(x, self.cos, self.sin, replay_up)
+        for index, layer in enumerate(self.layers):
+            hook = None
+            if layer_done is not None:
+                def hook(grad, index=index):
+                    layer_done(index)
+                    return grad
+            x = layer(x, self.cos, self.sin, replay_up, hook)
         hidden = self.final_norm(x).reshape(-1, self.shape.hidden)
         return _FrozenHeadLoss.apply(hidden, self.head, targets.reshape(-1), 1024, float(global_tokens))
 
 
 class QLoRAStep:
-    """Holds model, gradient arena and optimiser; ``run(tokens, targets)`` is one data-parallel training step."""
+    """Holds model, gradient arena and optimiser; ``run(tokens, targets)`` is one data-parallel training step.
+
+    Step anatomy: zero the gradient arena; forward; backward, during which every decoder layer's bucket of the arena
+    goes to the all-reduce (side stream) as soon as the layer's backward has run, so the exchange overlaps the backward
+    of the layers before it; join; one fused AdamW launch over the flat parameter arena (gradients scaled by 1 / world
+    in the same pass).  Forward + backward + collectives replay as one CUDA graph once warmed up.  Every
+    ``status_interval`` steps the device status word of the bounded waits is read (a host synchronisation) and a
+    non-zero value raises; with a :class:`StepGuard` the ranks also check each other on the host before each step."""
 
     def __init__(self, shape: DecoderShape, device, layers: Optional[int] = None, lr: float = 1e-4,
-                 cuda_graph: bool = False):
+                 cuda_graph: bool = False, status_interval: int = 50, guard: Optional[StepGuard] = None):
         self.shape = shape
         self.device = device
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.model = SyntheticDecoder(shape, device, layers=layers)
-        self.arena = GradArena(lora_parameters(self.model))
-        self.optimizer = torch.optim.AdamW(self.arena.params, lr=lr, weight_decay=0.0, fused=True)
+        params = lora_parameters(self.model)
+        # one bucket per decoder layer: the index of each layer's first adapter parameter
+        identity = {id(p): i for i, p in enumerate(params)}
+        starts = sorted(min(identity[id(p)] for p in layer.parameters() if p.requires_grad) for layer in self.model.layers)
+        self.arena = GradArena(params, bucket_starts=starts)
+        self.layer_bucket = [self.arena.bucket_of_param(start) for start in starts]
+        self.optimizer = ParamArena(self.arena, lr=lr, weight_decay=0.0)
         self.cuda_graph = cuda_graph
+        self.status_interval = int(status_interval)
+        self.guard = guard
+        self.steps = 0
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._static_tokens = self._static_targets = self._static_loss = None
         self._eager_steps = 0
         self.graph_launches = 0      # library kernel launches recorded in the CUDA graph
         self.replayed_launches = 0   # library kernel launches executed through graph replays so far
 
+    def _layer_done(self, index: int) -> None:
+        if self.world > 1:
+            self.arena.all_reduce_bucket(self.layer_bucket[index])
+
     def _forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         self.arena.zero()
-        loss = self.model.loss(tokens, targets, self.shape.tokens * self.world)
+        loss = self.model.loss(tokens, targets, self.shape.tokens * self.world,
+                               layer_done=self._layer_done if self.world > 1 else None)
         loss.backward()
+        self.arena.wait()            # the current stream joins the collectives issued from the backward
         return loss.detach()
 
     def _capture(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
-        """Record forward + backward of one micro-batch once; every later step replays the recording (the kernels
-        take raw pointers and never allocate or synchronise, so they are capture-safe)."""
+        """Record forward + backward (+ the overlapped collectives) of one micro-batch once; every later step replays
+        the recording (the kernels take raw pointers and never allocate or synchronise, so they are capture-safe)."""
         self._static_tokens = tokens.clone()
         self._static_targets = targets.clone()
         self._graph = torch.cuda.CUDAGraph()
@@ -236,6 +308,8 @@ class QLoRAStep:
         self.graph_launches = int(lib.molt_launch_count() - before)   # library kernels recorded; each replay runs them
 
     def run(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        if self.guard is not None:
+            self.guard.check(self.steps)     # host-side: every peer is alive and about to run the same step
         if self.cuda_graph and self._graph is None and self._eager_steps >= 2:
             self._capture(tokens, targets)
         if self._graph is not None:
@@ -247,9 +321,17 @@ class QLoRAStep:
         else:
             loss = self._forward_backward(tokens, targets)
             self._eager_steps += 1
-        self.arena.all_reduce()
-        self.optimizer.step()
+        self.optimizer.step(grad_scale=1.0)  # the loss is already normalised by the global token count
+        self.steps += 1
+        if self.status_interval > 0 and self.steps % self.status_interval == 0:
+            self.check_status()
         return loss
+
+    def check_status(self) -> None:
+        """Read the device status word (synchronises the stream); a bounded wait that expired left outputs incomplete."""
+        status = _native.read_status(self.device)
+        if status:
+            raise RuntimeError(f"a bounded device-side wait expired (status 0x{status:08x}); the step's results are invalid")
 
     def lora_parameter_count(self) -> int:
         return sum(p.numel() for p in self.arena.params)

@@ -70,3 +70,17 @@ def oracle_results(case: LinearCase):
 def assert_clean_status():
     status = _native.read_status()
     assert status == 0, f"device status word reports a bounded wait that expired: 0x{status:08x}"
+
+
+def dense_from_state(packed: torch.Tensor, state) -> torch.Tensor:
+    """deq(W) in fp32 on the host, computed by the oracle from the bytes and absmax a device-side quant state holds."""
+    order = oracle.HIGH_FIRST if state.nibble_order == "high-first" else oracle.LOW_FIRST
+    if state.nested:
+        nested = oracle.NestedAbsmax(state.absmax.cpu(), state.state2.absmax.cpu(), state.state2.code.cpu(),
+                                     float(state.offset), int(state.state2.blocksize))
+        scales = oracle.resolve_nested_absmax(nested)
+    else:
+        scales = state.absmax.cpu()
+    n, k = (int(v) for v in state.shape)
+    q = oracle.OracleNF4(packed.reshape(-1).cpu(), scales, (n, k), int(state.blocksize), n * k, order)
+    return oracle.nf4_dequantize(q)

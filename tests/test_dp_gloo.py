@@ -68,3 +68,104 @@ def test_two_rank_sharded_gradients_sum_to_full_batch():
         worst, same = results[rank]
         assert worst < 1e-5   # fp32 reduction-order tolerance
         assert same
+
+
+def _leaver_worker(rank: int, world: int, port: int, results):
+    """Three ranks train in lock step behind a StepGuard; rank 2 leaves between step 1 and step 2 (nothing in flight),
+    and the others must get RankLeftError on the host before they launch step 2's collective."""
+    import time
+
+    from molt_b200.data_parallel import RankLeftError, StepGuard
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    outcome = "none"
+    try:
+        guard = StepGuard(timeout=20.0)
+        grads = torch.nn.Parameter(torch.zeros(64))
+        arena = GradArena([grads], bucket_starts=[0])
+        for step in range(3):
+            if rank == 2 and step == 2:
+                guard.leave()                      # between steps: no kernel or collective of this rank is in flight
+                outcome = "left"
+                break
+            begin = time.monotonic()
+            try:
+                guard.check(step)
+            except RankLeftError as exc:
+                outcome = f"detected at step {step} after {time.monotonic() - begin:.2f} s: {exc}"
+                break
+            arena.zero()
+            arena.views[0].add_(float(rank + 1))
+            arena.all_reduce()
+            assert float(arena.flat[0]) == 6.0     # 1 + 2 + 3
+            outcome = f"ran step {step}"
+        results[rank] = outcome
+    finally:
+        # the survivors do not run another collective; tear the group down without a barrier
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(180)
+def test_rank_that_leaves_between_steps_is_detected_on_the_host():
+    world = 3
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(150)
+        assert p.exitcode == 0, "a rank hung or crashed instead of reporting the departure"
+    assert results[2] == "left"
+    for rank in (0, 1):
+        assert results[rank].startswith("detected at step 2"), results[rank]
+        assert "rank 2 left" in results[rank]
+
+
+def _silent_worker(rank: int, world: int, port: int, results):
+    """Rank 1 stops announcing steps without saying so (as a crashed process would); rank 0's guard times out."""
+    from molt_b200.data_parallel import RankLeftError, StepGuard
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        guard = StepGuard(timeout=1.5)
+        guard.check(0)
+        if rank == 1:
+            results[rank] = "silent"
+            return
+        try:
+            guard.check(1)
+            results[rank] = "no error"
+        except RankLeftError as exc:
+            results[rank] = f"timeout: {exc}"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_silent_rank_times_out_instead_of_hanging():
+    world = 2
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_silent_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(100)
+        assert p.exitcode == 0
+    assert results[1] == "silent" and results[0].startswith("timeout") and "did not reach step 1" in results[0]
+
+
+def test_layer_buckets_follow_the_given_starts():
+    params = [torch.nn.Parameter(torch.zeros(n)) for n in (10, 70, 64, 5, 130)]
+    arena = GradArena(params, bucket_starts=[0, 2, 4])
+    # listed from the last layer to the first; slices are padded to 64 elements
+    assert arena.buckets == [(arena.offsets[4], arena.flat.numel()), (arena.offsets[2], arena.offsets[4]),
+                             (0, arena.offsets[2])]
+    assert [arena.bucket_of_param(i) for i in range(5)] == [2, 2, 1, 1, 0]
+    with pytest.raises(ValueError):
+        GradArena(params, bucket_starts=[1, 3])

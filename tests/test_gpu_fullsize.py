@@ -17,7 +17,7 @@ import torch
 
 from oracle import molt_oracle as oracle
 from molt_b200 import _native
-from tests.gpu_utils import TOL, assert_clean_status
+from tests.gpu_utils import TOL, assert_clean_status, dense_from_state
 
 pytestmark = pytest.mark.gpu
 
@@ -43,15 +43,7 @@ class FullCase:
     def dense(self) -> torch.Tensor:
         """deq(W) in fp32 on the host, from the packed bytes and the absmax the device holds."""
         if self._dense is None:
-            order = oracle.HIGH_FIRST if self.state.nibble_order == "high-first" else oracle.LOW_FIRST
-            if self.state.nested:
-                nested = oracle.NestedAbsmax(self.state.absmax.cpu(), self.state.state2.absmax.cpu(),
-                                             self.state.state2.code.cpu(), float(self.state.offset), 256)
-                scales = oracle.resolve_nested_absmax(nested)
-            else:
-                scales = self.state.absmax.cpu()
-            q = oracle.OracleNF4(self.packed.reshape(-1).cpu(), scales, (self.n, self.k), 64, self.n * self.k, order)
-            self._dense = oracle.nf4_dequantize(q)
+            self._dense = dense_from_state(self.packed, self.state)
         return self._dense
 
     def desc(self):
