@@ -539,10 +539,11 @@ def profile_case(which, lib, device, desc, packed, state, lora_a, lora_b, x, dy,
             _native.check(lib.molt_nf4_lora_fwd(ctypes.byref(plain_desc), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
                                                 SCALING, RANK, y.data_ptr(), m, None, ws.data_ptr(), ws_bytes,
                                                 _native.PATH_TCGEN05, stream))
-        elif which == "gemv":
+        elif which in ("gemv", "gemv1"):
+            tokens = 16 if which == "gemv" else 1
             for d in (desc, plain_desc):   # nested absmax (the configuration's own form), then plain fp32 absmax
                 _native.check(lib.molt_nf4_gemv(ctypes.byref(d), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
-                                                SCALING, RANK, y.data_ptr(), 16, ws.data_ptr(), ws_bytes, stream))
+                                                SCALING, RANK, y.data_ptr(), tokens, ws.data_ptr(), ws_bytes, stream))
         elif which == "swiglu":
             gate, up, grad = dy, torch.roll(dy, 1, 0), torch.roll(dy, 2, 0)   # three distinct [M, N] tensors
             swiglu_forward(gate, up)
@@ -726,7 +727,7 @@ def main() -> int:
                         help="linear = the headline NF4-LoRA linear; step4 / step5 = full QLoRA step of BASELINE config 4 / 5")
     parser.add_argument("--no-graph", action="store_true", help="step workloads: run eagerly instead of replaying a CUDA graph")
     parser.add_argument("--layers", type=int, default=None, help="step workloads: use fewer decoder layers")
-    parser.add_argument("--profile", choices=("gemm_bwd", "linear_fwd", "gemv", "swiglu"), default=None,
+    parser.add_argument("--profile", choices=("gemm_bwd", "linear_fwd", "gemv", "gemv1", "swiglu"), default=None,
                         help="run one kernel family four times and exit (target of an ncu capture)")
     args = parser.parse_args()
     if args.steps < 1:
