@@ -47,6 +47,8 @@ extern "C" {
 /* Optional flags, OR-ed onto a path: schedule of the tensor-core GEMMs when the last wave of output tiles is partial. */
 #define MOLT_PATH_NO_SPLIT 0x100    /* keep the plain tile schedule                                      */
 #define MOLT_PATH_FORCE_SPLIT 0x200 /* cut the tiles of the last wave along the contraction whenever the shape allows it */
+#define MOLT_PATH_TALL_TILES 0x400  /* tensor-core GEMMs: 512-token tiles per CTA pair (two MMAs per decoded weight tile) */
+#define MOLT_PATH_SHORT_TILES 0x800 /* tensor-core GEMMs: 256-token tiles per CTA pair; neither flag = the library chooses */
 
 /* operations for molt_workspace_bytes */
 #define MOLT_OP_LORA_FWD 1

@@ -159,10 +159,12 @@ static bool aligned_case(const molt_nf4_desc* w, int rank) {
 static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m, bool forward, int* chosen,
                      int* gemm_flags = nullptr) {
   const bool aligned = aligned_case(w, rank);
-  MOLT_REQUIRE((requested & ~(0xff | MOLT_PATH_NO_SPLIT | MOLT_PATH_FORCE_SPLIT)) == 0, MOLT_E_VALUE,
-               "unknown kernel path flags 0x%x", requested);
+  MOLT_REQUIRE((requested & ~(0xff | MOLT_PATH_NO_SPLIT | MOLT_PATH_FORCE_SPLIT | MOLT_PATH_TALL_TILES |
+                              MOLT_PATH_SHORT_TILES)) == 0,
+               MOLT_E_VALUE, "unknown kernel path flags 0x%x", requested);
   if (gemm_flags != nullptr)
-    *gemm_flags = ((requested & MOLT_PATH_NO_SPLIT) ? kGemmNoSplit : 0) | ((requested & MOLT_PATH_FORCE_SPLIT) ? kGemmForceSplit : 0);
+    *gemm_flags = ((requested & MOLT_PATH_NO_SPLIT) ? kGemmNoSplit : 0) | ((requested & MOLT_PATH_FORCE_SPLIT) ? kGemmForceSplit : 0) |
+                  ((requested & MOLT_PATH_TALL_TILES) ? kGemmTallTiles : 0) | ((requested & MOLT_PATH_SHORT_TILES) ? kGemmShortTiles : 0);
   requested &= 0xff;
   if (requested == MOLT_PATH_AUTO) {
     if (!aligned) *chosen = MOLT_PATH_GENERAL;

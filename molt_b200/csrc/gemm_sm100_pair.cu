@@ -9,6 +9,13 @@
 // whole 256-wide tile.  Compared with a single-CTA tile this halves the decode work and the shared-memory operand
 // traffic per FLOP.
 //
+// Tall tiles (kSub = 2): a pair tile covers 512 token rows, i.e. every CTA holds TWO 128-row activation tiles per
+// contraction block and two accumulators (all 512 TMEM columns), and multiplies both by the SAME decoded B tile.  The
+// decode, the packed-code traffic and every handshake are then paid once per two MMAs, which is what bounds the kernel;
+// the price is that the epilogue of a tile no longer overlaps the whole next tile (the first accumulator is handed back
+// as soon as it is drained, so the next tile's first MMAs start early).  Short tiles (kSub = 1: 256 rows, two
+// accumulators used in turn) remain for small token counts and for shapes whose tall tiles quantise badly.
+//
 // Per CTA: two TMA rings (16 KB activation tiles; 4 KB packed-code tiles, deeper) run several blocks ahead of a
 // separate ring of decoded B half-tiles, so the global-memory latency is not serialised with the decode.
 // Decode: a decoder thread owns one 64-element segment (one absmax) per block.  It first forms the sixteen values
@@ -212,8 +219,9 @@ __device__ __forceinline__ void decode_word(uint32_t w, const SegmentTable& t, u
   }
 }
 
+template <int kSub>
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  constexpr int kBand = 8;  // 8 pair tiles = 2048 tokens share the L2 while the weight columns stream by
+  constexpr int kBand = 8 / kSub;  // 2048 tokens share the L2 while the weight columns stream by
   const int band_tiles = kBand * tiles_n;
   const int band = tile / band_tiles;
   const int first_m = band * kBand;
@@ -276,11 +284,11 @@ __device__ __forceinline__ void next_item(const WorkPlan& w, WorkItem& it) {
   tail_item(w, it);
 }
 // Slot of a pair's partial accumulator: two per pair, [0] for the part that ends a tile, [1] for the part that starts one.
-__host__ __device__ __forceinline__ size_t split_slot_offset(int pair, int starts_tile, int rank) {
-  return ((size_t)(pair * 2 + starts_tile) * 2 + rank) * BM * BN;
+__host__ __device__ __forceinline__ size_t split_slot_offset(int pair, int starts_tile, int sub, int rank, int subs) {
+  return ((size_t)((pair * 2 + starts_tile) * subs + sub) * 2 + rank) * BM * BN;
 }
 
-template <bool BACKWARD, int kLoadStages, int kBStages, int kStoreBufs, int kDecodeGroups>
+template <bool BACKWARD, int kSub, int kLoadStages, int kBStages, int kStoreBufs, int kDecodeGroups>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(kDecodeGroups), 1)
 nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_packed,
                            const __grid_constant__ CUtensorMap map_low, const __grid_constant__ CUtensorMap map_ext,
@@ -380,7 +388,8 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     // once block t - depth has been consumed.  One thread per warp runs the loop; it is kept short because its
     // iteration time bounds the whole pipeline.
     const bool codes = warp == kCodeWarp;
-    const int depth = codes ? kCodeStages : kLoadStages;
+    static_assert(kLoadStages % kSub == 0, "the activation ring holds whole blocks");
+    const int depth = codes ? kCodeStages : kLoadStages / kSub;   // in contraction blocks
     if (lane == 0) {
       // Failure injection for tests: with p.withhold = w the last w blocks of this CTA are never requested, so the
       // consumers' bounded waits run out.  total_blocks is only computed when the injection is on.
@@ -390,11 +399,11 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         for (WorkItem it = first_item(plan); it.valid; next_item(plan, it)) total_blocks += it.kb1 - it.kb0;
         total_blocks -= p.withhold;
       }
-      int t = 0, stage = 0;
+      int t = 0, stage = 0;                                     // stage: code stage, or first activation stage of the block
       for (WorkItem item = first_item(plan); item.valid && t < total_blocks; next_item(plan, item)) {
         int tm, tn;
-        pair_tile_coords(item.tile, p.tiles_m, p.tiles_n, tm, tn);
-        const int row0 = tm * 2 * BM + (int)rank * BM;          // first token row of this CTA
+        pair_tile_coords<kSub>(item.tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int row0 = tm * (2 * BM * kSub) + (int)rank * BM;  // first token row of this CTA (sub-tile s: + s * 2 * BM)
         const int col0 = tn * BN + (int)rank * BNH;             // first B row of this CTA
         bool ok = true;
         for (int kb = item.kb0; kb < item.kb1 && t < total_blocks; ++kb, ++t) {
@@ -411,14 +420,19 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
               mbar_arrive(bar_pkfull(stage));   // the low-rank block has no codes; keep the ring's phases in step
             }
             MOLT_TRACE(9, t);
+            if (++stage == kCodeStages) stage = 0;
           } else {
-            const uint32_t a_dst = load0 + (uint32_t)stage * kLoadStageBytes;
-            mbar_expect_tx(bar_ldfull(stage), kTileABytes);
-            if (kb < p.num_kb) tma_load_2d(a_dst, &map_in, kb * BK, row0, bar_ldfull(stage));
-            else tma_load_2d(a_dst, &map_low, 0, row0, bar_ldfull(stage));
+#pragma unroll
+            for (int sub = 0; sub < kSub; ++sub) {
+              const uint32_t a_dst = load0 + (uint32_t)(stage + sub) * kLoadStageBytes;
+              mbar_expect_tx(bar_ldfull(stage + sub), kTileABytes);
+              if (kb < p.num_kb) tma_load_2d(a_dst, &map_in, kb * BK, row0 + sub * 2 * BM, bar_ldfull(stage + sub));
+              else tma_load_2d(a_dst, &map_low, 0, row0 + sub * 2 * BM, bar_ldfull(stage + sub));
+            }
             MOLT_TRACE(0, t);
+            stage += kSub;
+            if (stage == kLoadStages) stage = 0;
           }
-          if (++stage == depth) stage = 0;
         }
         if (!ok) break;
       }
@@ -437,49 +451,65 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       // One thread runs this loop: it is the serial heart of the kernel (it feeds the tensor cores of two SMs),
       // so it holds nothing but the wait, the four MMAs and the commit.
       if (lane == 0) {
-        int ls = 0, bs = 0, acc = 0, g = 0;
-        uint32_t bphase = 0, acc_phase = 0;
+        int ls = 0, bs = 0, g = 0, tiles_done = 0;
+        uint32_t bphase = 0;
+        uint32_t slot_phase[2] = {0u, 0u};     // flips every time an accumulator has been handed to the epilogue
         bool ok = true;
-        for (WorkItem item = first_item(plan); item.valid && ok; next_item(plan, item)) {
-          ok = wait_on(bar_accempty(acc), acc_phase ^ 1u, 2);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+        for (WorkItem item = first_item(plan); item.valid && ok; next_item(plan, item), ++tiles_done) {
           uint32_t accumulate = 0u;
           for (int kb = item.kb0; kb < item.kb1; ++kb) {
-            // The decoders of both CTAs arrive on b_full only after their own activation tile has landed, so
+            // The decoders of both CTAs arrive on b_full only after their own activation tiles have landed, so
             // this one wait covers both operands in both CTAs.
             ok = wait_on(bar_bfull(bs), bphase, 4);
             if (!ok) break;
             MOLT_TRACE(6, g);
             tc_fence_after();
-            const uint32_t a_lo = a_lo0 + (uint32_t)ls * (kLoadStageBytes >> 4);
             const uint32_t b_lo = b_lo0 + (uint32_t)bs * (kTileBBytes >> 4);
-#ifdef MOLT_PAIR_EXP_NO_MMA      // timing experiment: no tensor work, only the commits (results are wrong)
-            if (false) {
-#else
-            if (kb < p.num_kb) {
-#endif
-              umma_bf16_pair(d_tmem, desc64(a_lo, desc_hi), desc64(b_lo, desc_hi), idesc, accumulate);
 #pragma unroll
-              for (int ks = 1; ks < BK / 16; ++ks)
-                umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc, 1u);
-            } else {   // the low-rank block
-              for (int ks = 0; ks < p.ext_steps; ++ks)
-                umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc,
-                               (accumulate | (uint32_t)(ks > 0)));
+            for (int sub = 0; sub < kSub; ++sub) {
+              // short tiles use the two accumulators in turn, tall tiles use both at once (one per sub-tile)
+              const int slot = kSub == 1 ? (tiles_done & 1) : sub;
+              if (kb == item.kb0) {   // first use in this tile: the epilogue must have drained the accumulator
+                ok = wait_on(bar_accempty(slot), slot_phase[slot] ^ 1u, 2);
+                if (!ok) break;
+                tc_fence_after();
+              }
+              const uint32_t d_tmem = tmem_base + (uint32_t)slot * BN;
+              const uint32_t a_lo = a_lo0 + (uint32_t)(ls + sub) * (kLoadStageBytes >> 4);
+#ifdef MOLT_PAIR_EXP_NO_MMA      // timing experiment: no tensor work, only the commits (results are wrong)
+              if (false) {
+#else
+              if (kb < p.num_kb) {
+#endif
+                umma_bf16_pair(d_tmem, desc64(a_lo, desc_hi), desc64(b_lo, desc_hi), idesc, accumulate);
+#pragma unroll
+                for (int ks = 1; ks < BK / 16; ++ks)
+                  umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc, 1u);
+              } else {   // the low-rank block
+                for (int ks = 0; ks < p.ext_steps; ++ks)
+                  umma_bf16_pair(d_tmem, desc64(a_lo + ks * 2, desc_hi), desc64(b_lo + ks * kBStep, desc_hi), idesc,
+                                 (accumulate | (uint32_t)(ks > 0)));
+              }
             }
+            if (!ok) break;
             accumulate = 1u;
             MOLT_TRACE(7, g);
-            // one commit releases this block's load stage and B stage in both CTAs once the MMAs have read them
+            // one commit releases this block's load stages and B stage in both CTAs once the MMAs have read them
             umma_commit_both(bar_consumed(g));
-            if (kb == item.kb1 - 1) umma_commit_both(bar_accfull(acc));
+            if (kb == item.kb1 - 1) {
+#pragma unroll
+              for (int sub = 0; sub < kSub; ++sub) {
+                const int slot = kSub == 1 ? (tiles_done & 1) : sub;
+                umma_commit_both(bar_accfull(slot));
+                slot_phase[slot] ^= 1u;
+              }
+            }
             MOLT_TRACE(1, g);
             ++g;
-            if (++ls == kLoadStages) ls = 0;
+            ls += kSub;
+            if (ls == kLoadStages) ls = 0;
             if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
           }
-          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
       }
       __syncwarp();
@@ -521,7 +551,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     int g_tile = 0;                // running block number of the item's first block
     for (WorkItem item = first_item(plan); item.valid && ok; g_tile += item.kb1 - item.kb0, next_item(plan, item)) {
       int tm, tn;
-      pair_tile_coords(item.tile, p.tiles_m, p.tiles_n, tm, tn);
+      pair_tile_coords<kSub>(item.tile, p.tiles_m, p.tiles_n, tm, tn);
       const int col0 = tn * BN + (int)rank * BNH;   // first B row (forward: weight row; backward: weight column)
       // forward : absmax[(col0 + i) * kpr + kb]            backward: absmax[(kb * 64 + j) * kpr + col0 / 64 + a]
       const float* scale_ptr;
@@ -556,7 +586,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
           if (kb >= item.kb1 || !ok) continue;
           const float scale = cur[q];
           const int g = g_tile + (kb - item.kb0);
-          const int ls = g % kLoadStages, bs = g % kBStages, cs = g % kCodeStages;
+          const int bs = g % kBStages, cs = g % kCodeStages;
           // The sixteen values this segment can take, as byte planes (needs only the absmax: done before the waits).
           SegmentTable table;
           if (kLutWords < 8 && kb < p.num_kb) table = make_segment_table(p.codebook, scale);
@@ -628,7 +658,11 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
             ext_phase ^= 1u;   // this group's barrier has completed once more
           }
           // this CTA's activation tile must have landed before the block is announced to the MMA thread
-          ok = wait_on(bar_ldfull(ls), (uint32_t)((g / kLoadStages) & 1), 9);
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub) {
+            const int a = g * kSub + sub;   // running number of the activation tile
+            ok = ok && wait_on(bar_ldfull(a % kLoadStages), (uint32_t)((a / kLoadStages) & 1), 9);
+          }
           if (!ok) continue;
           __syncwarp();
           if (lane == 0) mbar_arrive_remote(bfull_remote_base + 8u * (uint32_t)bs);
@@ -642,21 +676,24 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     // ================= epilogue: TMEM -> bf16 -> shared -> TMA store (own 128 token rows) =================
     const int row = warp * 32 + lane;
     const uint32_t accempty_remote_base = map_to_cta(bar_accempty(0), 0);
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    int store_buf = 0;
+    uint32_t full_phase[2] = {0u, 0u};     // flips every time an accumulator has been drained
+    int store_buf = 0, tiles_done = 0;
     bool ok = true;
-    for (WorkItem item = first_item(plan); item.valid && ok; next_item(plan, item)) {
+    for (WorkItem item = first_item(plan); item.valid && ok; next_item(plan, item), ++tiles_done) {
       int tm, tn;
-      pair_tile_coords(item.tile, p.tiles_m, p.tiles_n, tm, tn);
-      const int row0 = tm * 2 * BM + (int)rank * BM;
-      ok = wait_on(bar_accfull(acc), acc_phase, 8);
+      pair_tile_coords<kSub>(item.tile, p.tiles_m, p.tiles_n, tm, tn);
+#pragma unroll
+      for (int sub = 0; sub < kSub; ++sub) {
+      const int acc = kSub == 1 ? (tiles_done & 1) : sub;   // accumulator of this sub-tile
+      const int row0 = tm * (2 * BM * kSub) + sub * 2 * BM + (int)rank * BM;
+      ok = wait_on(bar_accfull(acc), full_phase[acc], 8);
       if (!ok) break;
+      full_phase[acc] ^= 1u;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)acc * BN;
       if (item.tile >= plan.full_tiles) {
         // ---- part of a split tile: the fp32 accumulator goes to this pair's slot, row-major ----
-        float* part = p.split_partial + split_slot_offset(pair_id, item.kb0 == 0 ? 1 : 0, (int)rank) + (size_t)row * BN;
+        float* part = p.split_partial + split_slot_offset(pair_id, item.kb0 == 0 ? 1 : 0, sub, (int)rank, kSub) + (size_t)row * BN;
         const bool row_valid = (long long)row0 + row < p.m;   // the fix-up kernel never reads rows past the end
         for (int cg = 0; cg < BN / 32; ++cg) {
           uint32_t v[32];
@@ -672,7 +709,6 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(accempty_remote_base + 8u * (uint32_t)acc);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         continue;
       }
       for (int cg = 0; cg < BN / 64; ++cg) {
@@ -720,7 +756,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(accempty_remote_base + 8u * (uint32_t)acc);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }   // sub-tiles
     }
     if (threadIdx.x == 0) tma_store_wait_all();
   }
@@ -740,16 +776,18 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
 
 // out[row, col] = bf16(sum over the parts of a split tile), parts added in pair order.  One thread per 8 columns.
 __global__ void __launch_bounds__(256) split_fixup_kernel(const float* __restrict__ partial, WorkPlan plan, int tiles_m,
-                                                          int tiles_n, long long m, long long out_cols,
+                                                          int tiles_n, int subs, long long m, long long out_cols,
                                                           __nv_bfloat16* __restrict__ out) {
   const int tail_tile = blockIdx.y;
   const int tile = plan.full_tiles + tail_tile;
   int tm, tn;
-  pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
-  const int idx = blockIdx.x * 256 + threadIdx.x;          // 2 * BM rows x BN / 8 column groups
-  const int r = idx / (BN / 8), cgroup = idx % (BN / 8);
-  const long long row = (long long)tm * 2 * BM + r, col = (long long)tn * BN + cgroup * 8;
+  if (subs == 2) pair_tile_coords<2>(tile, tiles_m, tiles_n, tm, tn);
+  else pair_tile_coords<1>(tile, tiles_m, tiles_n, tm, tn);
+  const int idx = blockIdx.x * 256 + threadIdx.x;          // 2 * BM * subs rows x BN / 8 column groups
+  const int r = idx / (BN / 8), cgroup = idx % (BN / 8);   // row inside the tile: sub-tile, CTA, row of the CTA
+  const long long row = (long long)tm * (2 * BM * subs) + r, col = (long long)tn * BN + cgroup * 8;
   if (row >= m || col >= out_cols) return;
+  const int sub = r / (2 * BM), cta = (r % (2 * BM)) / BM, local = r % BM;
   const int unit0 = tail_tile * plan.blocks, unit1 = unit0 + plan.blocks;
   int first = (int)(((long long)unit0 * plan.num_pairs) / plan.tail_units);   // the pair whose range holds unit0
   while (first + 1 < plan.num_pairs && tail_range_begin(plan, first + 1) <= unit0) ++first;
@@ -757,7 +795,7 @@ __global__ void __launch_bounds__(256) split_fixup_kernel(const float* __restric
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int c = first; c < plan.num_pairs && tail_range_begin(plan, c) < unit1; ++c) {
     const int start = tail_range_begin(plan, c) > unit0 ? tail_range_begin(plan, c) : unit0;
-    const float* src = partial + split_slot_offset(c, start == unit0 ? 1 : 0, r / BM) + (size_t)(r % BM) * BN + cgroup * 8;
+    const float* src = partial + split_slot_offset(c, start == unit0 ? 1 : 0, sub, cta, subs) + (size_t)local * BN + cgroup * 8;
     const float4 lo = __ldcg(reinterpret_cast<const float4*>(src)), hi = __ldcg(reinterpret_cast<const float4*>(src + 4));
     acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
     acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
@@ -803,9 +841,9 @@ bool sm100_gemm_supported(const WeightView& w, int rank) {
   return w.blocksize == 64 && w.k % 64 == 0 && w.n % 64 == 0 && rank <= 64;
 }
 
-// Scratch for splitting the last wave: two fp32 partial tiles per CTA pair.
+// Scratch for splitting the last wave: two fp32 partial tiles (of the tall kind) per CTA pair.
 size_t sm100_split_bytes() {
-  return pair::split_slot_offset(sm_count() / 2, 0, 0) * sizeof(float);
+  return pair::split_slot_offset(sm_count() / 2, 0, 0, 0, 2) * sizeof(float);
 }
 
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
@@ -860,21 +898,34 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
   p.k = w.k;
   p.num_kb = (int)(contraction / BK);
   p.ext_steps = has_low ? rp / 16 : 0;
-  p.tiles_m = (int)((m + 2 * BM - 1) / (2 * BM));
   p.tiles_n = (int)((out_cols + BN - 1) / BN);
   p.nibble_high_first = w.nibble_order == MOLT_NIBBLE_HIGH_FIRST ? 1 : 0;
   p.wait_cycles = wait_limit_cycles();
   p.withhold = take_withheld_blocks();
 #ifdef MOLT_PAIR_TRACE
   {
-    const char* tr = getenv("MOLT_B200_TRACE_PTR");   // device pointer (decimal) of a 16 KB trace buffer
+    const char* tr = getenv("MOLT_B200_TRACE_PTR");   // device pointer (decimal) of a 24 KB trace buffer
     p.trace = tr != nullptr ? reinterpret_cast<unsigned long long*>(strtoull(tr, nullptr, 10)) : nullptr;
   }
 #endif
   for (int i = 0; i < 16; ++i) p.codebook[i] = w.codebook[i];
 
-  const long long tiles = (long long)p.tiles_m * p.tiles_n;
   const long long all_pairs = sm_count() / 2;
+  const long long blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
+  // Tile height.  A tall tile (512 tokens per pair) does two MMAs per decoded B tile and costs about 1.5 short-tile
+  // blocks per block, plus an epilogue that is only partly hidden (about 4.5 blocks' worth); what decides is the
+  // number of waves each height needs on this device.  (Measured on B200, 14336 x 4096 weight: 0.84 us against 0.53 us
+  // per block and tile; at 16384 tokens the tall tiles are 1.5 times faster, at 1024 tokens backward the short ones.)
+  const auto waves = [&](long long tiles) { return (tiles + all_pairs - 1) / all_pairs; };
+  const long long tiles_short = ((m + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
+  const long long tiles_tall = ((m + 4 * BM - 1) / (4 * BM)) * p.tiles_n;
+  int subs = 1;
+  if (flags & kGemmTallTiles) subs = 2;
+  else if (!(flags & kGemmShortTiles) && m > 2 * BM &&
+           waves(tiles_tall) * (blocks * 150 + 450) < waves(tiles_short) * blocks * 100)
+    subs = 2;
+  p.tiles_m = (int)((m + 2 * BM * subs - 1) / (2 * BM * subs));
+  const long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long pairs = all_pairs;
   if (tiles < pairs) pairs = tiles;
   // Whole waves run the static schedule; a last partial wave is split along the contraction when scratch was given.
@@ -883,17 +934,18 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
   {
     const bool allowed = split_ws != nullptr && !(flags & kGemmNoSplit);
     const bool forced = (flags & kGemmForceSplit) != 0;
-    const long long blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
     if (tiles < all_pairs) {
       // Fewer tiles than CTA pairs (few tokens): cutting all tiles along the contraction so that every pair of the device
       // gets an equal run of blocks was measured and is slower (14336 x 4096 weight, 32..256 tokens: 55-69 us against
       // 52-54 us) -- the fp32 partial tiles and the fix-up launch cost more than the shorter runs save.
     } else {
       const long long rem = tiles % pairs;
-      // Splitting costs about 40 us (fp32 partial tiles out and in again, one more launch).  It pays when the last wave
-      // is at most half full and every pair still gets a run of blocks long enough to fill its pipeline (measured on
-      // the 14336 x 4096 weight: backward at 4096 tokens -8 %, forward with its 65-block tiles no gain).
-      const bool worth_it = (rem * 2 <= pairs && rem * blocks / pairs >= 32) || forced;
+      // Splitting the last, partial wave saves the idle part of that wave and costs the fp32 partial tiles (out and in
+      // again) plus one more launch: about 38 us with short tiles, 50 us with tall ones (measured).  A tile takes about
+      // 0.58 us (short) or 0.80 us (tall) per contraction block.
+      const double tile_us = blocks * (subs == 2 ? 0.80 : 0.58) + (subs == 2 ? 4.0 : 0.0);
+      const double saved_us = (1.0 - (double)rem / (double)pairs) * tile_us;
+      const bool worth_it = saved_us > (subs == 2 ? 50.0 : 38.0) * 1.15 || forced;
       if (allowed && rem != 0 && tiles > pairs && worth_it && rem * blocks >= pairs && rem * blocks * pairs < (1LL << 30)) {
         p.full_tiles = (int)(tiles - rem);
         p.split_partial = reinterpret_cast<float*>(split_ws);
@@ -901,35 +953,39 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
     }
   }
   const int grid = (int)pairs * 2;
-  constexpr int LS = kLoadStagesDefault, BS = kBStagesDefault, SB = 1, GR = kDecodeGroupsDefault;
-  static thread_local bool configured[64][2] = {};
+  constexpr int BS = kBStagesDefault, SB = 1, GR = kDecodeGroupsDefault;
+  constexpr int LS1 = kLoadStagesDefault;                 // short tiles: one activation tile per block
+  constexpr int LS2 = 8, BS2 = 3;                         // tall tiles: two per block (four blocks deep), B ring of three
+  static_assert(smem_bytes(LS2, BS2, SB) <= 232448 && smem_bytes(LS1, BS, SB) <= 232448, "shared memory budget");
+  static thread_local bool configured[64][2][2] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));
-  const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0];
+  const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0][subs - 1];
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3((unsigned)pair_threads(GR));
-  cfg.dynamicSmemBytes = smem_bytes(LS, BS, SB);
+  cfg.dynamicSmemBytes = subs == 2 ? smem_bytes(LS2, BS2, SB) : smem_bytes(LS1, BS, SB);
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (backward) {
-    if (need_config)
-      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<true, LS, BS, SB, GR>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(LS, BS, SB)));
-    MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemm_sm100_pair_kernel<true, LS, BS, SB, GR>, map_in, map_packed, map_low,
-                                 map_ext, map_out, p));
-  } else {
-    if (need_config)
-      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<false, LS, BS, SB, GR>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(LS, BS, SB)));
-    MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemm_sm100_pair_kernel<false, LS, BS, SB, GR>, map_in, map_packed, map_low,
-                                 map_ext, map_out, p));
-  }
-  if (need_config) configured[dev][backward ? 1 : 0] = true;
+#define MOLT_PAIR_LAUNCH(BWD, SUB, LS, BSTAGES)                                                              \
+  do {                                                                                                       \
+    if (need_config)                                                                                         \
+      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<BWD, SUB, LS, BSTAGES, SB, GR>,              \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,                            \
+                                     (int)smem_bytes(LS, BSTAGES, SB)));                                     \
+    MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemm_sm100_pair_kernel<BWD, SUB, LS, BSTAGES, SB, GR>, map_in,    \
+                                 map_packed, map_low, map_ext, map_out, p));                                 \
+  } while (0)
+  if (backward && subs == 2) MOLT_PAIR_LAUNCH(true, 2, LS2, BS2);
+  else if (backward) MOLT_PAIR_LAUNCH(true, 1, LS1, BS);
+  else if (subs == 2) MOLT_PAIR_LAUNCH(false, 2, LS2, BS2);
+  else MOLT_PAIR_LAUNCH(false, 1, LS1, BS);
+#undef MOLT_PAIR_LAUNCH
+  if (need_config) configured[dev][backward ? 1 : 0][subs - 1] = true;
   if (int rc = launch_status("nf4_gemm_sm100_pair_kernel")) return rc;
   if (p.full_tiles < tiles) {
     WorkPlan plan;
@@ -940,8 +996,8 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
     plan.num_tiles = (int)tiles;
     plan.tail_units = (int)(tiles - p.full_tiles) * plan.blocks;
     plan.tail_begin = plan.tail_end = 0;
-    dim3 fgrid((unsigned)(2 * BM * (BN / 8) / 256), (unsigned)(tiles - p.full_tiles));
-    split_fixup_kernel<<<fgrid, 256, 0, s>>>(p.split_partial, plan, p.tiles_m, p.tiles_n, m, out_cols, out);
+    dim3 fgrid((unsigned)(2 * BM * subs * (BN / 8) / 256), (unsigned)(tiles - p.full_tiles));
+    split_fixup_kernel<<<fgrid, 256, 0, s>>>(p.split_partial, plan, p.tiles_m, p.tiles_n, subs, m, out_cols, out);
     return launch_status("split_fixup_kernel");
   }
   return MOLT_OK;

@@ -44,8 +44,9 @@ int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_
 //   backward: out[m, k] = in[m, n] . deq(W)   + low[m, 0..rp) . ext[0..rp, k]           (ext = bf16(A)   [rp, k])
 // low is bf16 [m, 64]; low == nullptr skips the low-rank block.
 // split_ws: sm100_split_bytes() bytes of scratch for splitting the tiles of the last wave, or NULL (plain schedule)
-// flags: kGemmNoSplit keeps the plain schedule, kGemmForceSplit splits whenever the shape allows it
-constexpr int kGemmNoSplit = 1, kGemmForceSplit = 2;
+// flags: kGemmNoSplit keeps the plain schedule, kGemmForceSplit splits whenever the shape allows it; kGemmTallTiles /
+// kGemmShortTiles force the tile height (512 / 256 tokens per CTA pair) instead of the library's own choice
+constexpr int kGemmNoSplit = 1, kGemmForceSplit = 2, kGemmTallTiles = 4, kGemmShortTiles = 8;
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
                void* split_ws, int flags, cudaStream_t s);

@@ -18,16 +18,18 @@ from tests.gpu_utils import TOL, make_case, run_forward
 pytestmark = pytest.mark.gpu
 
 
-def test_bounded_wait_expires_reports_and_recovers(native_library):
-    case = make_case(256, 128, 300, 8, seed=2)            # two pair tiles of three contraction blocks each
+@pytest.mark.parametrize("height", ["short", "tall"])
+def test_bounded_wait_expires_reports_and_recovers(native_library, height):
+    path = _native.PATH_TCGEN05 | (_native.PATH_TALL_TILES if height == "tall" else _native.PATH_SHORT_TILES)
+    case = make_case(256, 128, 300, 8, seed=2)            # one or two pair tiles of three contraction blocks each
     y_ref = oracle.nf4_lora_forward(case.x, case.weight, case.a, case.b, case.scaling)
-    y_good, _ = run_forward(case, _native.PATH_TCGEN05)
+    y_good, _ = run_forward(case, path)
     assert _native.read_status() == 0
     _native.set_option(_native.OPT_WAIT_LIMIT_US, 3000)   # 3 ms instead of one second
     try:
         _native.set_option(_native.OPT_WITHHOLD_BLOCKS, 1)
         begin = time.perf_counter()
-        run_forward(case, _native.PATH_TCGEN05)
+        run_forward(case, path)
         torch.cuda.synchronize()                          # the kernel returns by itself
         elapsed = time.perf_counter() - begin
         status = _native.read_status()
@@ -36,7 +38,7 @@ def test_bounded_wait_expires_reports_and_recovers(native_library):
         assert elapsed < 2.0
         assert _native.read_status() == 0                 # reading cleared it
         # the injection applied to one launch only; the context is intact and the next call is right again
-        y_again, _ = run_forward(case, _native.PATH_TCGEN05)
+        y_again, _ = run_forward(case, path)
         torch.cuda.synchronize()
         assert _native.read_status() == 0
         assert torch.equal(y_again, y_good)

@@ -94,19 +94,22 @@ def test_config2_gemv_against_oracle(config2, m):
     assert oracle.rel_frobenius(y, want) <= TOL
 
 
-def test_config2_backward_at_4096_tokens_with_the_natural_split(config2):
-    """The benchmarked backward: 256 output tiles on 74 CTA pairs, the tiles of the last wave split along the
-    contraction by the library's own choice.  dX on sampled rows (among them rows of the split tiles), dA and dB in
-    full."""
+def test_config2_backward_at_4096_tokens_on_every_schedule(config2):
+    """The benchmarked backward, as the library schedules it by itself (tall tiles on this device), and on the other
+    schedules the same call can take: short tiles with the last wave split along the contraction (256 tiles on 74 CTA
+    pairs) and short tiles on the plain schedule.  dX on sampled rows against the oracle, dA and dB in full."""
     from molt_b200.methods._linear import linear_backward
 
     c, m = config2, 4096
     x, dy = c.tokens(m, c.k), c.tokens(m, c.n)
     dx, da, db = linear_backward(c.desc(), x, dy, c.a, c.b, c.scaling, None, True, True, path=_native.PATH_AUTO)
+    short = _native.PATH_TCGEN05 | _native.PATH_SHORT_TILES
+    dx_split, _, _ = linear_backward(c.desc(), x, dy, c.a, c.b, c.scaling, None, True, False, path=short)
     dx_plain, _, _ = linear_backward(c.desc(), x, dy, c.a, c.b, c.scaling, None, True, False,
-                                     path=_native.PATH_TCGEN05 | _native.PATH_NO_SPLIT)
+                                     path=short | _native.PATH_NO_SPLIT)
     assert_clean_status()
-    assert not torch.equal(dx, dx_plain), "the split schedule was expected to run at this size"
+    assert not torch.equal(dx_split, dx_plain), "short tiles were expected to split their last wave at this size"
+    assert oracle.rel_frobenius(dx_split, dx_plain.float()) < 1e-3
     assert oracle.rel_frobenius(dx, dx_plain.float()) < 1e-3
     rows = _sample_rows(m, count=64, seed=7)
     # the last wave's tiles are the last in band order: rows of the last band, last column tiles; sample there too
@@ -115,6 +118,7 @@ def test_config2_backward_at_4096_tokens_with_the_natural_split(config2):
     dy_rows = dy[rows.cuda()].float().cpu()
     want_dx = dy_rows @ c.dense() + c.scaling * ((dy_rows @ b) @ a)
     assert oracle.rel_frobenius(dx[rows.cuda()], want_dx) <= TOL
+    assert oracle.rel_frobenius(dx_split[rows.cuda()], want_dx) <= TOL
     xf, dyf = x.float().cpu(), dy.float().cpu()
     want_da = c.scaling * (dyf @ b).t() @ xf          # reference streaming/engine.py:41-44
     want_db = c.scaling * dyf.t() @ (xf @ a.t())

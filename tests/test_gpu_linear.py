@@ -108,12 +108,13 @@ def test_short_contractions(native_library, n, k, m):
 
 @pytest.mark.parametrize("n,k", [(2560, 1024), (1024, 2560)])
 def test_split_last_wave(native_library, n, k):
-    """80 output tiles on 74 CTA pairs (forward for the first shape, backward for the second): the six tiles of the
+    """80 output tiles (of the short kind) on 74 CTA pairs (forward for the first shape, backward for the second): the six tiles of the
     last wave are cut along the contraction, leave the GEMM as fp32 partial tiles and are summed by the fix-up kernel
     (forced here: for tiles this short the library would keep the plain schedule).  Results must match the oracle
     and, up to the order of fp32 additions, the plain schedule."""
     case = make_case(n, k, 2048, 16, seed=n + k, nested=True, order="high-first")
-    split, plain = PATHS["tcgen05"] | _native.PATH_FORCE_SPLIT, PATHS["tcgen05"] | _native.PATH_NO_SPLIT
+    short = PATHS["tcgen05"] | _native.PATH_SHORT_TILES
+    split, plain = short | _native.PATH_FORCE_SPLIT, short | _native.PATH_NO_SPLIT
     _check_all(case, split)
     y_split, _ = run_forward(case, split)
     dx_split, da_split, db_split = run_backward(case, split)
@@ -123,6 +124,37 @@ def test_split_last_wave(native_library, n, k):
     assert oracle.rel_frobenius(dx_split, dx_plain.float()) < 1e-3
     assert not (torch.equal(y_split, y_plain) and torch.equal(dx_split, dx_plain))   # the split schedule really ran
     assert torch.equal(da_split, da_plain) and torch.equal(db_split, db_plain)
+    assert_clean_status()
+
+
+@pytest.mark.parametrize("height", ["tall", "short"])
+@pytest.mark.parametrize("n,k,m,rank", [(512, 320, 300, 16), (256, 128, 513, 8), (1536, 256, 1100, 64), (320, 1536, 2048, 16)])
+def test_tile_heights(native_library, height, n, k, m, rank):
+    """Both tile heights of the tensor-core GEMM (512 and 256 tokens per CTA pair), forced, on token counts that leave
+    the last tile ragged in either; results must match the oracle and each other up to fp32 summation order."""
+    flag = _native.PATH_TALL_TILES if height == "tall" else _native.PATH_SHORT_TILES
+    case = make_case(n, k, m, rank, seed=n + m, nested=(k % 256 == 0), order="high-first")
+    _check_all(case, PATHS["tcgen05"] | flag)
+    y_this, _ = run_forward(case, PATHS["tcgen05"] | flag)
+    y_auto, _ = run_forward(case, PATHS["tcgen05"])
+    assert oracle.rel_frobenius(y_this, y_auto.float()) < 1e-3
+
+
+@pytest.mark.parametrize("n,k", [(2560, 1024), (1024, 2560)])
+def test_split_last_wave_of_tall_tiles(native_library, n, k):
+    """80 tall tiles (4096 tokens) on 74 CTA pairs: the six tiles of the last wave are cut along the contraction; both
+    accumulators of every part go out as fp32 partial tiles and the fix-up kernel adds them."""
+    case = make_case(n, k, 4096, 16, seed=n + k + 1, nested=True, order="high-first")
+    split = PATHS["tcgen05"] | _native.PATH_FORCE_SPLIT | _native.PATH_TALL_TILES
+    plain = PATHS["tcgen05"] | _native.PATH_NO_SPLIT | _native.PATH_TALL_TILES
+    _check_all(case, split)
+    y_split, _ = run_forward(case, split)
+    dx_split, da_split, db_split = run_backward(case, split)
+    y_plain, _ = run_forward(case, plain)
+    dx_plain, da_plain, db_plain = run_backward(case, plain)
+    assert oracle.rel_frobenius(y_split, y_plain.float()) < 1e-3
+    assert oracle.rel_frobenius(dx_split, dx_plain.float()) < 1e-3
+    assert not (torch.equal(y_split, y_plain) and torch.equal(dx_split, dx_plain))   # the split schedule really ran
     assert_clean_status()
 
 
