@@ -912,45 +912,47 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
 
   const long long all_pairs = sm_count() / 2;
   const long long blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
-  // Tile height.  A tall tile (512 tokens per pair) does two MMAs per decoded B tile and costs about 1.5 short-tile
-  // blocks per block, plus an epilogue that is only partly hidden (about 4.5 blocks' worth); what decides is the
-  // number of waves each height needs on this device.  (Measured on B200, 14336 x 4096 weight: 0.84 us against 0.53 us
-  // per block and tile; at 16384 tokens the tall tiles are 1.5 times faster, at 1024 tokens backward the short ones.)
-  const auto waves = [&](long long tiles) { return (tiles + all_pairs - 1) / all_pairs; };
-  const long long tiles_short = ((m + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
-  const long long tiles_tall = ((m + 4 * BM - 1) / (4 * BM)) * p.tiles_n;
+  // Schedule: tile height (short = 256 tokens per pair, tall = 512: two MMAs per decoded B tile) and whether the tiles
+  // of a last, partial wave are split along the contraction.  Every admissible combination is costed with figures
+  // measured on B200 (14336 x 4096 and 8960 x 1536 weights): a tile takes 0.58 us (short) or 0.80 us (tall) per
+  // contraction block, a tall tile 4 us more for its partly exposed epilogue; splitting costs 38 us (short) or 50 us
+  // (tall) for the fp32 partial tiles and the extra launch.  The cheapest estimate wins.
   int subs = 1;
-  if (flags & kGemmTallTiles) subs = 2;
-  else if (!(flags & kGemmShortTiles) && m > 2 * BM &&
-           waves(tiles_tall) * (blocks * 150 + 450) < waves(tiles_short) * blocks * 100)
-    subs = 2;
+  bool split = false;
+  {
+    const bool may_split = split_ws != nullptr && !(flags & kGemmNoSplit);
+    const bool forced_split = (flags & kGemmForceSplit) != 0;
+    double best = -1.0;
+    for (int cand = 1; cand <= 2; ++cand) {
+      if (cand == 2 && ((flags & kGemmShortTiles) || m <= 2 * BM)) continue;
+      if (cand == 1 && (flags & kGemmTallTiles) && m > 0) continue;
+      const long long tiles_c = ((m + 2 * BM * cand - 1) / (2 * BM * cand)) * p.tiles_n;
+      const double tile_us = blocks * (cand == 2 ? 0.80 : 0.58) + (cand == 2 ? 4.0 : 0.0);
+      const long long full = tiles_c / all_pairs, rem = tiles_c % all_pairs;
+      const double plain_us = (double)(full + (rem != 0 ? 1 : 0)) * tile_us;
+      // a split needs whole waves in front of it, at least one block per pair, and indices that fit 32 bits
+      const bool can_split = may_split && full >= 1 && rem != 0 && rem * blocks >= all_pairs &&
+                             rem * blocks * all_pairs < (1LL << 30);
+      const double split_us = (double)full * tile_us + (double)rem / (double)all_pairs * tile_us + (cand == 2 ? 50.0 : 38.0);
+      const bool take_split = can_split && (forced_split || split_us < plain_us);
+      const double est = take_split ? split_us : plain_us;
+      if (best < 0.0 || est < best) {
+        best = est;
+        subs = cand;
+        split = take_split;
+      }
+    }
+  }
   p.tiles_m = (int)((m + 2 * BM * subs - 1) / (2 * BM * subs));
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long pairs = all_pairs;
   if (tiles < pairs) pairs = tiles;
-  // Whole waves run the static schedule; a last partial wave is split along the contraction when scratch was given.
+  // Whole waves run the static schedule; the tiles of a split last wave leave the kernel as fp32 partial tiles.
   p.full_tiles = (int)tiles;
   p.split_partial = nullptr;
-  {
-    const bool allowed = split_ws != nullptr && !(flags & kGemmNoSplit);
-    const bool forced = (flags & kGemmForceSplit) != 0;
-    if (tiles < all_pairs) {
-      // Fewer tiles than CTA pairs (few tokens): cutting all tiles along the contraction so that every pair of the device
-      // gets an equal run of blocks was measured and is slower (14336 x 4096 weight, 32..256 tokens: 55-69 us against
-      // 52-54 us) -- the fp32 partial tiles and the fix-up launch cost more than the shorter runs save.
-    } else {
-      const long long rem = tiles % pairs;
-      // Splitting the last, partial wave saves the idle part of that wave and costs the fp32 partial tiles (out and in
-      // again) plus one more launch: about 38 us with short tiles, 50 us with tall ones (measured).  A tile takes about
-      // 0.58 us (short) or 0.80 us (tall) per contraction block.
-      const double tile_us = blocks * (subs == 2 ? 0.80 : 0.58) + (subs == 2 ? 4.0 : 0.0);
-      const double saved_us = (1.0 - (double)rem / (double)pairs) * tile_us;
-      const bool worth_it = saved_us > (subs == 2 ? 50.0 : 38.0) * 1.15 || forced;
-      if (allowed && rem != 0 && tiles > pairs && worth_it && rem * blocks >= pairs && rem * blocks * pairs < (1LL << 30)) {
-        p.full_tiles = (int)(tiles - rem);
-        p.split_partial = reinterpret_cast<float*>(split_ws);
-      }
-    }
+  if (split) {
+    p.full_tiles = (int)(tiles - tiles % pairs);
+    p.split_partial = reinterpret_cast<float*>(split_ws);
   }
   const int grid = (int)pairs * 2;
   constexpr int BS = kBStagesDefault, SB = 1, GR = kDecodeGroupsDefault;
