@@ -196,6 +196,17 @@ int molt_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_
 int molt_ce_softmax_grad(void* logits, const int64_t* targets, float* row_loss, int64_t rows, int64_t vocab,
                          float grad_scale, uintptr_t stream);
 
+/* GEMM against a dense, frozen bf16 weight [n, k] (the LM head), on the tensor-core kernel of the NF4 linears with its B
+ * tiles loaded ready-made: contract_over_rows == 0: out[m, n] = in[m, k] . weight^T (logits = hidden . head^T);
+ * contract_over_rows != 0: out[m, k] = in[m, n] . weight (dhidden = dlogits . head).  bf16 in and out, fp32 accumulation;
+ * n and k multiples of 64.  workspace (optional, molt_dense_gemm_workspace_bytes()): scratch for splitting a partial last
+ * wave of tiles; flags: MOLT_PATH_NO_SPLIT / FORCE_SPLIT / TALL_TILES / SHORT_TILES or 0.
+ * Replaces the two F.linear calls around the cross-entropy kernels at reference
+ * kernels/frozen_linear_cross_entropy.py:181-236 (with molt_ce_softmax_grad between them). */
+size_t molt_dense_gemm_workspace_bytes(void);
+int molt_dense_gemm(const void* weight, int64_t n, int64_t k, const void* in, void* out, int64_t m,
+                    int contract_over_rows, void* workspace, size_t workspace_bytes, int flags, uintptr_t stream);
+
 /* Gated MLP block: gate = P_g(x), up = P_u(x), y = P_d(silu(gate) * up).
  * gate_out [m, inter] is always written (it is what the replay schedule saves); up_out may be NULL when the
  * caller re-materialises `up` in backward.  Replaces _ResidualRecipeGatedNF4LoRA.forward

@@ -518,6 +518,35 @@ extern "C" int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* l
                  reinterpret_cast<cudaStream_t>(stream), flags);
 }
 
+// ---- dense frozen weight (LM head) -------------------------------------------------------------------
+extern "C" size_t molt_dense_gemm_workspace_bytes(void) { return sm100_split_bytes() + 256; }
+
+extern "C" int molt_dense_gemm(const void* weight, int64_t n, int64_t k, const void* in, void* out, int64_t m,
+                               int contract_over_rows, void* workspace, size_t workspace_bytes, int flags,
+                               uintptr_t stream) {
+  MOLT_REQUIRE(weight && in && out, MOLT_E_VALUE, "molt_dense_gemm: NULL tensor pointer");
+  MOLT_REQUIRE(n > 0 && k > 0 && m >= 0, MOLT_E_VALUE, "molt_dense_gemm: bad shape");
+  MOLT_REQUIRE(n % 64 == 0 && k % 64 == 0, MOLT_E_CAPABILITY,
+               "molt_dense_gemm: weight dimensions must be multiples of 64 (got [%lld, %lld])", (long long)n, (long long)k);
+  MOLT_REQUIRE(aligned16(weight) && aligned16(in) && aligned16(out), MOLT_E_VALUE,
+               "molt_dense_gemm: tensors must be 16-byte aligned");
+  MOLT_REQUIRE((flags & ~(MOLT_PATH_NO_SPLIT | MOLT_PATH_FORCE_SPLIT | MOLT_PATH_TALL_TILES | MOLT_PATH_SHORT_TILES)) == 0,
+               MOLT_E_VALUE, "molt_dense_gemm: unknown flags 0x%x", flags);
+  if (m == 0) return MOLT_OK;
+  const int gemm_flags = ((flags & MOLT_PATH_NO_SPLIT) ? kGemmNoSplit : 0) | ((flags & MOLT_PATH_FORCE_SPLIT) ? kGemmForceSplit : 0) |
+                         ((flags & MOLT_PATH_TALL_TILES) ? kGemmTallTiles : 0) | ((flags & MOLT_PATH_SHORT_TILES) ? kGemmShortTiles : 0);
+  // the split scratch is optional: without it the GEMM keeps the plain schedule
+  unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+  void* split = nullptr;
+  if (ws != nullptr) {
+    const uintptr_t start = (reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255);
+    if (start + sm100_split_bytes() <= reinterpret_cast<uintptr_t>(ws) + workspace_bytes) split = reinterpret_cast<void*>(start);
+  }
+  return sm100_dense_gemm(contract_over_rows != 0, reinterpret_cast<const __nv_bfloat16*>(weight), n, k,
+                          reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), m, split,
+                          gemm_flags, reinterpret_cast<cudaStream_t>(stream));
+}
+
 // ---- gated MLP block -------------------------------------------------------------------------------
 static int check_proj(const char* who, const molt_lora_proj* p) {
   MOLT_REQUIRE(p != nullptr && p->w != nullptr && p->lora_a != nullptr && p->lora_b != nullptr, MOLT_E_VALUE,

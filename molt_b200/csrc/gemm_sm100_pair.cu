@@ -16,6 +16,10 @@
 // as soon as it is drained, so the next tile's first MMAs start early).  Short tiles (kSub = 1: 256 rows, two
 // accumulators used in turn) remain for small token counts and for shapes whose tall tiles quantise badly.
 //
+// Dense variant (kDense): the same pipeline for a frozen bf16 weight (the LM head): the second producer warp loads the
+// B half-tiles ready-made by TMA into the B ring, one decode warp merely relays "both operands of this CTA have landed"
+// to the leader, everything else (tall tiles, MMA issue, epilogue, split schedule) is shared.
+//
 // Per CTA: two TMA rings (16 KB activation tiles; 4 KB packed-code tiles, deeper) run several blocks ahead of a
 // separate ring of decoded B half-tiles, so the global-memory latency is not serialised with the decode.
 // Decode: a decoder thread owns one 64-element segment (one absmax) per block.  It first forms the sixteen values
@@ -91,9 +95,9 @@ constexpr uint32_t kTileBBytes = BNH * BK * 2;         // 16384
 constexpr uint32_t kStoreBytes = BM * 64 * 2;          // 16384
 constexpr int kLutWords = MOLT_PAIR_LUT_WORDS;
 constexpr uint32_t kLutBytes = kLutWords > 0 ? 256 * 16 * 8 : 0;   // [byte][16 copies] of float2 (both codebook values of a byte)
-constexpr uint32_t smem_bytes(int load_stages, int b_stages, int store_bufs) {
-  return load_stages * kLoadStageBytes + kCodeStages * kPackedBytes + b_stages * kTileBBytes +
-         store_bufs * kStoreBytes + kLutBytes + 512 /*barriers*/ + 1024 /*alignment*/;
+constexpr uint32_t smem_bytes(int load_stages, int b_stages, int store_bufs, bool dense = false) {
+  return load_stages * kLoadStageBytes + (dense ? 0 : kCodeStages * kPackedBytes) + b_stages * kTileBBytes +
+         store_bufs * kStoreBytes + (dense ? 0 : kLutBytes) + 512 /*barriers*/ + 1024 /*alignment*/;
 }
 
 struct Params {
@@ -288,7 +292,7 @@ __host__ __device__ __forceinline__ size_t split_slot_offset(int pair, int start
   return ((size_t)((pair * 2 + starts_tile) * subs + sub) * 2 + rank) * BM * BN;
 }
 
-template <bool BACKWARD, int kSub, int kLoadStages, int kBStages, int kStoreBufs, int kDecodeGroups>
+template <bool BACKWARD, bool kDense, int kSub, int kLoadStages, int kBStages, int kStoreBufs, int kDecodeGroups>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(kDecodeGroups), 1)
 nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_constant__ CUtensorMap map_packed,
                            const __grid_constant__ CUtensorMap map_low, const __grid_constant__ CUtensorMap map_ext,
@@ -301,15 +305,16 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   const uint32_t base = (raw + 1023u) & ~1023u;
   const uint32_t load0 = base;
   const uint32_t codes0 = load0 + kLoadStages * kLoadStageBytes;
-  const uint32_t btile0 = codes0 + kCodeStages * kPackedBytes;
+  const uint32_t btile0 = codes0 + (kDense ? 0 : kCodeStages * kPackedBytes);
   const uint32_t store0 = btile0 + kBStages * kTileBBytes;
   const uint32_t lut0 = store0 + kStoreBufs * kStoreBytes;
-  const uint32_t bar0 = lut0 + kLutBytes;
+  const uint32_t bar0 = lut0 + (kDense ? 0 : kLutBytes);
   auto bar_ldfull = [&](int s) { return bar0 + 8u * s; };
   // consumed[g % 8] completes when the MMAs of contraction block number g (counted per CTA across tiles) have
   // finished reading their operands; ONE commit per block releases both the load stage and the B stage, in both
   // CTAs.  Sixteen slots exceed every ring depth, so a waiter can never be lapped.
   constexpr int kConsumedSlots = 16;
+  static_assert(kBStages <= kCodeStages, "the dense variant reuses the code ring's barriers for its B stages");
   static_assert(kLoadStages < kConsumedSlots && kCodeStages < kConsumedSlots && kBStages < kConsumedSlots,
                 "ring deeper than the consumed slots");
   auto bar_consumed = [&](int g) { return bar0 + 8u * (kLoadStages + (g & (kConsumedSlots - 1))); };
@@ -343,7 +348,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     for (int s = 0; s < kLoadStages; ++s) mbar_init(bar_ldfull(s), 1);
     for (int s = 0; s < kCodeStages; ++s) mbar_init(bar_pkfull(s), 1);
     for (int g = 0; g < kConsumedSlots; ++g) mbar_init(bar_consumed(g), 1);
-    for (int s = 0; s < kBStages; ++s) mbar_init(bar_bfull(s), 8);   // 4 warps of one group x 2 CTAs
+    for (int s = 0; s < kBStages; ++s) mbar_init(bar_bfull(s), kDense ? 2 : 8);   // 4 warps of one group (dense: one relay) x 2 CTAs
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_accfull(b), 1);
       mbar_init(bar_accempty(b), 2 * kEpilogueWarps);
@@ -351,7 +356,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     for (int gr = 0; gr < kDecodeGroups; ++gr) mbar_init(bar_ext(gr), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (kLutWords > 0) {
+  if (kLutWords > 0 && !kDense) {
     // byte -> (first element, second element) fp32 codebook values; 16 copies so that lane l reads bank pair l % 16
     float2* lut_ptr = reinterpret_cast<float2*>(smem_dyn + (lut0 - raw));
     for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
@@ -389,7 +394,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     // iteration time bounds the whole pipeline.
     const bool codes = warp == kCodeWarp;
     static_assert(kLoadStages % kSub == 0, "the activation ring holds whole blocks");
-    const int depth = codes ? kCodeStages : kLoadStages / kSub;   // in contraction blocks
+    const int depth = codes ? (kDense ? kBStages : kCodeStages) : kLoadStages / kSub;   // in contraction blocks
     if (lane == 0) {
       // Failure injection for tests: with p.withhold = w the last w blocks of this CTA are never requested, so the
       // consumers' bounded waits run out.  total_blocks is only computed when the injection is on.
@@ -409,7 +414,18 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         for (int kb = item.kb0; kb < item.kb1 && t < total_blocks; ++kb, ++t) {
           if (t >= depth) ok = wait_on(bar_consumed(t - depth), consumed_parity(t - depth), 1);
           if (!ok) break;
-          if (codes) {
+          if (codes && kDense) {
+            // the B half-tile itself, straight into the B ring (bar_pkfull doubles as "B stage has landed")
+            const uint32_t bt = btile0 + (uint32_t)stage * kTileBBytes;
+            mbar_expect_tx(bar_pkfull(stage), kTileBBytes);
+            if (!BACKWARD) {
+              tma_load_2d(bt, &map_packed, kb * BK, col0, bar_pkfull(stage));
+            } else {
+              tma_load_2d(bt, &map_packed, col0, kb * BK, bar_pkfull(stage));
+              tma_load_2d(bt + 8192u, &map_packed, col0 + 64, kb * BK, bar_pkfull(stage));
+            }
+            if (++stage == kBStages) stage = 0;
+          } else if (codes) {
             MOLT_TRACE(8, t);
             if (kb < p.num_kb) {
               const uint32_t pk_dst = codes0 + (uint32_t)stage * kPackedBytes;
@@ -513,6 +529,28 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         }
       }
       __syncwarp();
+    }
+  } else if (kDense && is_decode_warp(warp)) {
+    // ================= dense variant: one warp relays "this CTA's operands of block g have landed" =================
+    if (decode_warp_index(warp) == 0) {
+      const uint32_t bfull_remote_base = map_to_cta(bar_bfull(0), 0);
+      int g = 0, bs = 0;
+      uint32_t bphase = 0;
+      bool ok = true;
+      for (WorkItem item = first_item(plan); item.valid && ok; next_item(plan, item)) {
+        for (int kb = item.kb0; kb < item.kb1 && ok; ++kb, ++g) {
+          ok = wait_on(bar_pkfull(bs), bphase, 5);
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub) {
+            const int a = g * kSub + sub;
+            ok = ok && wait_on(bar_ldfull(a % kLoadStages), (uint32_t)((a / kLoadStages) & 1), 9);
+          }
+          if (!ok) break;
+          __syncwarp();
+          if (lane == 0) mbar_arrive_remote(bfull_remote_base + 8u * (uint32_t)bs);
+          if (++bs == kBStages) { bs = 0; bphase ^= 1u; }
+        }
+      }
     }
   } else if (is_decode_warp(warp) && decode_warp_index(warp) < 4 * kDecodeGroups) {
     // ================= NF4 decoders =================
@@ -846,6 +884,10 @@ size_t sm100_split_bytes() {
   return pair::split_slot_offset(sm_count() / 2, 0, 0, 0, 2) * sizeof(float);
 }
 
+int run_pair_gemm(bool backward, bool dense, pair::Params& p, const CUtensorMap& map_in, const CUtensorMap& map_packed,
+                  const CUtensorMap& map_low, const CUtensorMap& map_ext, const CUtensorMap& map_out,
+                  __nv_bfloat16* out, long long m, long long out_cols, void* split_ws, int flags, cudaStream_t s);
+
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
                void* split_ws, int flags, cudaStream_t s) {
@@ -891,15 +933,58 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
   Params p;
   p.packed = w.packed;
   p.absmax = absmax_f32;
-  p.status = device_status_word();
-  if (p.status == nullptr) return fail(MOLT_E_RUNTIME, "tcgen05 GEMM: no device status word");
   p.m = m;
   p.n = w.n;
   p.k = w.k;
   p.num_kb = (int)(contraction / BK);
   p.ext_steps = has_low ? rp / 16 : 0;
-  p.tiles_n = (int)((out_cols + BN - 1) / BN);
   p.nibble_high_first = w.nibble_order == MOLT_NIBBLE_HIGH_FIRST ? 1 : 0;
+  for (int i = 0; i < 16; ++i) p.codebook[i] = w.codebook[i];
+  return run_pair_gemm(backward, false, p, map_in, map_packed, map_low, map_ext, map_out, out, m, out_cols, split_ws,
+                       flags, s);
+}
+
+// out[m, n] = in[m, k] . weight[n, k]^T (forward) or out[m, k] = in[m, n] . weight[n, k] (backward) for a dense bf16
+// weight: the same kernel with its B tiles loaded ready-made (n, k multiples of 64).
+int sm100_dense_gemm(bool backward, const __nv_bfloat16* weight, long long n, long long k, const __nv_bfloat16* in,
+                     __nv_bfloat16* out, long long m, void* split_ws, int flags, cudaStream_t s) {
+  using namespace pair;
+  if (n % 64 != 0 || k % 64 != 0 || (reinterpret_cast<uintptr_t>(weight) & 15) != 0)
+    return fail(MOLT_E_CAPABILITY, "dense tcgen05 GEMM: n and k must be multiples of 64 and the weight 16-byte aligned");
+  const long long contraction = backward ? n : k;
+  const long long out_cols = backward ? k : n;
+  CUtensorMap map_in, map_weight, map_out;
+  if (int rc = make_tensor_map(&map_in, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, in, contraction, m, contraction * 2, BK, BM,
+                               CU_TENSOR_MAP_SWIZZLE_128B, "activations"))
+    return rc;
+  // forward: K-major half-tiles of 128 weight rows x 64 columns; backward: MN-major, two boxes of 64 rows x 64 columns
+  if (int rc = make_tensor_map(&map_weight, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, weight, k, n, k * 2, 64,
+                               backward ? 64 : BNH, CU_TENSOR_MAP_SWIZZLE_128B, "dense weight"))
+    return rc;
+  if (int rc = make_tensor_map(&map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, out_cols, m, out_cols * 2, 64, BM,
+                               CU_TENSOR_MAP_SWIZZLE_128B, "output"))
+    return rc;
+  Params p;
+  p.packed = nullptr;
+  p.absmax = nullptr;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.num_kb = (int)(contraction / BK);
+  p.ext_steps = 0;
+  p.nibble_high_first = 0;
+  for (int i = 0; i < 16; ++i) p.codebook[i] = 0.f;
+  return run_pair_gemm(backward, true, p, map_in, map_weight, map_in, map_in, map_out, out, m, out_cols, split_ws, flags, s);
+}
+
+// Schedule and launch, shared by the NF4 and the dense variant.
+int run_pair_gemm(bool backward, bool dense, pair::Params& p, const CUtensorMap& map_in, const CUtensorMap& map_packed,
+                  const CUtensorMap& map_low, const CUtensorMap& map_ext, const CUtensorMap& map_out,
+                  __nv_bfloat16* out, long long m, long long out_cols, void* split_ws, int flags, cudaStream_t s) {
+  using namespace pair;
+  p.status = device_status_word();
+  if (p.status == nullptr) return fail(MOLT_E_RUNTIME, "tcgen05 GEMM: no device status word");
+  p.tiles_n = (int)((out_cols + BN - 1) / BN);
   p.wait_cycles = wait_limit_cycles();
   p.withhold = take_withheld_blocks();
 #ifdef MOLT_PAIR_TRACE
@@ -908,7 +993,6 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
     p.trace = tr != nullptr ? reinterpret_cast<unsigned long long*>(strtoull(tr, nullptr, 10)) : nullptr;
   }
 #endif
-  for (int i = 0; i < 16; ++i) p.codebook[i] = w.codebook[i];
 
   const long long all_pairs = sm_count() / 2;
   const long long blocks = p.num_kb + (p.ext_steps > 0 ? 1 : 0);
@@ -958,36 +1042,46 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
   constexpr int BS = kBStagesDefault, SB = 1, GR = kDecodeGroupsDefault;
   constexpr int LS1 = kLoadStagesDefault;                 // short tiles: one activation tile per block
   constexpr int LS2 = 8, BS2 = 3;                         // tall tiles: two per block (four blocks deep), B ring of three
-  static_assert(smem_bytes(LS2, BS2, SB) <= 232448 && smem_bytes(LS1, BS, SB) <= 232448, "shared memory budget");
-  static thread_local bool configured[64][2][2] = {};
+  constexpr int DLS1 = 6, DBS1 = 7, DLS2 = 8, DBS2 = 5;   // dense variant: no code ring and no table, deeper B rings
+  static_assert(smem_bytes(LS2, BS2, SB) <= 232448 && smem_bytes(LS1, BS, SB) <= 232448 &&
+                smem_bytes(DLS1, DBS1, SB, true) <= 232448 && smem_bytes(DLS2, DBS2, SB, true) <= 232448,
+                "shared memory budget");
+  static thread_local bool configured[64][2][2][2] = {};
   int dev = 0;
   MOLT_CUDA(cudaGetDevice(&dev));
-  const bool need_config = dev >= 0 && dev < 64 && !configured[dev][backward ? 1 : 0][subs - 1];
+  const bool need_config = dev >= 0 && dev < 64 && !configured[dev][dense ? 1 : 0][backward ? 1 : 0][subs - 1];
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3((unsigned)pair_threads(GR));
-  cfg.dynamicSmemBytes = subs == 2 ? smem_bytes(LS2, BS2, SB) : smem_bytes(LS1, BS, SB);
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-#define MOLT_PAIR_LAUNCH(BWD, SUB, LS, BSTAGES)                                                              \
+#define MOLT_PAIR_LAUNCH(BWD, DENSE, SUB, LS, BSTAGES)                                                       \
   do {                                                                                                       \
+    cfg.dynamicSmemBytes = smem_bytes(LS, BSTAGES, SB, DENSE);                                               \
     if (need_config)                                                                                         \
-      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<BWD, SUB, LS, BSTAGES, SB, GR>,              \
+      MOLT_CUDA(cudaFuncSetAttribute(nf4_gemm_sm100_pair_kernel<BWD, DENSE, SUB, LS, BSTAGES, SB, GR>,       \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,                            \
-                                     (int)smem_bytes(LS, BSTAGES, SB)));                                     \
-    MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemm_sm100_pair_kernel<BWD, SUB, LS, BSTAGES, SB, GR>, map_in,    \
-                                 map_packed, map_low, map_ext, map_out, p));                                 \
+                                     (int)smem_bytes(LS, BSTAGES, SB, DENSE)));                              \
+    MOLT_CUDA(cudaLaunchKernelEx(&cfg, nf4_gemm_sm100_pair_kernel<BWD, DENSE, SUB, LS, BSTAGES, SB, GR>,     \
+                                 map_in, map_packed, map_low, map_ext, map_out, p));                         \
   } while (0)
-  if (backward && subs == 2) MOLT_PAIR_LAUNCH(true, 2, LS2, BS2);
-  else if (backward) MOLT_PAIR_LAUNCH(true, 1, LS1, BS);
-  else if (subs == 2) MOLT_PAIR_LAUNCH(false, 2, LS2, BS2);
-  else MOLT_PAIR_LAUNCH(false, 1, LS1, BS);
+  if (!dense) {
+    if (backward && subs == 2) MOLT_PAIR_LAUNCH(true, false, 2, LS2, BS2);
+    else if (backward) MOLT_PAIR_LAUNCH(true, false, 1, LS1, BS);
+    else if (subs == 2) MOLT_PAIR_LAUNCH(false, false, 2, LS2, BS2);
+    else MOLT_PAIR_LAUNCH(false, false, 1, LS1, BS);
+  } else {
+    if (backward && subs == 2) MOLT_PAIR_LAUNCH(true, true, 2, DLS2, DBS2);
+    else if (backward) MOLT_PAIR_LAUNCH(true, true, 1, DLS1, DBS1);
+    else if (subs == 2) MOLT_PAIR_LAUNCH(false, true, 2, DLS2, DBS2);
+    else MOLT_PAIR_LAUNCH(false, true, 1, DLS1, DBS1);
+  }
 #undef MOLT_PAIR_LAUNCH
-  if (need_config) configured[dev][backward ? 1 : 0][subs - 1] = true;
+  if (need_config) configured[dev][dense ? 1 : 0][backward ? 1 : 0][subs - 1] = true;
   if (int rc = launch_status("nf4_gemm_sm100_pair_kernel")) return rc;
   if (p.full_tiles < tiles) {
     WorkPlan plan;

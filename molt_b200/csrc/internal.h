@@ -50,6 +50,10 @@ constexpr int kGemmNoSplit = 1, kGemmForceSplit = 2, kGemmTallTiles = 4, kGemmSh
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
                void* split_ws, int flags, cudaStream_t s);
+// the same kernel for a dense bf16 weight [n, k] (B tiles loaded ready-made): forward out[m, n] = in . weight^T,
+// backward out[m, k] = in[m, n] . weight
+int sm100_dense_gemm(bool backward, const __nv_bfloat16* weight, long long n, long long k, const __nv_bfloat16* in,
+                     __nv_bfloat16* out, long long m, void* split_ws, int flags, cudaStream_t s);
 size_t sm100_split_bytes();
 size_t workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank, bool with_optional);
 bool sm100_gemm_supported(const WeightView& w, int rank);

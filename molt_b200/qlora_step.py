@@ -185,29 +185,43 @@ class DecoderLayer(nn.Module):
         return x + self.mlp.fused(normed.reshape(b * s, w), rematerialize_up=replay_up).view(b, s, w)
 
 
+def dense_gemm(weight: torch.Tensor, x: torch.Tensor, contract_over_rows: bool, flags: int = 0) -> torch.Tensor:
+    """``x @ weight.T`` (or ``x @ weight`` with ``contract_over_rows``) for a frozen bf16 weight ``[n, k]`` on the library's
+    tensor-core kernel (the NF4 linears' kernel with ready-made B tiles)."""
+    n, k = int(weight.shape[0]), int(weight.shape[1])
+    m = int(x.shape[0])
+    lib = _native.library()
+    out = torch.empty((m, k if contract_over_rows else n), dtype=torch.bfloat16, device=x.device)
+    ws = _native.workspace(lib.molt_dense_gemm_workspace_bytes(), x.device)
+    with torch.cuda.device(x.device):
+        _native.check(lib.molt_dense_gemm(weight.data_ptr(), n, k, x.data_ptr(), out.data_ptr(), m, int(contract_over_rows),
+                                          ws.data_ptr(), ws.numel(), int(flags), _native.stream_handle(x.device)))
+    return out
+
+
 class _FrozenHeadLoss(torch.autograd.Function):
     """Mean token cross-entropy through a frozen bf16 LM head, in row chunks, without keeping the logits:
-    logits = h . head^T (cuBLAS), then one fused kernel turns the bf16 logits in place into the softmax gradient
-    and emits the per-row loss, then dh = grad . head (the chunked scheme of reference
-    kernels/frozen_linear_cross_entropy.py:181-236)."""
+    logits = h . head^T, then one fused kernel turns the bf16 logits in place into the softmax gradient and emits the
+    per-row loss, then dh = grad . head -- both GEMMs on the library's dense tensor-core kernel (the scheme of reference
+    kernels/frozen_linear_cross_entropy.py:181-236; with 180 GB of HBM a chunk is the whole micro-batch by default)."""
 
     @staticmethod
     def forward(ctx, hidden, head, targets, chunk, denominator):
-        from molt_b200 import _native
-
         lib = _native.library()
         rows, vocab = hidden.shape[0], head.shape[0]
         grad = torch.empty_like(hidden)
         row_loss = torch.empty(rows, device=hidden.device, dtype=torch.float32)
         targets = targets.contiguous()
+        hidden = hidden.contiguous()
+        native = hidden.dtype == torch.bfloat16 and head.dtype == torch.bfloat16 and vocab % 64 == 0 and hidden.shape[1] % 64 == 0
         for start in range(0, rows, chunk):
             h = hidden[start:start + chunk]
-            logits = h @ head.t()
+            logits = dense_gemm(head, h, False) if native else h @ head.t()
             with torch.cuda.device(hidden.device):
                 _native.check(lib.molt_ce_softmax_grad(
                     logits.data_ptr(), targets[start:start + chunk].data_ptr(), row_loss[start:start + chunk].data_ptr(),
                     logits.shape[0], vocab, 1.0 / denominator, _native.stream_handle(hidden.device)))
-            grad[start:start + chunk] = logits @ head
+            grad[start:start + chunk] = dense_gemm(head, logits, True) if native else logits @ head
         ctx.save_for_backward(grad)
         return row_loss.sum() / denominator
 
@@ -228,6 +242,7 @@ class SyntheticDecoder(nn.Module):
                                  requires_grad=False)
         self.layers = nn.ModuleList(DecoderLayer(shape, gen, device) for _ in range(layers or shape.layers))
         self.final_norm = RMSNorm(shape.hidden, device)
+        self.head_chunk = 8192   # rows of logits alive at a time (8192 x 151936 bf16 = 2.5 GB at config 4's vocabulary)
         inv = 1.0 / (shape.rope_theta ** (torch.arange(0, shape.head_dim, 2, device=device).float() / shape.head_dim))
         angles = torch.outer(torch.arange(shape.seq_len, device=device).float(), inv)
         angles = torch.cat((angles, angles), dim=-1)
@@ -247,7 +262,7 @@ class SyntheticDecoder(nn.Module):
                     return grad
             x = layer(x, self.cos, self.sin, replay_up, hook)
         hidden = self.final_norm(x).reshape(-1, self.shape.hidden)
-        return _FrozenHeadLoss.apply(hidden, self.head, targets.reshape(-1), 1024, float(global_tokens))
+        return _FrozenHeadLoss.apply(hidden, self.head, targets.reshape(-1), self.head_chunk, float(global_tokens))
 
 
 class QLoRAStep:

@@ -215,3 +215,24 @@ def test_fused_adamw_matches_torch(native_library):
         ref.step()
     for p, q in zip(ours, theirs):
         torch.testing.assert_close(p.detach(), q.detach(), rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("n,k,m", [(1024, 256, 300), (151936, 1536, 512), (4096, 1024, 4096), (320, 64, 1)])
+@pytest.mark.parametrize("over_rows", [False, True])
+def test_dense_gemm_matches_fp32_matmul(native_library, n, k, m, over_rows):
+    """The frozen-head GEMMs (logits = h . head^T and dh = dlogits . head) on the library's dense tensor-core kernel against
+    an fp32 matmul of the same bf16 operands; tolerance 1e-2 relative Frobenius like the linears (measured ~2e-3)."""
+    from molt_b200 import _native
+    from molt_b200.qlora_step import dense_gemm
+    from oracle import molt_oracle as oracle
+
+    gen = torch.Generator(device="cuda").manual_seed(n + k + m)
+    weight = (torch.randn(n, k, device="cuda", generator=gen) * 0.05).bfloat16()
+    x = torch.randn(m, n if over_rows else k, device="cuda", generator=gen).bfloat16()
+    if n > 100000 and over_rows:
+        x *= 0.01          # keep the long contraction's result in a comfortable range
+    for flags in (0, _native.PATH_SHORT_TILES, _native.PATH_TALL_TILES | _native.PATH_FORCE_SPLIT):
+        got = dense_gemm(weight, x, over_rows, flags)
+        want = x.float() @ (weight.float() if over_rows else weight.float().t())
+        assert oracle.rel_frobenius(got, want) <= 1e-2, flags
+    assert _native.read_status() == 0
