@@ -680,6 +680,36 @@ def extras(lib, device, desc, packed, state, lora_a, lora_b, peaks):
     del copies
     out["forward_sweep_config2"] = sweep
 
+    # per-shape table of the projections of BASELINE configs 3 / 4 at 8192 tokens: forward linear (low-rank term and
+    # side kernels included) and the input-gradient GEMM alone
+    shapes = []
+    for n, k in ((8960, 1536), (1536, 8960), (1536, 1536), (256, 1536)):
+        w = torch.randn(n, k, device=device, generator=gen) * 0.02
+        from molt_b200.methods import quantize_nf4
+        pk, st = quantize_nf4(w, 64, False)
+        d = weight_desc(pk, st)
+        a = torch.randn(RANK, k, device=device, generator=gen) * 0.01
+        b = torch.randn(n, RANK, device=device, generator=gen) * 0.01
+        m = 8192
+        x = torch.randn(m, k, device=device, generator=gen).bfloat16()
+        dy = torch.randn(m, n, device=device, generator=gen).bfloat16()
+        y = torch.empty(m, n, device=device, dtype=torch.bfloat16)
+        dx = torch.empty(m, k, device=device, dtype=torch.bfloat16)
+        ws_bytes = max(lib.molt_workspace_bytes(_native.OP_LORA_FWD, m, n, k, RANK), lib.molt_workspace_bytes(_native.OP_DX, m, n, k, RANK))
+        ws = torch.empty(ws_bytes, device=device, dtype=torch.uint8)
+        stream = _native.stream_handle(device)
+        fwd_ms = event_time_ms(lambda: _native.check(lib.molt_nf4_lora_fwd(
+            ctypes.byref(d), x.data_ptr(), a.data_ptr(), b.data_ptr(), SCALING, RANK, y.data_ptr(), m, None, ws.data_ptr(),
+            ws_bytes, _native.PATH_AUTO, stream)), iters=10, warmup=3)
+        dx_ms = event_time_ms(lambda: _native.check(lib.molt_nf4_dx(
+            ctypes.byref(d), dy.data_ptr(), None, None, 0, 0.0, 0, dx.data_ptr(), m, ws.data_ptr(), ws_bytes,
+            _native.PATH_AUTO, stream)), iters=10, warmup=3)
+        flops = 2.0 * m * n * k
+        shapes.append({"n": n, "k": k, "m": m, "forward_ms": fwd_ms, "forward_frac_bf16_peak": flops / fwd_ms / 1e9 / peaks["bf16_tflops"],
+                       "dx_gemm_ms": dx_ms, "dx_gemm_frac_bf16_peak": flops / dx_ms / 1e9 / peaks["bf16_tflops"]})
+        del w, pk, x, dy, y, dx, ws
+    out["projection_shapes_config3_4"] = shapes
+
     rows, inter, hidden = 8192, 8960, 1536
     g = torch.randn(rows, inter, device=device, generator=gen).bfloat16()
     u = torch.randn(rows, inter, device=device, generator=gen).bfloat16()

@@ -90,7 +90,10 @@ constexpr int pair_threads(int groups) { return pair_warps(groups) * 32; }
 constexpr uint32_t kTileABytes = BM * BK * 2;          // 16384
 constexpr uint32_t kPackedBytes = BNH * BK / 2;        // 4096
 constexpr uint32_t kLoadStageBytes = kTileABytes;      // activation ring stage
-constexpr int kCodeStages = 8;                         // ring of packed-code tiles; runs further ahead than the activations
+#ifndef MOLT_PAIR_CODE_STAGES
+#define MOLT_PAIR_CODE_STAGES 8
+#endif
+constexpr int kCodeStages = MOLT_PAIR_CODE_STAGES;                         // ring of packed-code tiles; runs further ahead than the activations
 constexpr uint32_t kTileBBytes = BNH * BK * 2;         // 16384
 constexpr uint32_t kStoreBytes = BM * 64 * 2;          // 16384
 constexpr int kLutWords = MOLT_PAIR_LUT_WORDS;
@@ -314,9 +317,15 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
   // finished reading their operands; ONE commit per block releases both the load stage and the B stage, in both
   // CTAs.  Sixteen slots exceed every ring depth, so a waiter can never be lapped.
   constexpr int kConsumedSlots = 16;
-  static_assert(kBStages <= kCodeStages, "the dense variant reuses the code ring's barriers for its B stages");
+  constexpr int kPkBarriers = kDense ? kBStages : kCodeStages;   // the dense variant uses these barriers for its B stages
   static_assert(kLoadStages < kConsumedSlots && kCodeStages < kConsumedSlots && kBStages < kConsumedSlots,
                 "ring deeper than the consumed slots");
+  // A decode group starts block g once block g - kBStages has been consumed, so it runs at most kBStages blocks ahead
+  // of the consumed front.  Its parity waits on the code and activation rings are only meaningful if the previous use
+  // of the slot (block g - depth) lies behind that front: both rings must be at least kBStages blocks deep.  (The dense
+  // variant has one relay warp that takes the blocks in order, so it cannot run ahead.)
+  static_assert(kDense || (kBStages <= kCodeStages && kBStages <= kLoadStages / kSub),
+                "B ring deeper than the code ring or the activation ring: a decode group could pass a stale phase");
   auto bar_consumed = [&](int g) { return bar0 + 8u * (kLoadStages + (g & (kConsumedSlots - 1))); };
   auto bar_bfull = [&](int s) { return bar0 + 8u * (kLoadStages + kConsumedSlots + s); };          // used in the leader
   auto bar_accfull = [&](int b) { return bar0 + 8u * (kLoadStages + kConsumedSlots + kBStages + b); };
@@ -346,7 +355,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     plan_s.tail_begin = tail_range_begin(plan_s, plan_s.pair_id);
     plan_s.tail_end = tail_range_begin(plan_s, plan_s.pair_id + 1);
     for (int s = 0; s < kLoadStages; ++s) mbar_init(bar_ldfull(s), 1);
-    for (int s = 0; s < kCodeStages; ++s) mbar_init(bar_pkfull(s), 1);
+    for (int s = 0; s < kPkBarriers; ++s) mbar_init(bar_pkfull(s), 1);
     for (int g = 0; g < kConsumedSlots; ++g) mbar_init(bar_consumed(g), 1);
     for (int s = 0; s < kBStages; ++s) mbar_init(bar_bfull(s), kDense ? 2 : 8);   // 4 warps of one group (dense: one relay) x 2 CTAs
     for (int b = 0; b < 2; ++b) {
@@ -441,6 +450,9 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
 #pragma unroll
             for (int sub = 0; sub < kSub; ++sub) {
               const uint32_t a_dst = load0 + (uint32_t)(stage + sub) * kLoadStageBytes;
+#ifdef MOLT_PAIR_EXP_HALF_A      // timing experiment: the second activation tile of a block is not loaded (results are wrong)
+              if (sub == 1) { mbar_arrive(bar_ldfull(stage + sub)); continue; }
+#endif
               mbar_expect_tx(bar_ldfull(stage + sub), kTileABytes);
               if (kb < p.num_kb) tma_load_2d(a_dst, &map_in, kb * BK, row0 + sub * 2 * BM, bar_ldfull(stage + sub));
               else tma_load_2d(a_dst, &map_low, 0, row0 + sub * 2 * BM, bar_ldfull(stage + sub));
@@ -1041,7 +1053,11 @@ int run_pair_gemm(bool backward, bool dense, pair::Params& p, const CUtensorMap&
   const int grid = (int)pairs * 2;
   constexpr int BS = kBStagesDefault, SB = 1, GR = kDecodeGroupsDefault;
   constexpr int LS1 = kLoadStagesDefault;                 // short tiles: one activation tile per block
-  constexpr int LS2 = 8, BS2 = 3;                         // tall tiles: two per block (four blocks deep), B ring of three
+  #ifndef MOLT_PAIR_TALL_LS
+#define MOLT_PAIR_TALL_LS (kLutWords > 0 ? 6 : 8)
+#define MOLT_PAIR_TALL_BS 3
+#endif
+  constexpr int LS2 = MOLT_PAIR_TALL_LS, BS2 = MOLT_PAIR_TALL_BS;     // tall tiles: two per block (four blocks deep; three beside a table), B ring of three
   constexpr int DLS1 = 6, DBS1 = 7, DLS2 = 8, DBS2 = 5;   // dense variant: no code ring and no table, deeper B rings
   static_assert(smem_bytes(LS2, BS2, SB) <= 232448 && smem_bytes(LS1, BS, SB) <= 232448 &&
                 smem_bytes(DLS1, DBS1, SB, true) <= 232448 && smem_bytes(DLS2, DBS2, SB, true) <= 232448,

@@ -34,12 +34,28 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// try_wait that lets the hardware park the thread for up to hint_ns before it answers
+__device__ __forceinline__ bool mbar_try_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait: gives up after limit_cycles SM clock cycles.  Returns false when the wait expired or another role
 // of the CTA already gave up; the first to give up records (code, where, block) in the device status word.
+// Waiting warps share issue slots with the working ones, so the loop is kept short: the thread is parked inside
+// try_wait, and the abort flag and the clock are looked at once in sixteen rounds.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
                                           int where, long long limit_cycles) {
   if (mbar_try(bar, parity)) return true;
   const long long start = clock64();
+#ifdef MOLT_SPIN_OLD
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
@@ -49,6 +65,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+#else
+  for (;;) {
+#pragma unroll 1
+    for (int spin = 0; spin < 16; ++spin)
+      if (mbar_try_parked(bar, parity, 4000u)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - start > limit_cycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, (kStatusTimeout << 24) | (where << 16) | (int)(blockIdx.x & 0xffff));
+      return false;
+    }
+  }
+#endif
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
