@@ -38,17 +38,20 @@ extern "C" {
 #define MOLT_DTYPE_BF16 0
 #define MOLT_DTYPE_F32 1
 
-/* kernel selection for the linear ops; AUTO picks GEMV for M <= 16, the tcgen05 kernels for
- * aligned shapes (K % 64 == 0, N % 64 == 0, blocksize 64, rank <= 64) and the general kernels otherwise. */
+/* kernel selection for the linear ops; for aligned shapes (K % 64 == 0, N % 64 == 0, blocksize 64, rank <= 64) AUTO
+ * picks, forward, GEMV for M <= 16 and the few-token kernel for M <= 64, else the tcgen05 GEMM; the general kernels
+ * for every other shape. */
 #define MOLT_PATH_AUTO 0
 #define MOLT_PATH_GENERAL 1
 #define MOLT_PATH_TCGEN05 2
 #define MOLT_PATH_GEMV 3
+#define MOLT_PATH_FEW_TOKENS 4 /* forward, M <= 128: tcgen05 with the weight rows as the MMA rows and the tokens as its columns */
 /* Optional flags, OR-ed onto a path: schedule of the tensor-core GEMMs when the last wave of output tiles is partial. */
 #define MOLT_PATH_NO_SPLIT 0x100    /* keep the plain tile schedule                                      */
 #define MOLT_PATH_FORCE_SPLIT 0x200 /* cut the tiles of the last wave along the contraction whenever the shape allows it */
 #define MOLT_PATH_TALL_TILES 0x400  /* tensor-core GEMMs: 512-token tiles per CTA pair (two MMAs per decoded weight tile) */
 #define MOLT_PATH_SHORT_TILES 0x800 /* tensor-core GEMMs: 256-token tiles per CTA pair; neither flag = the library chooses */
+#define MOLT_PATH_EXACT_DECODE 0x1000 /* few-token kernel: decode with the dequantiser's bits instead of the table decode */
 
 /* operations for molt_workspace_bytes */
 #define MOLT_OP_LORA_FWD 1

@@ -22,7 +22,8 @@ OK, E_VALUE, E_CAPABILITY, E_RUNTIME, E_TIMEOUT = 0, 1, 2, 3, 4
 ABSMAX_F32, ABSMAX_NESTED = 0, 1
 NIBBLE_LOW_FIRST, NIBBLE_HIGH_FIRST = 0, 1
 DTYPE_BF16, DTYPE_F32 = 0, 1
-PATH_AUTO, PATH_GENERAL, PATH_TCGEN05, PATH_GEMV = 0, 1, 2, 3
+PATH_AUTO, PATH_GENERAL, PATH_TCGEN05, PATH_GEMV, PATH_FEW_TOKENS = 0, 1, 2, 3, 4
+PATH_EXACT_DECODE = 0x1000
 PATH_NO_SPLIT, PATH_FORCE_SPLIT, PATH_TALL_TILES, PATH_SHORT_TILES = 0x100, 0x200, 0x400, 0x800   # flags OR-ed onto a path
 OPT_WAIT_LIMIT_US, OPT_WITHHOLD_BLOCKS = 1, 2
 OP_LORA_FWD, OP_LORA_BWD, OP_DX, OP_MLP_FWD, OP_MLP_BWD = 1, 2, 3, 4, 5

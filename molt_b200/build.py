@@ -19,7 +19,7 @@ PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 BUILD_DIR = CSRC / "build"
 LIBRARY = PACKAGE_DIR / "libmolt_b200.so"
-SOURCES = ["api.cu", "elementwise.cu", "general.cu", "skinny.cu", "gemv.cu", "gemm_sm100_pair.cu", "static_scratch.cu"]
+SOURCES = ["api.cu", "elementwise.cu", "general.cu", "skinny.cu", "gemv.cu", "gemm_sm100_pair.cu", "skinny_sm100.cu", "static_scratch.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -160,19 +160,22 @@ static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m,
                      int* gemm_flags = nullptr) {
   const bool aligned = aligned_case(w, rank);
   MOLT_REQUIRE((requested & ~(0xff | MOLT_PATH_NO_SPLIT | MOLT_PATH_FORCE_SPLIT | MOLT_PATH_TALL_TILES |
-                              MOLT_PATH_SHORT_TILES)) == 0,
+                              MOLT_PATH_SHORT_TILES | MOLT_PATH_EXACT_DECODE)) == 0,
                MOLT_E_VALUE, "unknown kernel path flags 0x%x", requested);
   if (gemm_flags != nullptr)
     *gemm_flags = ((requested & MOLT_PATH_NO_SPLIT) ? kGemmNoSplit : 0) | ((requested & MOLT_PATH_FORCE_SPLIT) ? kGemmForceSplit : 0) |
-                  ((requested & MOLT_PATH_TALL_TILES) ? kGemmTallTiles : 0) | ((requested & MOLT_PATH_SHORT_TILES) ? kGemmShortTiles : 0);
+                  ((requested & MOLT_PATH_TALL_TILES) ? kGemmTallTiles : 0) | ((requested & MOLT_PATH_SHORT_TILES) ? kGemmShortTiles : 0) |
+                  ((requested & MOLT_PATH_EXACT_DECODE) ? kGemmExactDecode : 0);
   requested &= 0xff;
   if (requested == MOLT_PATH_AUTO) {
     if (!aligned) *chosen = MOLT_PATH_GENERAL;
     else if (forward && m <= 16) *chosen = MOLT_PATH_GEMV;
+    else if (forward && m <= 64) *chosen = MOLT_PATH_FEW_TOKENS;   // measured faster than the 256-token tiles up to here
     else *chosen = MOLT_PATH_TCGEN05;
     return MOLT_OK;
   }
-  MOLT_REQUIRE(requested == MOLT_PATH_GENERAL || requested == MOLT_PATH_TCGEN05 || requested == MOLT_PATH_GEMV,
+  MOLT_REQUIRE(requested == MOLT_PATH_GENERAL || requested == MOLT_PATH_TCGEN05 || requested == MOLT_PATH_GEMV ||
+                   requested == MOLT_PATH_FEW_TOKENS,
                MOLT_E_VALUE, "unknown kernel path %d", requested);
   if (requested != MOLT_PATH_GENERAL)
     MOLT_REQUIRE(aligned, MOLT_E_CAPABILITY,
@@ -182,6 +185,8 @@ static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m,
                  (long long)w->n, (long long)w->k, w->blocksize, rank);
   if (requested == MOLT_PATH_GEMV)
     MOLT_REQUIRE(forward && m <= 16, MOLT_E_CAPABILITY, "the GEMV kernel handles forward with at most 16 tokens");
+  if (requested == MOLT_PATH_FEW_TOKENS)
+    MOLT_REQUIRE(forward && m <= 128, MOLT_E_CAPABILITY, "the few-token kernel handles forward with at most 128 tokens");
   *chosen = requested;
   return MOLT_OK;
 }
@@ -230,6 +235,23 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
     }
     return gemv_forward(gview, xb, lora_a, lora_b, scaling, rank, yb, (int)m, reinterpret_cast<__nv_bfloat16*>(t_out), ws,
                         gemv_workspace_bytes(w->n, w->k), s);
+  }
+  if (path == MOLT_PATH_FEW_TOKENS) {
+    const size_t bytes = sm100_skinny_bytes(w->n, w->k, m);
+    void* ws = arena.take(bytes);
+    WeightView sview = view;
+    float* resolved = nullptr;
+    if (w->absmax_kind == MOLT_ABSMAX_NESTED && view.block2_shift < 0)   // a nested layout the kernel cannot read itself
+      resolved = reinterpret_cast<float*>(arena.take((size_t)((w->n * w->k + 63) / 64) * sizeof(float)));
+    if (arena.dry) return MOLT_OK;
+    MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
+    if (resolved != nullptr) {
+      if (int rc = molt_nf4_resolve_absmax(w, resolved, reinterpret_cast<uintptr_t>(s))) return rc;
+      sview.absmax = resolved;
+      sview.absmax_kind = MOLT_ABSMAX_F32;
+    }
+    return sm100_skinny_forward(sview, xb, lora_a, lora_b, scaling, rank, yb, (int)m,
+                                reinterpret_cast<__nv_bfloat16*>(t_out), ws, bytes, flags, s);
   }
   __nv_bfloat16* t = t_out != nullptr ? reinterpret_cast<__nv_bfloat16*>(t_out)
                                       : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));
@@ -411,10 +433,11 @@ size_t molt::workspace_bytes(int op, int64_t m, int64_t n, int64_t k, int rank, 
   fake.packed = reinterpret_cast<const uint8_t*>(uintptr_t(256));
   fake.absmax = fake.packed;
   size_t best = 0;
-  const int paths[3] = {MOLT_PATH_GENERAL, MOLT_PATH_TCGEN05, MOLT_PATH_GEMV};
+  const int paths[4] = {MOLT_PATH_GENERAL, MOLT_PATH_TCGEN05, MOLT_PATH_GEMV, MOLT_PATH_FEW_TOKENS};
   for (int path : paths) {
     if (path != MOLT_PATH_GENERAL && !(k % 64 == 0 && n % 64 == 0)) continue;
     if (path == MOLT_PATH_GEMV && !(op == MOLT_OP_LORA_FWD && m <= 16)) continue;
+    if (path == MOLT_PATH_FEW_TOKENS && !(op == MOLT_OP_LORA_FWD && m >= 1 && m <= 128)) continue;
     Arena arena(nullptr, 0, true, with_optional);
     if (op == MOLT_OP_LORA_FWD) lora_fwd_impl(&fake, nullptr, nullptr, nullptr, 1.f, rank, nullptr, m, nullptr, arena, path, 0);
     else if (op == MOLT_OP_LORA_BWD)

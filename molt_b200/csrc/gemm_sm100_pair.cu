@@ -158,11 +158,6 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 }
 // Barriers completed from the other CTA (remote arrives, tcgen05.commit of the leader) are waited on with the
 // ordinary CTA-scope try_wait.
-__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
-  uint64_t d;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
-  return d;
-}
 __device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                uint32_t accumulate) {
   asm volatile(
@@ -186,44 +181,6 @@ __device__ __forceinline__ void umma_commit_both(uint32_t local_bar_addr) {
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// ---- NF4 decode in registers ---------------------------------------------------------------------------------
-// The sixteen bf16 values of one segment, split into byte planes: lo[i] / hi[i] hold the low / high bytes of entries
-// 4 i .. 4 i + 3.
-struct SegmentTable {
-  uint32_t lo[4], hi[4];
-};
-__device__ __forceinline__ SegmentTable make_segment_table(const float (&codebook)[16], float absmax) {
-  uint32_t pairs[8];   // (entry 2 i, entry 2 i + 1) as bf16x2; one fp32 multiply and one rounding per entry
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-    pairs[i] = pack_bf16x2(__fmul_rn(codebook[2 * i], absmax), __fmul_rn(codebook[2 * i + 1], absmax));
-  SegmentTable t;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    t.lo[i] = __byte_perm(pairs[2 * i], pairs[2 * i + 1], 0x6420u);
-    t.hi[i] = __byte_perm(pairs[2 * i], pairs[2 * i + 1], 0x7531u);
-  }
-  return t;
-}
-// Eight codes (one 32-bit word, code i in bits 4 i .. 4 i + 3) -> eight bf16 values.  A byte permute indexes eight
-// bytes with the low three bits of a selector nibble (bit 3 would ask for sign replication, so it is masked off);
-// the code's top bit chooses between the two halves of the table through a byte mask.  pick01 / pick23 order the
-// result for the weight's nibble order.
-__device__ __forceinline__ void decode_word(uint32_t w, const SegmentTable& t, uint32_t pick01, uint32_t pick23,
-                                            uint32_t (&out)[4]) {
-  const uint32_t low3 = w & 0x77777777u;
-  const uint32_t top = (w >> 3) & 0x11111111u;
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    const uint32_t sel = c == 0 ? low3 : (low3 >> 16);   // prmt reads the low 16 bits of its selector
-    const uint32_t upper = __byte_perm(0x0000ff00u, 0u, c == 0 ? top : (top >> 16));   // 0xff where the code is >= 8
-    const uint32_t lo = (__byte_perm(t.lo[0], t.lo[1], sel) & ~upper) | (__byte_perm(t.lo[2], t.lo[3], sel) & upper);
-    const uint32_t hi = (__byte_perm(t.hi[0], t.hi[1], sel) & ~upper) | (__byte_perm(t.hi[2], t.hi[3], sel) & upper);
-    out[2 * c] = __byte_perm(lo, hi, pick01);
-    out[2 * c + 1] = __byte_perm(lo, hi, pick23);
-  }
 }
 
 template <int kSub>

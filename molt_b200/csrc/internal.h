@@ -39,6 +39,15 @@ int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_
                  int rank, __nv_bfloat16* y, int m, __nv_bfloat16* t_out, void* workspace, size_t workspace_bytes,
                  cudaStream_t s);
 
+// skinny_sm100.cu -- few-token forward (m <= 128) on the tensor cores with the operands swapped: weight rows are the
+// MMA rows, tokens its columns; reads a nested absmax itself when the second-level block size is a power of two.
+// t_out (optional): bf16 [m, 64] = x . A^T.  flags: kGemmExactDecode or 0.
+bool sm100_skinny_supported(const WeightView& w, int rank, long long m);
+size_t sm100_skinny_bytes(long long n, long long k, long long m);
+int sm100_skinny_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_a, const float* lora_b,
+                         float scaling, int rank, __nv_bfloat16* y, int m, __nv_bfloat16* t_out, void* workspace,
+                         size_t workspace_bytes, int flags, cudaStream_t s);
+
 // gemm_sm100_pair.cu -- tcgen05 / TMEM GEMM with the NF4 decode fused in front of the tensor core
 //   forward : out[m, n] = in[m, k] . deq(W)^T + low[m, 0..rp) . ext[n, 0..rp)^T        (ext = bf16(s B) [n, 64])
 //   backward: out[m, k] = in[m, n] . deq(W)   + low[m, 0..rp) . ext[0..rp, k]           (ext = bf16(A)   [rp, k])
@@ -47,6 +56,8 @@ int gemv_forward(const WeightView& w, const __nv_bfloat16* x, const float* lora_
 // flags: kGemmNoSplit keeps the plain schedule, kGemmForceSplit splits whenever the shape allows it; kGemmTallTiles /
 // kGemmShortTiles force the tile height (512 / 256 tokens per CTA pair) instead of the library's own choice
 constexpr int kGemmNoSplit = 1, kGemmForceSplit = 2, kGemmTallTiles = 4, kGemmShortTiles = 8;
+// few-token kernel: the decode that reproduces the dequantiser's bits instead of the faster table decode
+constexpr int kGemmExactDecode = 16;
 int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, const __nv_bfloat16* in,
                const __nv_bfloat16* low, const __nv_bfloat16* ext, int rp, __nv_bfloat16* out, long long m,
                void* split_ws, int flags, cudaStream_t s);

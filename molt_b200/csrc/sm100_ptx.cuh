@@ -125,6 +125,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
@@ -147,5 +156,54 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn_major) 
          ((uint32_t)(m >> 4) << 24);
 }
 
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
+// ---- NF4 decode in registers ---------------------------------------------------------------------------------
+// The sixteen bf16 values of one segment, split into byte planes: lo[i] / hi[i] hold the low / high bytes of entries
+// 4 i .. 4 i + 3.
+struct SegmentTable {
+  uint32_t lo[4], hi[4];
+};
+__device__ __forceinline__ SegmentTable make_segment_table(const float (&codebook)[16], float absmax) {
+  uint32_t pairs[8];   // (entry 2 i, entry 2 i + 1) as bf16x2; one fp32 multiply and one rounding per entry
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    pairs[i] = pack_bf16x2(__fmul_rn(codebook[2 * i], absmax), __fmul_rn(codebook[2 * i + 1], absmax));
+  SegmentTable t;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    t.lo[i] = __byte_perm(pairs[2 * i], pairs[2 * i + 1], 0x6420u);
+    t.hi[i] = __byte_perm(pairs[2 * i], pairs[2 * i + 1], 0x7531u);
+  }
+  return t;
+}
+// Eight codes (one 32-bit word, code i in bits 4 i .. 4 i + 3) -> eight bf16 values.  A byte permute indexes eight
+// bytes with the low three bits of a selector nibble (bit 3 would ask for sign replication, so it is masked off);
+// the code's top bit chooses between the two halves of the table through a byte mask.  pick01 / pick23 order the
+// result for the weight's nibble order.
+__device__ __forceinline__ void decode_word(uint32_t w, const SegmentTable& t, uint32_t pick01, uint32_t pick23,
+                                            uint32_t (&out)[4]) {
+  const uint32_t low3 = w & 0x77777777u;
+  const uint32_t top = (w >> 3) & 0x11111111u;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const uint32_t sel = c == 0 ? low3 : (low3 >> 16);   // prmt reads the low 16 bits of its selector
+    const uint32_t upper = __byte_perm(0x0000ff00u, 0u, c == 0 ? top : (top >> 16));   // 0xff where the code is >= 8
+    const uint32_t lo = (__byte_perm(t.lo[0], t.lo[1], sel) & ~upper) | (__byte_perm(t.lo[2], t.lo[3], sel) & upper);
+    const uint32_t hi = (__byte_perm(t.hi[0], t.hi[1], sel) & ~upper) | (__byte_perm(t.hi[2], t.hi[3], sel) & upper);
+    out[2 * c] = __byte_perm(lo, hi, pick01);
+    out[2 * c + 1] = __byte_perm(lo, hi, pick23);
+  }
+}
+
+
+// Tiled tensor map (2-D) through the driver entry point; defined next to the CTA-pair GEMM.
+int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* ptr, uint64_t inner, uint64_t outer,
+                    uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle,
+                    const char* what);
 
 }  // namespace molt

@@ -48,6 +48,34 @@ def test_bounded_wait_expires_reports_and_recovers(native_library, height):
         _native.set_option(_native.OPT_WAIT_LIMIT_US, 1000000)
 
 
+def test_few_token_kernel_wait_expires_reports_and_recovers(native_library):
+    """The same for the few-token kernel: its code producer requests one block fewer than the decoders expect."""
+    path = _native.PATH_FEW_TOKENS
+    case = make_case(256, 128, 40, 8, seed=3)             # one CTA, two row tiles of two contraction blocks each
+    y_ref = oracle.nf4_lora_forward(case.x, case.weight, case.a, case.b, case.scaling)
+    y_good, _ = run_forward(case, path)
+    assert _native.read_status() == 0
+    _native.set_option(_native.OPT_WAIT_LIMIT_US, 3000)
+    try:
+        _native.set_option(_native.OPT_WITHHOLD_BLOCKS, 1)
+        begin = time.perf_counter()
+        run_forward(case, path)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - begin
+        status = _native.read_status()
+        assert status != 0 and (status >> 24) == _native.E_TIMEOUT, hex(status)
+        assert 1 <= ((status >> 16) & 0xff) <= 9
+        assert elapsed < 2.0
+        y_again, _ = run_forward(case, path)
+        torch.cuda.synchronize()
+        assert _native.read_status() == 0
+        assert torch.equal(y_again, y_good)
+        assert oracle.rel_frobenius(y_again, y_ref) <= TOL
+    finally:
+        _native.set_option(_native.OPT_WITHHOLD_BLOCKS, 0)
+        _native.set_option(_native.OPT_WAIT_LIMIT_US, 1000000)
+
+
 def test_option_values_are_checked(native_library):
     with pytest.raises(ValueError):
         _native.set_option(_native.OPT_WAIT_LIMIT_US, 1)

@@ -265,3 +265,29 @@ def test_packed_backward_input_operators(native_library):
         assert oracle.rel_frobenius(fused, want) <= TOL
     with pytest.raises(ValueError, match="width"):
         packed_nf4_backward_input(torch.zeros(2, 3, device="cuda", dtype=torch.bfloat16), case.packed, case.state)
+
+
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("m", [1, 5, 16, 17, 33, 64, 100, 128])
+@pytest.mark.parametrize("n,k,rank,nested,order", [(1536, 1024, 16, True, "high-first"), (320, 192, 7, False, "low-first"),
+                                                   (2048, 4096, 64, True, "low-first")])
+def test_few_token_path(native_library, m, n, k, rank, nested, order, exact):
+    """Forward with at most 128 tokens on the swapped-operand tcgen05 kernel (weight rows are the MMA rows): parts of a
+    row tile computed by different CTAs, a last tile with 64 valid rows, ranks that are not multiples of 16, both absmax
+    forms (the nested one resolved inside the kernel), and both decodes: the table decode (bf16 codebook pair times
+    bf16 absmax) and the one with the dequantiser's bits.
+    Must match the oracle, and the low-rank product it returns must match the one of the tensor-core path."""
+    case = make_case(n, k, m, rank, seed=n + k + m, nested=nested, order=order)
+    path = _native.PATH_FEW_TOKENS | (_native.PATH_EXACT_DECODE if exact else 0)
+    y_ref = oracle_results(case)[0]
+    y, t = run_forward(case, path, keep_t=True)
+    torch.cuda.synchronize()
+    assert_clean_status()
+    assert oracle.rel_frobenius(y, y_ref) <= TOL
+    y2, t2 = run_forward(case, _native.PATH_TCGEN05, keep_t=True)
+    assert oracle.rel_frobenius(y, y2.float()) <= (2e-3 if exact else 6e-3)
+    assert oracle.rel_frobenius(t[:, :rank].float(), t2[:, :rank].float()) <= 4e-3
+    assert not t[:, rank:].any()
+    # deterministic: a second call gives the same bits
+    y3, _ = run_forward(case, path, keep_t=False)
+    assert torch.equal(y3, y)
