@@ -34,10 +34,10 @@ if str(ROOT) not in sys.path:
 
 N_OUT, K_IN, RANK, ALPHA, M_PER_GPU = 14336, 4096, 16, 32.0, 4096
 SCALING = ALPHA / RANK
-# dram__bytes_read.sum + dram__bytes_write.sum of one backward GEMM launch at M = 4096 (353.0 MB + 39.9 MB, the fp32
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward GEMM launch at M = 4096 (238.5 MB + 23.6 MB, the fp32
 # partial tiles of the split last wave included), taken from an ncu --set full capture of `bench.py --profile gemm_bwd`;
 # the summary of that capture sits under profiles/.
-GEMM_BWD_DRAM_BYTES_PER_LAUNCH = 392.9e6
+GEMM_BWD_DRAM_BYTES_PER_LAUNCH = 262.1e6
 METRIC = "nf4_lora_linear_fwd_bwd_tflops"
 WORKLOAD = ("NF4-LoRA linear fwd+bwd, W[14336,4096] NF4 bs64 double-quant absmax, r=16 alpha=32, "
             "M=4096 tokens per GPU, bf16")
@@ -544,6 +544,11 @@ def profile_case(which, lib, device, desc, packed, state, lora_a, lora_b, x, dy,
             for d in (desc, plain_desc):   # nested absmax (the configuration's own form), then plain fp32 absmax
                 _native.check(lib.molt_nf4_gemv(ctypes.byref(d), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
                                                 SCALING, RANK, y.data_ptr(), tokens, ws.data_ptr(), ws_bytes, stream))
+        elif which == "few_tokens":
+            for tokens in (16, 64):   # nested absmax, read by the kernel itself
+                _native.check(lib.molt_nf4_lora_fwd(ctypes.byref(desc), x.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
+                                                    SCALING, RANK, y.data_ptr(), tokens, None, ws.data_ptr(), ws_bytes,
+                                                    _native.PATH_FEW_TOKENS, stream))
         elif which == "swiglu":
             gate, up, grad = dy, torch.roll(dy, 1, 0), torch.roll(dy, 2, 0)   # three distinct [M, N] tensors
             swiglu_forward(gate, up)
@@ -757,7 +762,7 @@ def main() -> int:
                         help="linear = the headline NF4-LoRA linear; step4 / step5 = full QLoRA step of BASELINE config 4 / 5")
     parser.add_argument("--no-graph", action="store_true", help="step workloads: run eagerly instead of replaying a CUDA graph")
     parser.add_argument("--layers", type=int, default=None, help="step workloads: use fewer decoder layers")
-    parser.add_argument("--profile", choices=("gemm_bwd", "linear_fwd", "gemv", "gemv1", "swiglu"), default=None,
+    parser.add_argument("--profile", choices=("gemm_bwd", "linear_fwd", "gemv", "gemv1", "few_tokens", "swiglu"), default=None,
                         help="run one kernel family four times and exit (target of an ncu capture)")
     args = parser.parse_args()
     if args.steps < 1:
