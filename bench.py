@@ -261,6 +261,7 @@ def run_ours(args) -> int:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")   # keeps NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
     lib = _native.library()
     peaks = measured_peaks()
@@ -632,6 +633,7 @@ def run_step_workload(args) -> int:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")   # keeps NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
     shape = QWEN25_1P5B if args.workload == "step4" else LLAMA3_8B
     line = measure_step(shape, args.workload, args.steps, args.warmup, args.layers, not args.no_graph, world, rank,
