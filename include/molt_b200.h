@@ -184,6 +184,26 @@ int molt_rmsnorm_fwd(const void* x, const void* weight, int weight_dtype, float 
 int molt_rmsnorm_bwd(const void* grad_out, const void* x, const void* weight, int weight_dtype, float eps,
                      float weight_offset, void* grad_x, int64_t rows, int64_t width, uintptr_t stream);
 
+/* The residual add fused with the RMSNorm behind it: sum_out = bf16(x + delta), out = RMSNorm(sum_out) as
+ * molt_rmsnorm_fwd computes it (one pass over the hidden states instead of two).  width a multiple of 8.  Fuses the
+ * residual add of the decoder layer with reference kernels/frozen_rmsnorm.py:11-23. */
+int molt_add_rmsnorm_fwd(const void* x, const void* delta, const void* weight, int weight_dtype, float eps,
+                         float weight_offset, void* sum_out, void* out, int64_t rows, int64_t width, uintptr_t stream);
+
+/* Its backward: grad_x = bf16(grad_sum + RMSNorm-backward(grad_out; sum)), the gradient of both x and delta
+ * (reference kernels/frozen_rmsnorm.py:25-37 plus the gradient accumulation of the residual stream). */
+int molt_add_rmsnorm_bwd(const void* grad_out, const void* grad_sum, const void* sum, const void* weight,
+                         int weight_dtype, float eps, float weight_offset, void* grad_x, int64_t rows, int64_t width,
+                         uintptr_t stream);
+
+/* Rotary position embedding of q [batch, seq, heads, head_dim] and k [batch, seq, kv_heads, head_dim] (bf16) into
+ * q_out / k_out (which may be q / k themselves): (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin) over the two halves of
+ * every head vector; cos / sin are bf16 [seq, head_dim] tables with equal halves; inverse != 0 applies the transposed
+ * rotation (the gradient).  head_dim a multiple of 16; kv_heads = 0 rotates q alone.  Part of the step driver around the path (the reference trainer
+ * uses the model's own). */
+int molt_rope(const void* q, const void* k, void* q_out, void* k_out, const void* cos_table, const void* sin_table,
+              int64_t batch, int64_t seq, int heads, int kv_heads, int head_dim, int inverse, uintptr_t stream);
+
 /* One AdamW step (decoupled weight decay, bias correction as in torch.optim.AdamW) over flat fp32 arrays of `count`
  * elements (a multiple of 4): every adapter's parameters, gradients and moments laid end to end, so one launch steps
  * them all.  grad is multiplied by grad_scale first (1 / world size after a summing all-reduce).  step counts from 1.

@@ -31,7 +31,8 @@ OP_LORA_FWD, OP_LORA_BWD, OP_DX, OP_MLP_FWD, OP_MLP_BWD = 1, 2, 3, 4, 5
 EXPORTS = (
     "molt_version", "molt_last_error", "molt_launch_count", "molt_set_option", "molt_read_status", "molt_nf4_dequant", "molt_nf4_resolve_absmax",
     "molt_workspace_bytes", "molt_nf4_lora_fwd", "molt_nf4_lora_fwd_static", "molt_nf4_lora_bwd", "molt_nf4_dx", "molt_nf4_gemv",
-    "molt_swiglu_fwd", "molt_swiglu_bwd", "molt_rmsnorm_fwd", "molt_rmsnorm_bwd", "molt_adamw_step", "molt_dense_gemm",
+    "molt_swiglu_fwd", "molt_swiglu_bwd", "molt_rmsnorm_fwd", "molt_rmsnorm_bwd", "molt_add_rmsnorm_fwd",
+    "molt_add_rmsnorm_bwd", "molt_rope", "molt_adamw_step", "molt_dense_gemm",
     "molt_dense_gemm_workspace_bytes", "molt_ce_softmax_grad", "molt_mlp_workspace_bytes", "molt_mlp_fwd",
     "molt_mlp_bwd",
 )
@@ -112,6 +113,12 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.molt_rmsnorm_fwd.argtypes = [vp, vp, i32, f32, f32, vp, i64, i64, up]
     lib.molt_rmsnorm_bwd.restype = i32
     lib.molt_rmsnorm_bwd.argtypes = [vp, vp, vp, i32, f32, f32, vp, i64, i64, up]
+    lib.molt_add_rmsnorm_fwd.restype = i32
+    lib.molt_add_rmsnorm_fwd.argtypes = [vp, vp, vp, i32, f32, f32, vp, vp, i64, i64, up]
+    lib.molt_add_rmsnorm_bwd.restype = i32
+    lib.molt_add_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, i32, f32, f32, vp, i64, i64, up]
+    lib.molt_rope.restype = i32
+    lib.molt_rope.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, up]
     lib.molt_adamw_step.restype = i32
     lib.molt_adamw_step.argtypes = [vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, i64, f32, up]
     lib.molt_dense_gemm_workspace_bytes.restype = sz

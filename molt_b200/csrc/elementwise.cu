@@ -288,6 +288,119 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 }
 
 // ------------------------------------------------------------------------------------------------
+// Residual add fused with the RMSNorm that follows it (one pass over the hidden states instead of two):
+//   forward : sum = bf16(x + delta);  out = bf16(sum * rsqrt(mean(sum^2) + eps) * (w + offset))
+//   backward: grad_x = bf16(grad_sum + inv * (dy (w + offset) - sum inv * mean(dy (w + offset) * sum inv)))
+// The norm is taken from the ROUNDED sum, the tensor the backward sees.  One warp per row, width a multiple of 8.
+// ------------------------------------------------------------------------------------------------
+template <typename WT, bool BACKWARD>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ a,      // fwd: x;     bwd: sum
+                                                          const __nv_bfloat16* __restrict__ b,      // fwd: delta; bwd: dy
+                                                          const __nv_bfloat16* __restrict__ c_in,   // bwd: grad_sum
+                                                          const WT* __restrict__ weight, float eps, float weight_offset,
+                                                          __nv_bfloat16* __restrict__ sum_out,      // fwd only
+                                                          __nv_bfloat16* __restrict__ out, long long rows,
+                                                          long long width) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp; row < rows; row += warps) {
+    const long long base = row * width;
+    float sq = 0.f, dot = 0.f;
+    for (long long c = lane * 8LL; c < width; c += 256) {
+      float av[8], bv[8];
+      unpack8(__ldcs(reinterpret_cast<const uint4*>(a + base + c)), av);
+      unpack8(__ldcs(reinterpret_cast<const uint4*>(b + base + c)), bv);
+      if (!BACKWARD) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) packed[i] = pack_bf16x2(av[2 * i] + bv[2 * i], av[2 * i + 1] + bv[2 * i + 1]);
+        const uint4 stored = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(sum_out + base + c) = stored;   // re-read below, from L1/L2
+        float sv[8];
+        unpack8(stored, sv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sq += sv[i] * sv[i];
+      } else {
+        float wv[8];
+        load_weight8<WT>(weight, c, weight_offset, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          sq += av[i] * av[i];
+          dot += bv[i] * wv[i] * av[i];
+        }
+      }
+    }
+    sq = warp_sum(sq);
+    const float inv = rsqrtf(sq / (float)width + eps);
+    float correction = 0.f;
+    if (BACKWARD) correction = warp_sum(dot) * inv / (float)width;
+    __syncwarp();
+    for (long long c = lane * 8LL; c < width; c += 256) {
+      float wv[8], res[8];
+      load_weight8<WT>(weight, c, weight_offset, wv);
+      if (!BACKWARD) {
+        float sv[8];
+        unpack8(*reinterpret_cast<const uint4*>(sum_out + base + c), sv);   // this lane's own store
+#pragma unroll
+        for (int i = 0; i < 8; ++i) res[i] = sv[i] * inv * wv[i];
+      } else {
+        float sv[8], gv[8], rv[8];
+        unpack8(*reinterpret_cast<const uint4*>(a + base + c), sv);
+        unpack8(*reinterpret_cast<const uint4*>(b + base + c), gv);
+        unpack8(__ldcs(reinterpret_cast<const uint4*>(c_in + base + c)), rv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) res[i] = rv[i] + inv * (gv[i] * wv[i] - sv[i] * inv * correction);
+      }
+      __stcs(reinterpret_cast<uint4*>(out + base + c), make_uint4(pack_bf16x2(res[0], res[1]), pack_bf16x2(res[2], res[3]),
+                                                                  pack_bf16x2(res[4], res[5]), pack_bf16x2(res[6], res[7])));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Rotary position embedding (in place or into other buffers) on the query and key projections of a whole batch:
+//   (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin),   x1 / x2 = first / second half of a head's vector;
+// inverse = 1 applies the transposed rotation (the gradient).  fp32 arithmetic, one rounding.
+// q [batch, seq, heads, d], k [batch, seq, kv_heads, d], cos / sin [seq, d] (both halves equal), all bf16.
+// One thread rotates 8 elements of the first half with their partners in the second half.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rope_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k, __nv_bfloat16* q_out,
+                                                   __nv_bfloat16* k_out, const __nv_bfloat16* __restrict__ cos_t,
+                                                   const __nv_bfloat16* __restrict__ sin_t, long long tokens, int seq,
+                                                   int heads, int kv_heads, int d, float sign) {
+  const int per_vec = d / 16;                       // threads per head vector
+  const long long vectors = tokens * (heads + kv_heads);
+  const long long total = vectors * per_vec;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long vec = i / per_vec;
+    const int part = (int)(i - vec * per_vec);
+    const long long token = vec / (heads + kv_heads);
+    const int head = (int)(vec - token * (heads + kv_heads));
+    const long long offset = head < heads ? (token * heads + head) * (long long)d
+                                          : (token * kv_heads + (head - heads)) * (long long)d;
+    const __nv_bfloat16* x = (head < heads ? q : k) + offset;
+    __nv_bfloat16* y = (head < heads ? q_out : k_out) + offset;   // may be x itself: a thread reads before it writes
+    const int pos = (int)(token % seq);
+    float x1[8], x2[8], cv[8], sv[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + part * 8), x1);
+    unpack8(*reinterpret_cast<const uint4*>(x + d / 2 + part * 8), x2);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(cos_t + (long long)pos * d + part * 8)), cv);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(sin_t + (long long)pos * d + part * 8)), sv);
+    float o1[8], o2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o1[j] = x1[j] * cv[j] - sign * x2[j] * sv[j];
+      o2[j] = x2[j] * cv[j] + sign * x1[j] * sv[j];
+    }
+    *reinterpret_cast<uint4*>(y + part * 8) = make_uint4(pack_bf16x2(o1[0], o1[1]), pack_bf16x2(o1[2], o1[3]),
+                                                         pack_bf16x2(o1[4], o1[5]), pack_bf16x2(o1[6], o1[7]));
+    *reinterpret_cast<uint4*>(y + d / 2 + part * 8) = make_uint4(pack_bf16x2(o2[0], o2[1]), pack_bf16x2(o2[2], o2[3]),
+                                                                 pack_bf16x2(o2[4], o2[5]), pack_bf16x2(o2[6], o2[7]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // AdamW over flat fp32 arrays (decoupled weight decay, bias correction as torch.optim.AdamW computes it).
 // All adapter parameters, their gradients and both moments live in flat arenas, so one launch steps every adapter.
 // ------------------------------------------------------------------------------------------------
@@ -449,6 +562,71 @@ extern "C" int molt_rmsnorm_bwd(const void* grad_out, const void* x, const void*
   MOLT_REQUIRE(grad_out != nullptr, MOLT_E_VALUE, "molt_rmsnorm_bwd: NULL tensor pointer");
   return rmsnorm_launch("molt_rmsnorm_bwd", x, weight, weight_dtype, grad_out, eps, weight_offset, grad_x, rows, width,
                         stream);
+}
+
+static int add_rmsnorm_launch(const char* who, const void* a, const void* b, const void* c, const void* weight,
+                              int weight_dtype, float eps, float weight_offset, void* sum_out, void* out, int64_t rows,
+                              int64_t width, bool backward, uintptr_t stream) {
+  MOLT_REQUIRE(a && b && weight && out && (backward ? c != nullptr : sum_out != nullptr), MOLT_E_VALUE,
+               "%s: NULL tensor pointer", who);
+  MOLT_REQUIRE(rows >= 0 && width > 0 && width % 8 == 0, MOLT_E_VALUE, "%s: width must be a positive multiple of 8", who);
+  MOLT_REQUIRE(weight_dtype == MOLT_DTYPE_F32 || weight_dtype == MOLT_DTYPE_BF16, MOLT_E_CAPABILITY,
+               "%s: weight dtype must be bf16 or fp32", who);
+  MOLT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(out) && aligned16(weight) && (c == nullptr || aligned16(c)) &&
+                   (sum_out == nullptr || aligned16(sum_out)),
+               MOLT_E_VALUE, "%s: tensors must be 16-byte aligned", who);
+  if (rows == 0) return MOLT_OK;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long blocks = (rows + 7) / 8;   // eight warps (rows) per block
+  const unsigned grid = (unsigned)(blocks < (long long)sm_count() * 8 ? blocks : (long long)sm_count() * 8);
+  auto* ab = reinterpret_cast<const __nv_bfloat16*>(a);
+  auto* bb = reinterpret_cast<const __nv_bfloat16*>(b);
+  auto* cb = reinterpret_cast<const __nv_bfloat16*>(c);
+  auto* sb = reinterpret_cast<__nv_bfloat16*>(sum_out);
+  auto* ob = reinterpret_cast<__nv_bfloat16*>(out);
+  if (weight_dtype == MOLT_DTYPE_F32) {
+    auto* w = reinterpret_cast<const float*>(weight);
+    if (backward) add_rmsnorm_kernel<float, true><<<grid, 256, 0, s>>>(ab, bb, cb, w, eps, weight_offset, sb, ob, rows, width);
+    else add_rmsnorm_kernel<float, false><<<grid, 256, 0, s>>>(ab, bb, cb, w, eps, weight_offset, sb, ob, rows, width);
+  } else {
+    auto* w = reinterpret_cast<const __nv_bfloat16*>(weight);
+    if (backward) add_rmsnorm_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(ab, bb, cb, w, eps, weight_offset, sb, ob, rows, width);
+    else add_rmsnorm_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(ab, bb, cb, w, eps, weight_offset, sb, ob, rows, width);
+  }
+  return launch_status("add_rmsnorm_kernel");
+}
+
+extern "C" int molt_add_rmsnorm_fwd(const void* x, const void* delta, const void* weight, int weight_dtype, float eps,
+                                    float weight_offset, void* sum_out, void* out, int64_t rows, int64_t width,
+                                    uintptr_t stream) {
+  return add_rmsnorm_launch("molt_add_rmsnorm_fwd", x, delta, nullptr, weight, weight_dtype, eps, weight_offset, sum_out,
+                            out, rows, width, false, stream);
+}
+
+extern "C" int molt_add_rmsnorm_bwd(const void* grad_out, const void* grad_sum, const void* sum, const void* weight,
+                                    int weight_dtype, float eps, float weight_offset, void* grad_x, int64_t rows,
+                                    int64_t width, uintptr_t stream) {
+  return add_rmsnorm_launch("molt_add_rmsnorm_bwd", sum, grad_out, grad_sum, weight, weight_dtype, eps, weight_offset,
+                            nullptr, grad_x, rows, width, true, stream);
+}
+
+extern "C" int molt_rope(const void* q, const void* k, void* q_out, void* k_out, const void* cos_table,
+                         const void* sin_table, int64_t batch, int64_t seq, int heads, int kv_heads, int head_dim,
+                         int inverse, uintptr_t stream) {
+  MOLT_REQUIRE(q && k && q_out && k_out && cos_table && sin_table, MOLT_E_VALUE, "molt_rope: NULL tensor pointer");
+  MOLT_REQUIRE(batch >= 0 && seq > 0 && heads > 0 && kv_heads >= 0, MOLT_E_VALUE, "molt_rope: bad sizes");
+  MOLT_REQUIRE(head_dim > 0 && head_dim % 16 == 0, MOLT_E_CAPABILITY, "molt_rope: head_dim must be a multiple of 16");
+  MOLT_REQUIRE(aligned16(q) && aligned16(k) && aligned16(q_out) && aligned16(k_out) && aligned16(cos_table) &&
+                   aligned16(sin_table),
+               MOLT_E_VALUE, "molt_rope: tensors must be 16-byte aligned");
+  if (batch == 0) return MOLT_OK;
+  const long long total = batch * seq * (long long)(heads + kv_heads) * (head_dim / 16);
+  rope_kernel<<<grid_for(total, 256, 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(q), reinterpret_cast<const __nv_bfloat16*>(k),
+      reinterpret_cast<__nv_bfloat16*>(q_out), reinterpret_cast<__nv_bfloat16*>(k_out),
+      reinterpret_cast<const __nv_bfloat16*>(cos_table), reinterpret_cast<const __nv_bfloat16*>(sin_table), batch * seq,
+      (int)seq, heads, kv_heads, head_dim, inverse ? -1.0f : 1.0f);
+  return launch_status("rope_kernel");
 }
 
 extern "C" int molt_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, int64_t count,

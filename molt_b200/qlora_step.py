@@ -124,6 +124,81 @@ class _FrozenRMSNorm(torch.autograd.Function):
         return out.reshape(ctx.shape), None, None
 
 
+class _AddFrozenRMSNorm(torch.autograd.Function):
+    """``stream = residual + delta`` and ``normed = RMSNorm(stream)`` in one pass over the hidden states; in backward one
+    kernel adds the RMSNorm gradient to the gradient arriving on ``stream`` (what autograd would otherwise accumulate
+    with a separate add)."""
+
+    @staticmethod
+    def forward(ctx, residual, delta, weight, eps):
+        rows = residual.reshape(-1, residual.shape[-1])
+        other = delta.reshape(rows.shape)
+        rows = rows if rows.is_contiguous() else rows.contiguous()
+        other = other if other.is_contiguous() else other.contiguous()
+        stream, normed = torch.empty_like(rows), torch.empty_like(rows)
+        dtype = _native.DTYPE_F32 if weight.dtype == torch.float32 else _native.DTYPE_BF16
+        with torch.cuda.device(rows.device):
+            _native.check(_native.library().molt_add_rmsnorm_fwd(rows.data_ptr(), other.data_ptr(), weight.data_ptr(), dtype,
+                                                                 float(eps), 0.0, stream.data_ptr(), normed.data_ptr(),
+                                                                 rows.shape[0], rows.shape[1],
+                                                                 _native.stream_handle(rows.device)))
+        ctx.save_for_backward(stream, weight)
+        ctx.eps, ctx.weight_dtype, ctx.shape = float(eps), dtype, residual.shape
+        return stream.reshape(residual.shape), normed.reshape(residual.shape)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_stream, grad_normed):
+        stream, weight = ctx.saved_tensors
+
+        def rows_of(grad):
+            grad = grad.reshape(stream.shape)
+            if grad.dtype != torch.bfloat16:
+                grad = grad.to(torch.bfloat16)
+            return grad if grad.is_contiguous() else grad.contiguous()
+
+        gs, gn = rows_of(grad_stream), rows_of(grad_normed)
+        out = torch.empty_like(stream)
+        with torch.cuda.device(stream.device):
+            _native.check(_native.library().molt_add_rmsnorm_bwd(gn.data_ptr(), gs.data_ptr(), stream.data_ptr(),
+                                                                 weight.data_ptr(), ctx.weight_dtype, ctx.eps, 0.0,
+                                                                 out.data_ptr(), stream.shape[0], stream.shape[1],
+                                                                 _native.stream_handle(stream.device)))
+        out = out.reshape(ctx.shape)
+        return out, out, None, None
+
+
+class _Rope(torch.autograd.Function):
+    """Rotary embedding of one projection output (``[batch, seq, heads * head_dim]``) in one kernel; the gradient is
+    the transposed rotation."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin, heads, head_dim):
+        ctx.save_for_backward(cos, sin)
+        ctx.dims = (x.shape[0], x.shape[1], heads, head_dim)
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        _Rope._launch(x, out, cos, sin, ctx.dims, 0)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad):
+        cos, sin = ctx.saved_tensors
+        grad = grad.contiguous()
+        out = torch.empty_like(grad)   # the incoming buffer is autograd's
+        _Rope._launch(grad, out, cos, sin, ctx.dims, 1)
+        return out, None, None, None, None
+
+    @staticmethod
+    def _launch(x, out, cos, sin, dims, inverse):
+        batch, seq, heads, head_dim = dims
+        with torch.cuda.device(x.device):
+            _native.check(_native.library().molt_rope(x.data_ptr(), x.data_ptr(), out.data_ptr(), out.data_ptr(),
+                                                      cos.data_ptr(), sin.data_ptr(), batch, seq, heads, 0, head_dim,
+                                                      inverse, _native.stream_handle(x.device)))
+
+
 class RMSNorm(nn.Module):
     def __init__(self, width: int, device, eps: float = 1e-6):
         super().__init__()
@@ -134,6 +209,13 @@ class RMSNorm(nn.Module):
         if x.is_cuda and x.dtype == torch.bfloat16:
             return _FrozenRMSNorm.apply(x, self.weight, self.eps)
         return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+
+    def add_and_norm(self, residual: torch.Tensor, delta: torch.Tensor):
+        """``(residual + delta, self(residual + delta))``, fused on the GPU."""
+        if residual.is_cuda and residual.dtype == torch.bfloat16 and delta.dtype == torch.bfloat16 and residual.shape[-1] % 8 == 0:
+            return _AddFrozenRMSNorm.apply(residual, delta, self.weight, self.eps)
+        stream = residual + delta
+        return stream, self(stream)
 
 
 class Attention(nn.Module):
@@ -149,11 +231,18 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         b, s, _ = x.shape
         sh = self.shape
-        q = self.q_proj(x).view(b, s, sh.heads, sh.head_dim).transpose(1, 2)
-        k = self.k_proj(x).view(b, s, sh.kv_heads, sh.head_dim).transpose(1, 2)
-        v = self.v_proj(x).view(b, s, sh.kv_heads, sh.head_dim).transpose(1, 2)
-        q = _rope(q, cos, sin)
-        k = _rope(k, cos, sin)
+        q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        fused = q.is_cuda and q.dtype == torch.bfloat16 and sh.head_dim % 16 == 0 and cos.shape[-2] == s
+        if fused:   # one kernel per projection ([batch, seq, heads, head_dim] layout)
+            cos2, sin2 = cos.reshape(s, sh.head_dim), sin.reshape(s, sh.head_dim)
+            q = _Rope.apply(q, cos2, sin2, sh.heads, sh.head_dim)
+            k = _Rope.apply(k, cos2, sin2, sh.kv_heads, sh.head_dim)
+        q = q.view(b, s, sh.heads, sh.head_dim).transpose(1, 2)
+        k = k.view(b, s, sh.kv_heads, sh.head_dim).transpose(1, 2)
+        v = v.view(b, s, sh.kv_heads, sh.head_dim).transpose(1, 2)
+        if not fused:
+            q = _rope(q, cos, sin)
+            k = _rope(k, cos, sin)
         out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         return self.o_proj(out.transpose(1, 2).reshape(b, s, sh.heads * sh.head_dim))
 
@@ -175,14 +264,25 @@ class DecoderLayer(nn.Module):
                             _projection(shape.hidden, shape.intermediate, shape, gen, device))
 
     def forward(self, x, cos, sin, replay_up: bool, on_backward_done=None):
-        if on_backward_done is not None and x.requires_grad:
-            # fires when the gradient of this layer's input exists, i.e. when every adapter gradient of the layer has
-            # been written: the moment its bucket can go to the all-reduce
-            x.register_hook(on_backward_done)
-        x = x + self.attn(self.input_norm(x), cos, sin)
-        normed = self.post_norm(x)
+        """The layer on its own: returns the residual stream after it."""
+        stream, delta = self.step(x, None, cos, sin, replay_up, on_backward_done)
+        return stream + delta
+
+    def step(self, residual, delta, cos, sin, replay_up: bool, on_backward_done=None):
+        """The layer inside a stack.  The stream entering it is ``residual + delta`` (``delta`` None: just ``residual``);
+        returns ``(stream after the attention block, output of the MLP)``, so that the add of the MLP output is fused
+        with the next norm (the next layer's, or the final one)."""
+        if delta is None:
+            stream, normed = residual, self.input_norm(residual)
+        else:
+            stream, normed = self.input_norm.add_and_norm(residual, delta)
+        if on_backward_done is not None and normed.requires_grad:
+            # fires when the gradient of the attention block's input exists, i.e. when every adapter gradient of the
+            # layer has been written (the MLP's came first): the moment its bucket can go to the all-reduce
+            normed.register_hook(on_backward_done)
+        stream, normed = self.post_norm.add_and_norm(stream, self.attn(normed, cos, sin))
         b, s, w = normed.shape
-        return x + self.mlp.fused(normed.reshape(b * s, w), rematerialize_up=replay_up).view(b, s, w)
+        return stream, self.mlp.fused(normed.reshape(b * s, w), rematerialize_up=replay_up).view(b, s, w)
 
 
 def dense_gemm(weight: torch.Tensor, x: torch.Tensor, contract_over_rows: bool, flags: int = 0) -> torch.Tensor:
@@ -253,15 +353,16 @@ class SyntheticDecoder(nn.Module):
              layer_done=None) -> torch.Tensor:
         """``layer_done(index)``, when given, is called during backward as soon as layer ``index`` has produced all of
         its adapter gradients (layers finish from the last to the first)."""
-        x = F.embedding(tokens, self.embed).requires_grad_()
+        stream, delta = F.embedding(tokens, self.embed).requires_grad_(), None
         for index, layer in enumerate(self.layers):
             hook = None
             if layer_done is not None:
                 def hook(grad, index=index):
                     layer_done(index)
                     return grad
-            x = layer(x, self.cos, self.sin, replay_up, hook)
-        hidden = self.final_norm(x).reshape(-1, self.shape.hidden)
+            stream, delta = layer.step(stream, delta, self.cos, self.sin, replay_up, hook)
+        _, hidden = self.final_norm.add_and_norm(stream, delta)
+        hidden = hidden.reshape(-1, self.shape.hidden)
         return _FrozenHeadLoss.apply(hidden, self.head, targets.reshape(-1), self.head_chunk, float(global_tokens))
 
 

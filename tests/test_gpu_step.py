@@ -236,3 +236,61 @@ def test_dense_gemm_matches_fp32_matmul(native_library, n, k, m, over_rows):
         want = x.float() @ (weight.float() if over_rows else weight.float().t())
         assert oracle.rel_frobenius(got, want) <= 1e-2, flags
     assert _native.read_status() == 0
+
+
+def test_add_rmsnorm_matches_the_separate_ops(native_library):
+    """Residual add fused with the norm behind it: the sum is the bf16 add, the norm equals molt_rmsnorm_fwd on that sum,
+    and the backward equals RMSNorm backward plus the gradient arriving on the stream (fp32 reference, 1e-2)."""
+    from molt_b200.qlora_step import RMSNorm, _AddFrozenRMSNorm
+
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    rows, width = 300, 1536
+    x = (torch.randn(2, rows // 2, width, device="cuda", generator=gen)).bfloat16().requires_grad_()
+    delta = (torch.randn(2, rows // 2, width, device="cuda", generator=gen) * 0.5).bfloat16().requires_grad_()
+    norm = RMSNorm(width, torch.device("cuda"))
+    with torch.no_grad():
+        norm.weight.copy_((1 + 0.1 * torch.randn(width, device="cuda", generator=gen)).bfloat16())
+    stream, normed = _AddFrozenRMSNorm.apply(x, delta, norm.weight, norm.eps)
+    assert torch.equal(stream, x.detach() + delta.detach())
+    assert torch.equal(normed, norm(stream.detach()))
+    g_stream = torch.randn_like(stream)
+    g_normed = torch.randn_like(normed)
+    torch.autograd.backward([stream, normed], [g_stream, g_normed])
+    # fp32 reference
+    xs = (x.detach().float() + delta.detach().float()).bfloat16().float().requires_grad_()
+    ref = torch.nn.functional.rms_norm(xs, (width,), norm.weight.float(), norm.eps)
+    ref.backward(g_normed.float())
+    expected = xs.grad + g_stream.float()
+    for grad in (x.grad, delta.grad):
+        assert (grad.float() - expected).norm() / expected.norm() <= 1e-2
+    assert torch.equal(x.grad, delta.grad)
+
+
+def test_rope_kernel_matches_torch(native_library):
+    """Rotary embedding of q and k in one kernel each against the cat/mul formulation in fp32; the gradient is the
+    transposed rotation."""
+    from molt_b200.qlora_step import _Rope, _rope
+
+    gen = torch.Generator(device="cuda").manual_seed(6)
+    b, s, heads, kv, d = 2, 96, 6, 2, 64
+    inv = 1.0 / (1e4 ** (torch.arange(0, d, 2, device="cuda").float() / d))
+    angles = torch.outer(torch.arange(s, device="cuda").float(), inv)
+    angles = torch.cat((angles, angles), dim=-1)
+    cos, sin = angles.cos().bfloat16(), angles.sin().bfloat16()
+    q0 = torch.randn(b, s, heads * d, device="cuda", generator=gen).bfloat16()
+    k0 = torch.randn(b, s, kv * d, device="cuda", generator=gen).bfloat16()
+    ql, kl = q0.clone().requires_grad_(), k0.clone().requires_grad_()
+    q = _Rope.apply(ql, cos, sin, heads, d)
+    k = _Rope.apply(kl, cos, sin, kv, d)
+
+    def reference(x, n):
+        x = x.float().view(b, s, n, d).transpose(1, 2)
+        return _rope(x, cos.float()[None, None], sin.float()[None, None]).transpose(1, 2).reshape(b, s, n * d)
+
+    qr, kr = q0.float().requires_grad_(), k0.float().requires_grad_()
+    q_ref, k_ref = reference(qr, heads), reference(kr, kv)
+    assert (q.float() - q_ref).abs().max() <= 2e-2 and (k.float() - k_ref).abs().max() <= 2e-2
+    gq, gk = torch.randn_like(q), torch.randn_like(k)
+    torch.autograd.backward([q, k], [gq, gk])
+    torch.autograd.backward([q_ref, k_ref], [gq.float(), gk.float()])
+    assert (ql.grad.float() - qr.grad).abs().max() <= 3e-2 and (kl.grad.float() - kr.grad).abs().max() <= 3e-2
