@@ -665,7 +665,7 @@ def extras(lib, device, desc, packed, state, lora_a, lora_b, peaks):
                         state2=state.state2, offset=state.offset)
         pk = packed.clone()
         copies.append((pk, st, weight_desc(pk, st)))
-    for m in (1, 16, 32, 64, 128, 256, 1024, 4096, 16384):
+    for m in (1, 8, 16, 32, 64, 128, 256, 1024, 4096, 16384):
         x = torch.randn(m, K_IN, device=device, generator=gen).bfloat16()
         y = torch.empty(m, N_OUT, device=device, dtype=torch.bfloat16)
         ws_bytes = lib.molt_workspace_bytes(_native.OP_LORA_FWD, m, N_OUT, K_IN, RANK)
@@ -681,7 +681,7 @@ def extras(lib, device, desc, packed, state, lora_a, lora_b, peaks):
         ms = graph_time_ms([call(c[2]) for c in copies], replays=20 if m <= 1024 else 3)
         flops = linear_flops(m, backward=False)
         bytes_alg = N_OUT * K_IN // 2 + nblocks + nblocks // 256 * 4 + m * K_IN * 2 + m * N_OUT * 2 + RANK * (K_IN + N_OUT) * 4
-        sweep.append({"m": m, "ms": ms, "path": "gemv" if m <= 16 else "few_tokens" if m <= 64 else "tcgen05", "tflops": flops / ms / 1e9,
+        sweep.append({"m": m, "ms": ms, "path": "gemv" if m <= 8 else "few_tokens" if m <= 128 else "tcgen05", "tflops": flops / ms / 1e9,
                       "frac_bf16_peak": flops / ms / 1e9 / peaks["bf16_tflops"],
                       "gbs": bytes_alg / ms / 1e6, "frac_hbm": bytes_alg / ms / 1e6 / peaks["hbm_gbs"]})
     del copies

@@ -39,7 +39,7 @@ extern "C" {
 #define MOLT_DTYPE_F32 1
 
 /* kernel selection for the linear ops; for aligned shapes (K % 64 == 0, N % 64 == 0, blocksize 64, rank <= 64) AUTO
- * picks, forward, GEMV for M <= 16 and the few-token kernel for M <= 64, else the tcgen05 GEMM; the general kernels
+ * picks, forward, GEMV for M <= 8 and the few-token kernel for M <= 128, else the tcgen05 GEMM; the general kernels
  * for every other shape. */
 #define MOLT_PATH_AUTO 0
 #define MOLT_PATH_GENERAL 1

@@ -169,8 +169,9 @@ static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m,
   requested &= 0xff;
   if (requested == MOLT_PATH_AUTO) {
     if (!aligned) *chosen = MOLT_PATH_GENERAL;
-    else if (forward && m <= 16) *chosen = MOLT_PATH_GEMV;
-    else if (forward && m <= 64) *chosen = MOLT_PATH_FEW_TOKENS;   // measured faster than the 256-token tiles up to here
+    else if (forward && m <= 8) *chosen = MOLT_PATH_GEMV;          // one token tile of the streaming kernel
+    else if (forward && m <= 128) *chosen = MOLT_PATH_FEW_TOKENS;  // measured faster than the GEMV's second token tile
+                                                                   // and than the GEMM's 256-token tiles
     else *chosen = MOLT_PATH_TCGEN05;
     return MOLT_OK;
   }

@@ -499,27 +499,30 @@ __global__ void __launch_bounds__(kLowrankThreads) skinny_lowrank_kernel(const _
 }
 
 // y[tok, row] = bf16(sum of the parts of the row's tile, in CTA order, + sum_j bf16(s B[row, j]) bf16(T[tok, j])),
-// T = sum of its K slices, rounded to bf16.  Grid (row tiles, groups of kFinishTokens tokens), one thread per row: many
-// blocks of few tokens when there are few tokens (the kernel is a chain of dependent round trips to memory and only
-// parallelism hides them), blocks of sixteen tokens otherwise (the adapter row is then read once per sixteen tokens).
-// The blocks of tile 0 also write T (bf16, [m, 64], zero padded) when the caller wants it.
-template <int kFinishTokens>
-__global__ void __launch_bounds__(BR) skinny_finish_kernel(const float* __restrict__ partial, int nt, int max_parts,
-                                                           Ranges ranges, int nb, long long units,
-                                                           const float* __restrict__ low_part, int m, int m_pad,
-                                                           const float* __restrict__ lora_b, float scaling, int rank,
-                                                           long long n, __nv_bfloat16* __restrict__ y,
-                                                           __nv_bfloat16* __restrict__ t_out) {
-  __shared__ float t_s[kFinishTokens][64];
-  const int tile = blockIdx.x, tok0 = blockIdx.y * kFinishTokens;
-  const long long row = (long long)tile * BR + threadIdx.x;
+// T = sum of its K slices, rounded to bf16.  Grid (row tiles, groups of 16 tokens); a block has one thread per (row,
+// group of kTok tokens), i.e. 128 * 16 / kTok threads: the kernel is a chain of dependent round trips to memory with
+// little arithmetic, so it wants many warps per SM rather than long threads.  The blocks of tile 0 also write T
+// (bf16, [m, 64], zero padded) when the caller wants it.
+template <int kTok>
+__global__ void __launch_bounds__(BR * 16 / kTok) skinny_finish_kernel(const float* __restrict__ partial, int nt, int max_parts,
+                                                                      Ranges ranges, int nb, long long units,
+                                                                      const float* __restrict__ low_part, int m, int m_pad,
+                                                                      const float* __restrict__ lora_b, float scaling,
+                                                                      int rank, long long n, __nv_bfloat16* __restrict__ y,
+                                                                      __nv_bfloat16* __restrict__ t_out) {
+  constexpr int kThreadsF = BR * 16 / kTok;
+  __shared__ float t_s[16][64];
+  const int tile = blockIdx.x;
+  const int r = threadIdx.x & (BR - 1);
+  const int tok0 = blockIdx.y * 16, tokq = tok0 + (threadIdx.x / BR) * kTok;   // first token of the block / of this thread
+  const long long row = (long long)tile * BR + r;
   const bool row_ok = row < n;
   // The CTAs whose ranges hold units of this tile: range c starts at floor(units c / ctas), so the last range that
   // starts at or before unit u is floor(((u + 1) ctas - 1) / units).
   const long long unit0 = (long long)tile * nb, unit1 = unit0 + nb;
   const int first = (int)(((unit0 + 1) * ranges.ctas - 1) / units);
   const int last = (int)((unit1 * ranges.ctas - 1) / units);
-  for (int i = threadIdx.x; i < kFinishTokens * rank; i += BR) {
+  for (int i = threadIdx.x; i < 16 * rank; i += kThreadsF) {
     const int t = i / rank, j = i - t * rank;
     float total = 0.f;
     if (tok0 + t < m) {
@@ -528,42 +531,43 @@ __global__ void __launch_bounds__(BR) skinny_finish_kernel(const float* __restri
     }
     t_s[t][j] = __bfloat162float(__float2bfloat16_rn(total));
   }
-  float acc[kFinishTokens];
+  float acc[kTok];
 #pragma unroll
-  for (int t = 0; t < kFinishTokens; ++t) acc[t] = 0.f;
+  for (int t = 0; t < kTok; ++t) acc[t] = 0.f;
   if (row_ok) {
     for (int c = first; c <= last; ++c) {
       const int slot = tile - range_begin(ranges, c) / nb;
-      const float* src = partial + ((size_t)c * max_parts + slot) * (size_t)(nt * BR) + threadIdx.x;
+      const float* src = partial + ((size_t)c * max_parts + slot) * (size_t)(nt * BR) + r;
 #pragma unroll
-      for (int t = 0; t < kFinishTokens; ++t)
-        if (tok0 + t < m) acc[t] += __ldcg(src + (size_t)(tok0 + t) * BR);
+      for (int t = 0; t < kTok; ++t)
+        if (tokq + t < m) acc[t] += __ldcg(src + (size_t)(tokq + t) * BR);
     }
   }
   __syncthreads();
   if (t_out != nullptr && tile == 0) {   // T itself, zero padded to 64 columns
-    for (int i = threadIdx.x; i < kFinishTokens * 64; i += BR) {
+    for (int i = threadIdx.x; i < 16 * 64; i += kThreadsF) {
       const int t = i >> 6, j = i & 63;
       if (tok0 + t < m) t_out[(size_t)(tok0 + t) * 64 + j] = __float2bfloat16_rn(j < rank ? t_s[t][j] : 0.f);
     }
   }
-  if (!row_ok) return;
+  if (!row_ok || tokq >= m) return;
+  const int tl = tokq - tok0;
   for (int j0 = 0; j0 < rank; j0 += 16) {
     float b[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j)
       b[j] = j0 + j < rank ? __bfloat162float(__float2bfloat16_rn(scaling * __ldg(lora_b + row * rank + j0 + j))) : 0.f;
 #pragma unroll
-    for (int t = 0; t < kFinishTokens; ++t) {
+    for (int t = 0; t < kTok; ++t) {
       float sum = 0.f;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) sum = fmaf(b[j], j0 + j < rank ? t_s[t][j0 + j] : 0.f, sum);
+      for (int j = 0; j < 16; ++j) sum = fmaf(b[j], j0 + j < rank ? t_s[tl + t][j0 + j] : 0.f, sum);
       acc[t] += sum;
     }
   }
 #pragma unroll
-  for (int t = 0; t < kFinishTokens; ++t)
-    if (tok0 + t < m) y[(size_t)(tok0 + t) * n + row] = __float2bfloat16_rn(acc[t]);
+  for (int t = 0; t < kTok; ++t)
+    if (tokq + t < m) y[(size_t)(tokq + t) * n + row] = __float2bfloat16_rn(acc[t]);
 }
 
 struct Plan {
@@ -700,17 +704,17 @@ int sm100_skinny_forward(const WeightView& w, const __nv_bfloat16* x, const floa
   if (int rc = launch_status("nf4_skinny_sm100_kernel")) return rc;
 
   // an ordinary launch: placing its blocks early, as a programmatic dependent, was measured to be slower
-  if (m <= 16) {
-    const dim3 fgrid((unsigned)p.tiles, (unsigned)((m + 3) / 4));
-    skinny_finish_kernel<4><<<fgrid, BR, 0, s>>>(partial, pl.nt, pl.max_parts, pl.ranges, p.num_kb,
-                                                  (long long)p.tiles * p.num_kb, low_part, m, pl.m_pad, lora_b, scaling,
-                                                  rank, w.n, y, t_out);
-  } else {
-    const dim3 fgrid((unsigned)p.tiles, (unsigned)((m + 15) / 16));
+  // few tokens: few blocks, so short threads and many warps per block; more tokens: the grid fills the machine anyway
+  // and long threads do less redundant work (adapter row, range arithmetic)
+  const dim3 fgrid((unsigned)p.tiles, (unsigned)((m + 15) / 16));
+  if (m <= 16)
+    skinny_finish_kernel<4><<<fgrid, BR * 4, 0, s>>>(partial, pl.nt, pl.max_parts, pl.ranges, p.num_kb,
+                                                      (long long)p.tiles * p.num_kb, low_part, m, pl.m_pad, lora_b,
+                                                      scaling, rank, w.n, y, t_out);
+  else
     skinny_finish_kernel<16><<<fgrid, BR, 0, s>>>(partial, pl.nt, pl.max_parts, pl.ranges, p.num_kb,
                                                    (long long)p.tiles * p.num_kb, low_part, m, pl.m_pad, lora_b, scaling,
                                                    rank, w.n, y, t_out);
-  }
   return launch_status("skinny_finish_kernel");
 }
 

@@ -36,9 +36,9 @@ def weight_desc(packed: torch.Tensor, quant_state: Any) -> _native.NF4Desc:
 def weight_desc_for_tokens(packed: torch.Tensor, quant_state: Any, tokens: int) -> _native.NF4Desc:
     """Descriptor to use for a call with this many tokens.  A double-quantised absmax is resolved to fp32 once and the
     result cached on the state, as the reference does (methods/nf4_backward.py:145-164); the tensor-core kernels then
-    read it directly instead of resolving it in front of every GEMM.  Up to 64 tokens the GEMV and few-token kernels
+    read it directly instead of resolving it in front of every GEMM.  Up to 128 tokens the GEMV and few-token kernels
     read the 8-bit form themselves (fewer bytes), so those calls keep the state's own descriptor."""
-    if tokens <= 64 or not getattr(quant_state, "nested", False):
+    if tokens <= 128 or not getattr(quant_state, "nested", False):
         return weight_desc(packed, quant_state)
     cached = getattr(quant_state, "_molt_desc_resolved", None)
     key = (packed.data_ptr(), quant_state.absmax.data_ptr())
