@@ -126,8 +126,9 @@ struct Params {
 #define MOLT_CTRACE(role, index) do {} while (0)
 #endif
 
+// 88 registers per thread leave room on the SM for the blocks of the low-rank side kernel, which runs beside this one.
 template <int NT, bool kNested, bool kTable>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __maxnreg__(88)
 nf4_skinny_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_packed,
                         const __grid_constant__ Params p) {
   extern __shared__ unsigned char smem_dyn[];
@@ -175,6 +176,11 @@ nf4_skinny_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // Launched as a programmatic dependent of the kernel before it in the stream: the set-up above touches no global
+  // memory; nothing below runs before that kernel has completed and its writes are visible.  Then the kernel behind
+  // (the low-rank side kernel, which needs nothing from this one) may start beside this grid.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (kNested) {
     float* table = reinterpret_cast<float*>(smem_dyn + (code2_0 - raw));
     for (int i = threadIdx.x; i < 256; i += blockDim.x) table[i] = __ldg(p.code2 + i);
@@ -443,18 +449,16 @@ nf4_skinny_sm100_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
-  // the kernel in front of this one (the low-rank input's first stage) has completed before this grid does, so the
-  // kernel behind may read both results
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) MOLT_CTRACE(15, 3);
 }
 
 // Low-rank input, first stage: part[ks][tok][j] = sum over the ks-th slice of K of x[tok][k] * bf16(A[j][k]).
-// Grid (adapter rows, K slices, groups of 16 tokens); the slices are added in a fixed order by the reader.
-__global__ void __launch_bounds__(kLowrankThreads) skinny_lowrank_kernel(const __nv_bfloat16* __restrict__ x,
+// Grid (adapter rows, K slices, groups of 16 tokens); the slices are added in a fixed order by the reader.  Launched
+// behind the streaming kernel as its programmatic dependent and without waiting for it (it reads only x and A), so its
+// blocks run beside that grid on the registers and shared memory it leaves free.
+__global__ void __maxnreg__(64) skinny_lowrank_kernel(const __nv_bfloat16* __restrict__ x,
                                                                          const float* __restrict__ a, int m, int m_pad,
                                                                          long long k, float* __restrict__ part) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the streaming kernel does not read this result
   __shared__ float red[kLowrankThreads / 32][16];
   const int j = blockIdx.x, ks = blockIdx.y, tok0 = blockIdx.z * 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -496,6 +500,9 @@ __global__ void __launch_bounds__(kLowrankThreads) skinny_lowrank_kernel(const _
     for (int wv = 0; wv < kLowrankThreads / 32; ++wv) total += red[wv][t];
     part[((size_t)ks * m_pad + tok0 + t) * 64 + j] = total;
   }
+  // This grid must not be seen as complete before the streaming kernel in front of it is: the kernel behind is an
+  // ordinary launch that orders itself after this one only.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // y[tok, row] = bf16(sum of the parts of the row's tile, in CTA order, + sum_j bf16(s B[row, j]) bf16(T[tok, j])),
@@ -654,10 +661,6 @@ int sm100_skinny_forward(const WeightView& w, const __nv_bfloat16* x, const floa
   }
 #endif
 
-  skinny_lowrank_kernel<<<dim3((unsigned)rank, kLowrankSlices, (unsigned)(pl.m_pad / 16)), kLowrankThreads, 0, s>>>(
-      x, lora_a, m, pl.m_pad, w.k, low_part);
-  if (int rc = launch_status("skinny_lowrank_kernel")) return rc;
-
   const bool nested = w.absmax_kind == MOLT_ABSMAX_NESTED;
   const bool table = !(flags & kGemmExactDecode);   // table decode unless the caller asks for the dequantiser's bits
   static thread_local bool configured[64][4][2][2] = {};
@@ -702,6 +705,17 @@ int sm100_skinny_forward(const WeightView& w, const __nv_bfloat16* x, const floa
 #undef MOLT_SKINNY_BY_NT
 #undef MOLT_SKINNY_LAUNCH
   if (int rc = launch_status("nf4_skinny_sm100_kernel")) return rc;
+
+  {   // the low-rank input, beside the streaming kernel (the second stage behind both is an ordinary launch)
+    cudaLaunchConfig_t lcfg = {};
+    lcfg.gridDim = dim3((unsigned)rank, kLowrankSlices, (unsigned)(pl.m_pad / 16));
+    lcfg.blockDim = dim3(kLowrankThreads);
+    lcfg.stream = s;
+    lcfg.attrs = attr;
+    lcfg.numAttrs = 1;
+    MOLT_CUDA(cudaLaunchKernelEx(&lcfg, skinny_lowrank_kernel, x, lora_a, m, pl.m_pad, (long long)w.k, low_part));
+    if (int rc = launch_status("skinny_lowrank_kernel")) return rc;
+  }
 
   // an ordinary launch: placing its blocks early, as a programmatic dependent, was measured to be slower
   // few tokens: few blocks, so short threads and many warps per block; more tokens: the grid fills the machine anyway
