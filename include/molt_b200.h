@@ -230,6 +230,45 @@ size_t molt_dense_gemm_workspace_bytes(void);
 int molt_dense_gemm(const void* weight, int64_t n, int64_t k, const void* in, void* out, int64_t m,
                     int contract_over_rows, void* workspace, size_t workspace_bytes, int flags, uintptr_t stream);
 
+/* bf16 "shadow" operands of one adapter for the tensor-core kernels, so that they need not be rebuilt from the fp32
+ * masters in front of every call: a16 [rp, k] = bf16(A) (rp = rank rounded up to 16, extra rows zero), bs [n, 64] =
+ * bf16(scaling * B) (extra columns zero), bt [rp, n] = its transpose.  The caller owns the buffers and refreshes them
+ * with molt_lora_shadow_refresh whenever A or B changed (i.e. after each optimizer step).  Counterpart of the
+ * reference's bf16 LoRA shadows (methods/lora_shadow.py:19-141). */
+typedef struct molt_lora_shadow {
+  const void* a16;
+  const void* bs;
+  const void* bt;
+} molt_lora_shadow;
+
+/* One adapter of a refresh: masters in, shadows out (all device pointers). */
+typedef struct molt_lora_shadow_item {
+  const float* lora_a; /* [rank, k] */
+  const float* lora_b; /* [n, rank] */
+  float scaling;
+  int32_t rank;
+  int64_t n, k;        /* multiples of 64 */
+  void* a16;
+  void* bs;
+  void* bt;
+} molt_lora_shadow_item;
+
+/* Rebuilds the shadows of `count` adapters in ONE launch; `items` is an array in DEVICE memory (the host builds it
+ * once).  Meant to follow molt_adamw_step in the stream. */
+int molt_lora_shadow_refresh(const molt_lora_shadow_item* items, int count, int64_t max_n, int64_t max_k,
+                             uintptr_t stream);
+
+/* molt_nf4_lora_fwd / molt_nf4_lora_bwd with the adapter's shadows given: the tensor-core path skips its operand
+ * preparation (shadow may be NULL: then exactly the plain entry points).  lora_a / lora_b are still needed (kernels
+ * for few tokens and general shapes read the masters). */
+int molt_nf4_lora_fwd_prepared(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
+                               float scaling, int rank, const molt_lora_shadow* shadow, void* y, int64_t m, void* t_out,
+                               void* workspace, size_t workspace_bytes, int path, uintptr_t stream);
+int molt_nf4_lora_bwd_prepared(const molt_nf4_desc* w, const void* x, const void* dy, const float* lora_a,
+                               const float* lora_b, float scaling, int rank, const molt_lora_shadow* shadow, void* dx,
+                               float* da, float* db, int64_t m, const void* t_in, int accumulate, void* workspace,
+                               size_t workspace_bytes, int path, uintptr_t stream);
+
 /* Gated MLP block: gate = P_g(x), up = P_u(x), y = P_d(silu(gate) * up).
  * gate_out [m, inter] is always written (it is what the replay schedule saves); up_out may be NULL when the
  * caller re-materialises `up` in backward.  Replaces _ResidualRecipeGatedNF4LoRA.forward
@@ -240,6 +279,7 @@ typedef struct molt_lora_proj {
   const float* lora_b;  /* [n, rank] */
   float scaling;
   int32_t rank;
+  const struct molt_lora_shadow* shadow; /* optional bf16 operands kept up to date by the caller (see below), or NULL */
 } molt_lora_proj;
 
 /* Scratch bytes of molt_mlp_fwd (op = MOLT_OP_MLP_FWD) / molt_mlp_bwd (op = MOLT_OP_MLP_BWD) for m tokens;

@@ -32,7 +32,8 @@ EXPORTS = (
     "molt_version", "molt_last_error", "molt_launch_count", "molt_set_option", "molt_read_status", "molt_nf4_dequant", "molt_nf4_resolve_absmax",
     "molt_workspace_bytes", "molt_nf4_lora_fwd", "molt_nf4_lora_fwd_static", "molt_nf4_lora_bwd", "molt_nf4_dx", "molt_nf4_gemv",
     "molt_swiglu_fwd", "molt_swiglu_bwd", "molt_rmsnorm_fwd", "molt_rmsnorm_bwd", "molt_add_rmsnorm_fwd",
-    "molt_add_rmsnorm_bwd", "molt_rope", "molt_adamw_step", "molt_dense_gemm",
+    "molt_add_rmsnorm_bwd", "molt_rope", "molt_adamw_step", "molt_dense_gemm", "molt_nf4_lora_fwd_prepared",
+    "molt_nf4_lora_bwd_prepared", "molt_lora_shadow_refresh",
     "molt_dense_gemm_workspace_bytes", "molt_ce_softmax_grad", "molt_mlp_workspace_bytes", "molt_mlp_fwd",
     "molt_mlp_bwd",
 )
@@ -58,6 +59,28 @@ class NF4Desc(ctypes.Structure):
     ]
 
 
+class LoraShadow(ctypes.Structure):
+    """Mirror of ``molt_lora_shadow``: bf16 operands of one adapter kept up to date by the caller."""
+
+    _fields_ = [("a16", ctypes.c_void_p), ("bs", ctypes.c_void_p), ("bt", ctypes.c_void_p)]
+
+
+class LoraShadowItem(ctypes.Structure):
+    """Mirror of ``molt_lora_shadow_item``."""
+
+    _fields_ = [
+        ("lora_a", ctypes.c_void_p),
+        ("lora_b", ctypes.c_void_p),
+        ("scaling", ctypes.c_float),
+        ("rank", ctypes.c_int32),
+        ("n", ctypes.c_int64),
+        ("k", ctypes.c_int64),
+        ("a16", ctypes.c_void_p),
+        ("bs", ctypes.c_void_p),
+        ("bt", ctypes.c_void_p),
+    ]
+
+
 class LoraProj(ctypes.Structure):
     """Mirror of ``molt_lora_proj``."""
 
@@ -67,6 +90,7 @@ class LoraProj(ctypes.Structure):
         ("lora_b", ctypes.c_void_p),
         ("scaling", ctypes.c_float),
         ("rank", ctypes.c_int32),
+        ("shadow", ctypes.POINTER(LoraShadow)),
     ]
 
 
@@ -97,6 +121,14 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.molt_workspace_bytes.argtypes = [i32, i64, i64, i64, i32]
     lib.molt_nf4_lora_fwd.restype = i32
     lib.molt_nf4_lora_fwd.argtypes = [desc, vp, vp, vp, f32, i32, vp, i64, vp, vp, sz, i32, up]
+    shadow = ctypes.POINTER(LoraShadow)
+    lib.molt_nf4_lora_fwd_prepared.restype = i32
+    lib.molt_nf4_lora_fwd_prepared.argtypes = [desc, vp, vp, vp, f32, i32, shadow, vp, i64, vp, vp, sz, i32, up]
+    lib.molt_nf4_lora_bwd_prepared.restype = i32
+    lib.molt_nf4_lora_bwd_prepared.argtypes = [desc, vp, vp, vp, vp, f32, i32, shadow, vp, vp, vp, i64, vp, i32, vp, sz,
+                                               i32, up]
+    lib.molt_lora_shadow_refresh.restype = i32
+    lib.molt_lora_shadow_refresh.argtypes = [vp, i32, i64, i64, up]
     lib.molt_nf4_lora_fwd_static.restype = i32
     lib.molt_nf4_lora_fwd_static.argtypes = [desc, vp, vp, vp, f32, i32, vp, i64, i32, up]
     lib.molt_nf4_lora_bwd.restype = i32

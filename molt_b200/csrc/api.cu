@@ -217,7 +217,7 @@ static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s,
 // ---- forward ---------------------------------------------------------------------------------------
 static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
                          float scaling, int rank, void* y, int64_t m, void* t_out, Arena& arena, int path,
-                         cudaStream_t s, int flags = 0) {
+                         cudaStream_t s, int flags = 0, const molt_lora_shadow* shadow = nullptr) {
   const WeightView view = make_view(w);
   const int rp = padded_rank(rank);
   auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -262,9 +262,12 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
     if (int rc = general_rowsum(true, xb, lora_a, 1.0f, m, w->k, rank, t, 64, s)) return rc;
     return general_forward(view, xb, t, 64, lora_b, scaling, rank, yb, m, s);
   }
-  // tcgen05 path
-  auto* a16 = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
-  auto* bs = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)w->n * 64 * 2));
+  // tcgen05 path; with shadows the bf16 operands are the caller's and only a nested absmax is left to prepare
+  const bool shadowed = shadow != nullptr && shadow->a16 != nullptr && shadow->bs != nullptr;
+  auto* a16 = shadowed ? const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(shadow->a16))
+                       : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
+  auto* bs = shadowed ? const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(shadow->bs))
+                      : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)w->n * 64 * 2));
   const float* absmax = nullptr;
   float* to_resolve = nullptr;
   if (int rc = resolved_absmax(w, arena, s, &absmax, &to_resolve)) return rc;
@@ -274,7 +277,9 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
   MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
   MOLT_REQUIRE((reinterpret_cast<uintptr_t>(lora_a) & 15) == 0, MOLT_E_CAPABILITY,
                "molt_nf4_lora_fwd: lora_a must start on a 16-byte boundary for the tensor-core path");
-  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, bs, nullptr, &view, to_resolve, s)) return rc;
+  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, shadowed ? nullptr : a16, shadowed ? nullptr : bs,
+                         nullptr, &view, to_resolve, s))
+    return rc;
   if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t, s)) return rc;
   return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, split, flags, s);
 }
@@ -282,7 +287,8 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
 // ---- backward --------------------------------------------------------------------------------------
 static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, const float* lora_a,
                          const float* lora_b, float scaling, int rank, void* dx, float* da, float* db, int64_t m,
-                         const void* t_in, int accumulate, Arena& arena, int path, cudaStream_t s, int flags = 0) {
+                         const void* t_in, int accumulate, Arena& arena, int path, cudaStream_t s, int flags = 0,
+                         const molt_lora_shadow* shadow = nullptr) {
   const WeightView view = make_view(w);
   const int rp = padded_rank(rank);
   auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -311,8 +317,11 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
     }
     return MOLT_OK;
   }
-  auto* a16 = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
-  auto* bt = reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->n * 2));
+  const bool shadowed = shadow != nullptr && shadow->a16 != nullptr && shadow->bt != nullptr;
+  auto* a16 = shadowed ? const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(shadow->a16))
+                       : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->k * 2));
+  auto* bt = shadowed ? const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(shadow->bt))
+                      : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)rp * w->n * 2));
   float* partial_a = nullptr;
   float* partial_b = nullptr;
   if (want_grads) {
@@ -329,7 +338,9 @@ static int lora_bwd_impl(const molt_nf4_desc* w, const void* x, const void* dy, 
   MOLT_REQUIRE(fits, MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace too small");
   MOLT_REQUIRE((reinterpret_cast<uintptr_t>(lora_a) & 15) == 0, MOLT_E_CAPABILITY,
                "molt_nf4_lora_bwd: lora_a must start on a 16-byte boundary for the tensor-core path");
-  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, a16, nullptr, bt, &view, to_resolve, s)) return rc;
+  if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, shadowed ? nullptr : a16, nullptr,
+                         shadowed ? nullptr : bt, &view, to_resolve, s))
+    return rc;
   if (int rc = rowsum_mma(gb, bt, rp, m, w->n, u, s)) return rc;  // U = dY . (sB)
   if (dxb != nullptr)
     if (int rc = sm100_gemm(true, view, absmax, gb, u, a16, rp, dxb, m, split, flags, s)) return rc;
@@ -460,6 +471,14 @@ extern "C" size_t molt_workspace_bytes(int op, int64_t m, int64_t n, int64_t k, 
 extern "C" int molt_nf4_lora_fwd(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
                                  float scaling, int rank, void* y, int64_t m, void* t_out, void* workspace,
                                  size_t workspace_bytes, int path, uintptr_t stream) {
+  return molt_nf4_lora_fwd_prepared(w, x, lora_a, lora_b, scaling, rank, nullptr, y, m, t_out, workspace, workspace_bytes,
+                                    path, stream);
+}
+
+extern "C" int molt_nf4_lora_fwd_prepared(const molt_nf4_desc* w, const void* x, const float* lora_a,
+                                          const float* lora_b, float scaling, int rank, const molt_lora_shadow* shadow,
+                                          void* y, int64_t m, void* t_out, void* workspace, size_t workspace_bytes,
+                                          int path, uintptr_t stream) {
   int64_t blocks = 0;
   if (int rc = check_linear_args("molt_nf4_lora_fwd", w, rank, m, &blocks)) return rc;
   MOLT_REQUIRE(x && lora_a && lora_b && y, MOLT_E_VALUE, "molt_nf4_lora_fwd: NULL tensor pointer");
@@ -471,7 +490,7 @@ extern "C" int molt_nf4_lora_fwd(const molt_nf4_desc* w, const void* x, const fl
   MOLT_REQUIRE(workspace != nullptr, MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace is NULL");
   Arena arena(workspace, workspace_bytes);
   return lora_fwd_impl(w, x, lora_a, lora_b, scaling, rank, y, m, t_out, arena, chosen,
-                       reinterpret_cast<cudaStream_t>(stream), flags);
+                       reinterpret_cast<cudaStream_t>(stream), flags, shadow);
 }
 
 extern "C" int molt_nf4_gemv(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
@@ -485,6 +504,14 @@ extern "C" int molt_nf4_lora_bwd(const molt_nf4_desc* w, const void* x, const vo
                                  const float* lora_b, float scaling, int rank, void* dx, float* da, float* db,
                                  int64_t m, const void* t_in, int accumulate, void* workspace, size_t workspace_bytes,
                                  int path, uintptr_t stream) {
+  return molt_nf4_lora_bwd_prepared(w, x, dy, lora_a, lora_b, scaling, rank, nullptr, dx, da, db, m, t_in, accumulate,
+                                    workspace, workspace_bytes, path, stream);
+}
+
+extern "C" int molt_nf4_lora_bwd_prepared(const molt_nf4_desc* w, const void* x, const void* dy, const float* lora_a,
+                                          const float* lora_b, float scaling, int rank, const molt_lora_shadow* shadow,
+                                          void* dx, float* da, float* db, int64_t m, const void* t_in, int accumulate,
+                                          void* workspace, size_t workspace_bytes, int path, uintptr_t stream) {
   int64_t blocks = 0;
   if (int rc = check_linear_args("molt_nf4_lora_bwd", w, rank, m, &blocks)) return rc;
   MOLT_REQUIRE(dy && lora_a && lora_b, MOLT_E_VALUE, "molt_nf4_lora_bwd: NULL tensor pointer");
@@ -507,7 +534,15 @@ extern "C" int molt_nf4_lora_bwd(const molt_nf4_desc* w, const void* x, const vo
   MOLT_REQUIRE(workspace != nullptr, MOLT_E_VALUE, "molt_nf4_lora_bwd: workspace is NULL");
   Arena arena(workspace, workspace_bytes);
   return lora_bwd_impl(w, x, dy, lora_a, lora_b, scaling, rank, dx, da, db, m, t_in, accumulate, arena, chosen,
-                       reinterpret_cast<cudaStream_t>(stream), flags);
+                       reinterpret_cast<cudaStream_t>(stream), flags, shadow);
+}
+
+extern "C" int molt_lora_shadow_refresh(const molt_lora_shadow_item* items, int count, int64_t max_n, int64_t max_k,
+                                        uintptr_t stream) {
+  MOLT_REQUIRE(count >= 0 && (count == 0 || items != nullptr), MOLT_E_VALUE, "molt_lora_shadow_refresh: bad item list");
+  MOLT_REQUIRE(max_n > 0 && max_k > 0 && max_n % 64 == 0 && max_k % 64 == 0, MOLT_E_VALUE,
+               "molt_lora_shadow_refresh: max_n and max_k must be positive multiples of 64");
+  return lora_shadow_refresh(items, count, max_n, max_k, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int molt_nf4_dx(const molt_nf4_desc* w, const void* dy, const void* lora_grad, const void* lora_a,
@@ -610,7 +645,7 @@ static int mlp_fwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, co
       if (int rc = molt_swiglu_fwd(gate_out, up_buf, hidden, m * inter, MOLT_DTYPE_BF16, reinterpret_cast<uintptr_t>(s)))
         return rc;
     if (int rc = lora_fwd_impl(projs[i]->w, ins[i], projs[i]->lora_a, projs[i]->lora_b, projs[i]->scaling,
-                               projs[i]->rank, outs[i], m, nullptr, arena, chosen, s))
+                               projs[i]->rank, outs[i], m, nullptr, arena, chosen, s, 0, projs[i]->shadow))
       return rc;
     if (arena.used > high) high = arena.used;
   }
@@ -637,7 +672,7 @@ static int mlp_bwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, co
   if (up_saved == nullptr) {
     if (int rc = pick_path(MOLT_PATH_AUTO, up->w, up->rank, m, true, &chosen)) return rc;
     if (int rc = lora_fwd_impl(up->w, x, up->lora_a, up->lora_b, up->scaling, up->rank, up_buf, m, nullptr, arena,
-                               chosen, s))
+                               chosen, s, 0, up->shadow))
       return rc;
     up_val = up_buf;
     if (arena.used > high) high = arena.used;
@@ -649,7 +684,7 @@ static int mlp_bwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, co
   arena.used = mark;
   if (int rc = pick_path(MOLT_PATH_AUTO, down->w, down->rank, m, false, &chosen)) return rc;
   if (int rc = lora_bwd_impl(down->w, hidden, dy, down->lora_a, down->lora_b, down->scaling, down->rank, dh, grads[4],
-                             grads[5], m, nullptr, accumulate, arena, chosen, s))
+                             grads[5], m, nullptr, accumulate, arena, chosen, s, 0, down->shadow))
     return rc;
   if (arena.used > high) high = arena.used;
   // 4. dup = dh * silu(gate), dgate = silu'(gate) * dh * up (:385-387); dgate overwrites dh
@@ -659,13 +694,13 @@ static int mlp_bwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, co
   arena.used = mark;
   if (int rc = pick_path(MOLT_PATH_AUTO, gate->w, gate->rank, m, false, &chosen)) return rc;
   if (int rc = lora_bwd_impl(gate->w, x, dh, gate->lora_a, gate->lora_b, gate->scaling, gate->rank, dx, grads[0],
-                             grads[1], m, nullptr, accumulate, arena, chosen, s))
+                             grads[1], m, nullptr, accumulate, arena, chosen, s, 0, gate->shadow))
     return rc;
   if (arena.used > high) high = arena.used;
   arena.used = mark;
   if (int rc = pick_path(MOLT_PATH_AUTO, up->w, up->rank, m, false, &chosen)) return rc;
   if (int rc = lora_bwd_impl(up->w, x, dup_buf, up->lora_a, up->lora_b, up->scaling, up->rank, dx_up, grads[2],
-                             grads[3], m, nullptr, accumulate, arena, chosen, s))
+                             grads[3], m, nullptr, accumulate, arena, chosen, s, 0, up->shadow))
     return rc;
   if (arena.used > high) high = arena.used;
   arena.used = high;

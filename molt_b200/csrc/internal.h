@@ -22,6 +22,8 @@ int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, l
               cudaStream_t s);
 int rowsum_mma(const __nv_bfloat16* in, const __nv_bfloat16* wt, int rp, long long m, long long cols,
                __nv_bfloat16* out, cudaStream_t s);
+// the bf16 operands of `count` adapters in one launch (items: device array)
+int lora_shadow_refresh(const molt_lora_shadow_item* items, int count, long long max_n, long long max_k, cudaStream_t s);
 // low[m, 64] = lora_grad[m, rank] zero-padded; a16[rp, k] = bf16(scaling * A), rows >= rank zero (A bf16 or fp32)
 int dx_lora_prep(const __nv_bfloat16* lora_grad, int rank, long long m, const void* lora_a, int lora_a_dtype,
                  float scaling, int rp, long long k, __nv_bfloat16* low, __nv_bfloat16* a16, cudaStream_t s);

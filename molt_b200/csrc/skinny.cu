@@ -24,16 +24,15 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 // Any of the three outputs may be NULL.  The same launch also resolves a nested absmax to fp32 when `resolved` is given
 // (one launch instead of two in front of every GEMM).
 // ------------------------------------------------------------------------------------------------
-__global__ void lora_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, float scaling, int rank,
-                                 int rp, long long n, long long k, __nv_bfloat16* __restrict__ a16,
-                                 __nv_bfloat16* __restrict__ bs, __nv_bfloat16* __restrict__ bt, WeightView w,
-                                 float* __restrict__ resolved, long long absmax_blocks) {
-  // One item per thread out of the four lists laid end to end, so that all of them are in flight together:
-  // a16 (8 elements), bs (one row of 64), bt (one column), resolved absmax (4 blocks).
+// One item of the preparation lists of one adapter (a16: 8 elements, bs: one row of 64, bt: one column); returns the
+// index left over when i lies past the three lists, or -1 when the item was handled.
+__device__ __forceinline__ long long lora_prep_item(long long i, const float* __restrict__ a, const float* __restrict__ b,
+                                                    float scaling, int rank, int rp, long long n, long long k,
+                                                    __nv_bfloat16* __restrict__ a16, __nv_bfloat16* __restrict__ bs,
+                                                    __nv_bfloat16* __restrict__ bt) {
   const long long items_a = a16 != nullptr ? (long long)rp * k / 8 : 0;
   const long long items_bs = bs != nullptr ? n : 0;
   const long long items_bt = bt != nullptr ? n : 0;
-  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (i < items_a) {
     const long long e = i * 8;
     const int r = (int)(e / k);
@@ -44,7 +43,7 @@ __global__ void lora_prep_kernel(const float* __restrict__ a, const float* __res
       out[2] = pack_bf16x2(hi.x, hi.y); out[3] = pack_bf16x2(hi.z, hi.w);
     }
     *reinterpret_cast<uint4*>(a16 + e) = make_uint4(out[0], out[1], out[2], out[3]);
-    return;
+    return -1;
   }
   i -= items_a;
   if (i < items_bs) {   // one row of B -> one 64-wide row of bs (128 bytes)
@@ -58,15 +57,26 @@ __global__ void lora_prep_kernel(const float* __restrict__ a, const float* __res
     uint4* dst = reinterpret_cast<uint4*>(bs + i * 64);
 #pragma unroll
     for (int q = 0; q < 8; ++q) dst[q] = make_uint4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
-    return;
+    return -1;
   }
   i -= items_bs;
   if (i < items_bt) {   // one row of B -> one column of bt: neighbouring threads write neighbouring elements of every row
     for (int r = 0; r < rp; ++r)
       bt[(long long)r * n + i] = __float2bfloat16_rn(r < rank ? scaling * __ldg(b + i * rank + r) : 0.f);
-    return;
+    return -1;
   }
-  i -= items_bt;
+  return i - items_bt;
+}
+
+__global__ void lora_prep_kernel(const float* __restrict__ a, const float* __restrict__ b, float scaling, int rank,
+                                 int rp, long long n, long long k, __nv_bfloat16* __restrict__ a16,
+                                 __nv_bfloat16* __restrict__ bs, __nv_bfloat16* __restrict__ bt, WeightView w,
+                                 float* __restrict__ resolved, long long absmax_blocks) {
+  // One item per thread out of the four lists laid end to end, so that all of them are in flight together:
+  // a16 (8 elements), bs (one row of 64), bt (one column), resolved absmax (4 blocks).
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  i = lora_prep_item(i, a, b, scaling, rank, rp, n, k, a16, bs, bt);
+  if (i < 0) return;
   if (resolved != nullptr) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -74,6 +84,16 @@ __global__ void lora_prep_kernel(const float* __restrict__ a, const float* __res
       if (blk < absmax_blocks) resolved[blk] = load_absmax(w, blk);
     }
   }
+}
+
+// The shadows of many adapters in one launch: blockIdx.y = adapter, the blocks of a row walk its item lists.
+__global__ void __launch_bounds__(256) lora_shadow_refresh_kernel(const molt_lora_shadow_item* __restrict__ items) {
+  const molt_lora_shadow_item it = items[blockIdx.y];
+  const int rp = (it.rank + 15) / 16 * 16;
+  const long long total = (long long)rp * it.k / 8 + 2 * it.n;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    lora_prep_item(i, it.lora_a, it.lora_b, it.scaling, it.rank, rp, it.n, it.k, reinterpret_cast<__nv_bfloat16*>(it.a16),
+                   reinterpret_cast<__nv_bfloat16*>(it.bs), reinterpret_cast<__nv_bfloat16*>(it.bt));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -352,6 +372,15 @@ int lora_prep(const float* a, const float* b, float scaling, int rank, int rp, l
   lora_prep_kernel<<<(unsigned)((items + 255) / 256), 256, 0, s>>>(a, b, scaling, rank, rp, n, k, a16, bs, bt, view,
                                                                     absmax_blocks > 0 ? resolved : nullptr, absmax_blocks);
   return launch_status("lora_prep_kernel");
+}
+
+int lora_shadow_refresh(const molt_lora_shadow_item* items, int count, long long max_n, long long max_k, cudaStream_t s) {
+  if (count == 0) return MOLT_OK;
+  const long long most = 64 * max_k / 8 + 2 * max_n;   // items of the largest adapter (rank <= 64)
+  long long blocks = (most + 255) / 256;
+  if (blocks > 64) blocks = 64;                        // grid-stride: 64 x count blocks fill the device
+  lora_shadow_refresh_kernel<<<dim3((unsigned)blocks, (unsigned)count), 256, 0, s>>>(items);
+  return launch_status("lora_shadow_refresh_kernel");
 }
 
 int dx_lora_prep(const __nv_bfloat16* lora_grad, int rank, long long m, const void* lora_a, int lora_a_dtype,

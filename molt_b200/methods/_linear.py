@@ -75,9 +75,66 @@ def check_linear_inputs(x: torch.Tensor, packed: torch.Tensor, lora_a: torch.Ten
         raise ValueError("LoRA A must be [rank, in_features] and B [out_features, rank]")
 
 
+SHADOW_SLOT = "_molt_lora_shadow"   # attribute of a LoRA A master: the adapter's LoraShadows (bf16 operands), if any
+
+
+class LoraShadows:
+    """bf16 operands of one adapter for the tensor-core kernels (``molt_lora_shadow``): ``a16 [rp, k]``, ``bs [n, 64]``
+    = bf16(scaling * B), ``bt [rp, n]`` = its transpose, so that they are not rebuilt from the fp32 masters in front of every call
+    (reference methods/lora_shadow.py:19-141).  Whoever changes the masters refreshes them afterwards (:class:`ShadowTable`);
+    ``attach`` makes the fused ops use them (found through the A master)."""
+
+    def __init__(self, lora_a: torch.Tensor, lora_b: torch.Tensor, scaling: float):
+        rank, k = (int(v) for v in lora_a.shape)
+        n = int(lora_b.shape[0])
+        rp = (rank + 15) // 16 * 16
+        dev = lora_a.device
+        self.lora_a, self.lora_b, self.scaling, self.rank, self.n, self.k = lora_a, lora_b, float(scaling), rank, n, k
+        self.a16 = torch.zeros((rp, k), dtype=torch.bfloat16, device=dev)
+        self.bs = torch.zeros((n, 64), dtype=torch.bfloat16, device=dev)
+        self.bt = torch.zeros((rp, n), dtype=torch.bfloat16, device=dev)
+        self.struct = _native.LoraShadow(self.a16.data_ptr(), self.bs.data_ptr(), self.bt.data_ptr())
+
+    def item(self) -> _native.LoraShadowItem:
+        return _native.LoraShadowItem(self.lora_a.data_ptr(), self.lora_b.data_ptr(), self.scaling, self.rank, self.n,
+                                      self.k, self.a16.data_ptr(), self.bs.data_ptr(), self.bt.data_ptr())
+
+    def attach(self) -> None:
+        setattr(self.lora_a, SHADOW_SLOT, self)
+
+    def detach(self) -> None:
+        if getattr(self.lora_a, SHADOW_SLOT, None) is self:
+            delattr(self.lora_a, SHADOW_SLOT)
+
+
+class ShadowTable:
+    """The item list of many adapters in device memory, built once; ``refresh()`` rebuilds all their shadows in one
+    launch on the current stream (call it after the optimizer step)."""
+
+    def __init__(self, shadows):
+        self.shadows = list(shadows)
+        if not self.shadows:
+            raise ValueError("no adapters")
+        items = (_native.LoraShadowItem * len(self.shadows))(*[s.item() for s in self.shadows])
+        raw = torch.frombuffer(bytearray(bytes(items)), dtype=torch.uint8)
+        self.device = self.shadows[0].a16.device
+        self.table = raw.to(self.device)
+        self.max_n = max(s.n for s in self.shadows)
+        self.max_k = max(s.k for s in self.shadows)
+
+    def refresh(self) -> None:
+        with torch.cuda.device(self.device):
+            _native.check(_native.library().molt_lora_shadow_refresh(self.table.data_ptr(), len(self.shadows), self.max_n,
+                                                                     self.max_k, _native.stream_handle(self.device)))
+
+
+def _shadow_struct(shadow: Optional["LoraShadows"]):
+    return ctypes.byref(shadow.struct) if shadow is not None else None
+
+
 def linear_forward(desc: _native.NF4Desc, x2: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tensor,
-                   scaling: float, keep_low_rank: bool, path: int = _native.PATH_AUTO
-                   ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                   scaling: float, keep_low_rank: bool, path: int = _native.PATH_AUTO,
+                   shadow: Optional[LoraShadows] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """y = x . deq(W)^T + s (x A^T) B^T for a 2-D bf16 x.  Returns (y, T) where T = x A^T padded to 64 columns."""
     n, k, m, rank = int(desc.n), int(desc.k), int(x2.shape[0]), int(lora_a.shape[0])
     if x2.shape[1] != k or lora_a.shape[1] != k or lora_b.shape[0] != n:
@@ -93,16 +150,18 @@ def linear_forward(desc: _native.NF4Desc, x2: torch.Tensor, lora_a: torch.Tensor
     nbytes = lib.molt_workspace_bytes(_native.OP_LORA_FWD, m, n, k, rank)
     ws = _native.workspace(nbytes, device)
     with torch.cuda.device(device):
-        _native.check(lib.molt_nf4_lora_fwd(
+        _native.check(lib.molt_nf4_lora_fwd_prepared(
             ctypes.byref(desc), x2.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(), float(scaling), rank,
-            y.data_ptr(), m, _native.ptr(t), ws.data_ptr(), ws.numel(), path, _native.stream_handle(device)))
+            _shadow_struct(shadow), y.data_ptr(), m, _native.ptr(t), ws.data_ptr(), ws.numel(), path,
+            _native.stream_handle(device)))
     return y, t
 
 
 def linear_backward(desc: _native.NF4Desc, x2: Optional[torch.Tensor], dy2: torch.Tensor, lora_a: torch.Tensor,
                     lora_b: torch.Tensor, scaling: float, t: Optional[torch.Tensor], need_dx: bool,
                     need_adapter_grads: bool, grad_a_out: Optional[torch.Tensor] = None,
-                    grad_b_out: Optional[torch.Tensor] = None, path: int = _native.PATH_AUTO):
+                    grad_b_out: Optional[torch.Tensor] = None, path: int = _native.PATH_AUTO,
+                    shadow: Optional[LoraShadows] = None):
     """dX, dA, dB of the linear.  When ``grad_a_out``/``grad_b_out`` are given the adapter gradients are
     accumulated into them in place (fp32) and returned as None."""
     n, k, m, rank = int(desc.n), int(desc.k), int(dy2.shape[0]), int(lora_a.shape[0])
@@ -127,10 +186,10 @@ def linear_backward(desc: _native.NF4Desc, x2: Optional[torch.Tensor], dy2: torc
     nbytes = lib.molt_workspace_bytes(_native.OP_LORA_BWD, m, n, k, rank)
     ws = _native.workspace(nbytes, device)
     with torch.cuda.device(device):
-        _native.check(lib.molt_nf4_lora_bwd(
+        _native.check(lib.molt_nf4_lora_bwd_prepared(
             ctypes.byref(desc), _native.ptr(x2), dy2.data_ptr(), lora_a.data_ptr(), lora_b.data_ptr(),
-            float(scaling), rank, _native.ptr(dx), _native.ptr(da), _native.ptr(db), m, _native.ptr(t), accumulate,
-            ws.data_ptr(), ws.numel(), path, _native.stream_handle(device)))
+            float(scaling), rank, _shadow_struct(shadow), _native.ptr(dx), _native.ptr(da), _native.ptr(db), m,
+            _native.ptr(t), accumulate, ws.data_ptr(), ws.numel(), path, _native.stream_handle(device)))
     if accumulate:
         return dx, None, None
     return dx, da, db
@@ -154,7 +213,8 @@ class NF4LoRAFunction(torch.autograd.Function):
         if desc is None:
             desc = weight_desc_for_tokens(packed_weight, quant_state, int(x2.shape[0]))
         needs_backward = any(ctx.needs_input_grad[i] for i in (0, 2, 3))
-        y, t = linear_forward(desc, x2, lora_a, lora_b, float(scaling), keep_low_rank=needs_backward)
+        ctx.shadow = getattr(lora_a, SHADOW_SLOT, None)
+        y, t = linear_forward(desc, x2, lora_a, lora_b, float(scaling), keep_low_rank=needs_backward, shadow=ctx.shadow)
         ctx.desc = desc
         ctx.quant_state = quant_state
         ctx.scaling = float(scaling)
@@ -176,7 +236,7 @@ class NF4LoRAFunction(torch.autograd.Function):
         need_grads = ctx.needs_input_grad[2] or ctx.needs_input_grad[3]
         slot_a, slot_b = ctx.slots
         dx, da, db = linear_backward(ctx.desc, x2, dy2, lora_a, lora_b, ctx.scaling, t if t.numel() else None,
-                                     need_dx, need_grads, slot_a, slot_b)
+                                     need_dx, need_grads, slot_a, slot_b, shadow=ctx.shadow)
         if dx is not None:
             dx = dx.reshape(ctx.input_shape)
         return dx, None, da, db, None, None, None, None

@@ -21,7 +21,7 @@ import torch
 from molt_b200 import _native
 from molt_b200.core.errors import CapabilityError
 from molt_b200.kernels.gated_activation import swiglu_backward, swiglu_forward
-from molt_b200.methods._linear import (GRAD_SLOT, check_linear_inputs, linear_backward, linear_forward,
+from molt_b200.methods._linear import (GRAD_SLOT, SHADOW_SLOT, check_linear_inputs, linear_backward, linear_forward,
                                        weight_desc_for_tokens)
 from molt_b200.methods.nf4_lora import _adapter_of, _bf16_autocast_active, is_lora_4bit_linear
 
@@ -147,13 +147,15 @@ def asymmetric_gated_nf4_lora(
 # Whole block as one node.
 # --------------------------------------------------------------------------------------------------------
 
-def _proj_struct(desc, lora_a, lora_b, scaling) -> _native.LoraProj:
+def _proj_struct(desc, lora_a, lora_b, scaling, shadow=None) -> _native.LoraProj:
     proj = _native.LoraProj()
     proj.w = ctypes.pointer(desc)
     proj.lora_a = lora_a.data_ptr()
     proj.lora_b = lora_b.data_ptr()
     proj.scaling = float(scaling)
     proj.rank = int(lora_a.shape[0])
+    if shadow is not None:   # the adapter's bf16 operands are kept up to date by its owner
+        proj.shadow = ctypes.pointer(shadow.struct)
     return proj
 
 
@@ -197,7 +199,8 @@ class _GatedMLPNF4LoRA(torch.autograd.Function):
             raise ValueError("input width must match the gate/up projection in_features")
         adapters = [t.contiguous() for t in (gate_a, gate_b, up_a, up_b, down_a, down_b)]
         scalings = (float(gate_scaling), float(up_scaling), float(down_scaling))
-        projs = [_proj_struct(descs[i], adapters[2 * i], adapters[2 * i + 1], scalings[i]) for i in range(3)]
+        ctx.shadows = tuple(getattr(t, SHADOW_SLOT, None) for t in (gate_a, up_a, down_a))
+        projs = [_proj_struct(descs[i], adapters[2 * i], adapters[2 * i + 1], scalings[i], ctx.shadows[i]) for i in range(3)]
         lib = _native.library()
         device = x2.device
         gate_out = torch.empty((m, inter), dtype=torch.bfloat16, device=device)
@@ -246,7 +249,8 @@ class _GatedMLPNF4LoRA(torch.autograd.Function):
             dy2 = dy2.to(torch.bfloat16)
         m = x2.shape[0]
         device = x2.device
-        projs = [_proj_struct(ctx.descs[i], adapters[2 * i], adapters[2 * i + 1], ctx.scalings[i]) for i in range(3)]
+        projs = [_proj_struct(ctx.descs[i], adapters[2 * i], adapters[2 * i + 1], ctx.scalings[i], ctx.shadows[i])
+                 for i in range(3)]
         lib = _native.library()
         dx = torch.empty_like(x2)
         use_slots = all(slot is not None for slot in ctx.slots)

@@ -22,6 +22,7 @@ from torch.nn import functional as F
 
 from molt_b200 import _native
 from molt_b200.data_parallel import GradArena, ParamArena, StepGuard, lora_parameters
+from molt_b200.methods._linear import LoraShadows, ShadowTable
 from molt_b200.methods.quant_state import NestedState, QuantState
 from molt_b200.modules import GatedMLP, NF4LoRALinear
 from molt_b200.streaming.nf4 import NF4_CODEBOOK
@@ -366,6 +367,20 @@ class SyntheticDecoder(nn.Module):
         return _FrozenHeadLoss.apply(hidden, self.head, targets.reshape(-1), self.head_chunk, float(global_tokens))
 
 
+def attach_lora_shadows(model: nn.Module) -> list:
+    """Give every active adapter of ``model``'s NF4-LoRA linears its bf16 operand buffers and make the fused ops use them;
+    returns the list (for a :class:`ShadowTable`).  The caller refreshes them whenever the masters change."""
+    made = []
+    for module in model.modules():
+        if isinstance(module, NF4LoRALinear):
+            for adapter in module.active_adapters:
+                shadow = LoraShadows(module.lora_A[adapter].weight, module.lora_B[adapter].weight,
+                                     float(module.scaling[adapter]))
+                shadow.attach()
+                made.append(shadow)
+    return made
+
+
 class QLoRAStep:
     """Holds model, gradient arena and optimiser; ``run(tokens, targets)`` is one data-parallel training step.
 
@@ -377,7 +392,8 @@ class QLoRAStep:
     non-zero value raises; with a :class:`StepGuard` the ranks also check each other on the host before each step."""
 
     def __init__(self, shape: DecoderShape, device, layers: Optional[int] = None, lr: float = 1e-4,
-                 cuda_graph: bool = False, status_interval: int = 50, guard: Optional[StepGuard] = None):
+                 cuda_graph: bool = False, status_interval: int = 50, guard: Optional[StepGuard] = None,
+                 lora_shadows: bool = True):
         self.shape = shape
         self.device = device
         self.world = dist.get_world_size() if dist.is_initialized() else 1
@@ -389,6 +405,11 @@ class QLoRAStep:
         self.arena = GradArena(params, bucket_starts=starts)
         self.layer_bucket = [self.arena.bucket_of_param(start) for start in starts]
         self.optimizer = ParamArena(self.arena, lr=lr, weight_decay=0.0)
+        # bf16 operands of every adapter, rebuilt by one launch behind each optimizer step (made after the parameter
+        # arena: they record the masters' final addresses), so that no linear call converts its adapter first
+        self.shadows = ShadowTable(attach_lora_shadows(self.model)) if lora_shadows else None
+        if self.shadows is not None:
+            self.shadows.refresh()
         self.cuda_graph = cuda_graph
         self.status_interval = int(status_interval)
         self.guard = guard
@@ -438,6 +459,8 @@ class QLoRAStep:
             loss = self._forward_backward(tokens, targets)
             self._eager_steps += 1
         self.optimizer.step(grad_scale=1.0)  # the loss is already normalised by the global token count
+        if self.shadows is not None:
+            self.shadows.refresh()           # same stream, behind the step: the next forward sees the new adapters
         self.steps += 1
         if self.status_interval > 0 and self.steps % self.status_interval == 0:
             self.check_status()

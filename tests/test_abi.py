@@ -18,7 +18,8 @@ def declared_functions():
 
 def test_header_declares_the_expected_entry_points():
     names = declared_functions()
-    for required in ("molt_nf4_dequant", "molt_nf4_lora_fwd", "molt_nf4_lora_bwd", "molt_nf4_dx", "molt_nf4_gemv",
+    for required in ("molt_nf4_dequant", "molt_nf4_lora_fwd", "molt_nf4_lora_bwd", "molt_nf4_lora_fwd_prepared",
+                     "molt_nf4_lora_bwd_prepared", "molt_lora_shadow_refresh", "molt_nf4_dx", "molt_nf4_gemv",
                      "molt_swiglu_fwd", "molt_swiglu_bwd", "molt_mlp_fwd", "molt_mlp_bwd", "molt_workspace_bytes",
                      "molt_last_error", "molt_version"):
         assert required in names
@@ -41,7 +42,10 @@ def test_struct_layout_matches_header(native_library):
     # 4 pointers, 1 float, 5 int32, 2 int64, 16 floats
     assert ctypes.sizeof(_native.NF4Desc) == 4 * 8 + 4 + 5 * 4 + 2 * 8 + 16 * 4
     assert _native.NF4Desc.n.offset == 56 and _native.NF4Desc.codebook.offset == 72
-    assert ctypes.sizeof(_native.LoraProj) == 32
+    assert ctypes.sizeof(_native.LoraProj) == 40 and _native.LoraProj.shadow.offset == 32
+    assert ctypes.sizeof(_native.LoraShadow) == 24
+    # 2 pointers, float, int32, 2 int64, 3 pointers
+    assert ctypes.sizeof(_native.LoraShadowItem) == 2 * 8 + 4 + 4 + 2 * 8 + 3 * 8 and _native.LoraShadowItem.a16.offset == 40
 
 
 def test_version_and_workspace_queries_run_without_a_gpu(native_library):

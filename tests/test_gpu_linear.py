@@ -299,3 +299,54 @@ def test_few_token_path(native_library, m, n, k, rank, nested, order, exact):
     # deterministic: a second call gives the same bits
     y3, _ = run_forward(case, path, keep_t=False)
     assert torch.equal(y3, y)
+
+
+@pytest.mark.parametrize("n,k,m,rank,nested", [(1536, 1024, 300, 16, False), (320, 192, 40, 7, True),
+                                               (2560, 1024, 2048, 64, False), (1536, 8960, 5, 16, False)])
+def test_lora_shadows_give_the_same_bits_as_the_per_call_conversion(native_library, n, k, m, rank, nested):
+    """The bf16 adapter operands kept by the optimizer's side (reference methods/lora_shadow.py:19-141) stand in for the
+    conversion in front of each call: same kernels, same operands, so the results are identical, on every path."""
+    from molt_b200.methods._linear import LoraShadows, ShadowTable, linear_backward, linear_forward, weight_desc_for_tokens
+
+    case = make_case(n, k, m, rank, nested=nested, seed=77)
+    desc = weight_desc_for_tokens(case.packed, case.state, m)
+    a, b = case.a.cuda(), case.b.cuda()
+    x, dy = case.x.cuda().bfloat16(), case.dy.cuda().bfloat16()
+    other = LoraShadows(torch.randn(5, 64, device="cuda"), torch.randn(128, 5, device="cuda"), 0.5)
+    shadow = LoraShadows(a, b, case.scaling)
+    ShadowTable([other, shadow]).refresh()       # two adapters of different shapes in one launch
+    rp = (rank + 15) // 16 * 16
+    assert torch.equal(shadow.a16[:rank], a.bfloat16()) and not shadow.a16[rank:].any()
+    assert torch.equal(shadow.bs[:, :rank], (case.scaling * b).bfloat16()) and not shadow.bs[:, rank:].any()
+    assert torch.equal(shadow.bt[:rank], (case.scaling * b).bfloat16().t()) and shadow.bt.shape == (rp, n)
+    assert torch.equal(other.a16[:5], other.lora_a.bfloat16())
+    for path in (_native.PATH_AUTO, _native.PATH_TCGEN05):
+        y0, t0 = linear_forward(desc, x, a, b, case.scaling, True, path)
+        y1, t1 = linear_forward(desc, x, a, b, case.scaling, True, path, shadow=shadow)
+        assert torch.equal(y0, y1) and torch.equal(t0, t1)
+        g0 = linear_backward(desc, x, dy, a, b, case.scaling, t0, True, True, path=path)
+        g1 = linear_backward(desc, x, dy, a, b, case.scaling, t1, True, True, path=path, shadow=shadow)
+        assert all(torch.equal(u, v) for u, v in zip(g0, g1))
+    assert_clean_status()
+    y_ref = oracle_results(case)[0]
+    assert oracle.rel_frobenius(y1, y_ref) <= TOL
+    if not nested:   # one launch fewer per call on the tensor-core path: the operand preparation is gone
+        count = native_library.molt_launch_count
+        c0 = count()
+        linear_forward(desc, x, a, b, case.scaling, True, _native.PATH_TCGEN05)
+        c1 = count()
+        linear_forward(desc, x, a, b, case.scaling, True, _native.PATH_TCGEN05, shadow=shadow)
+        c2 = count()
+        linear_backward(desc, x, dy, a, b, case.scaling, t0, True, True, path=_native.PATH_TCGEN05)
+        c3 = count()
+        linear_backward(desc, x, dy, a, b, case.scaling, t0, True, True, path=_native.PATH_TCGEN05, shadow=shadow)
+        c4 = count()
+        assert (c2 - c1, c4 - c3) == (c1 - c0 - 1, c3 - c2 - 1)
+    # stale shadows are what the kernels use: the owner has to refresh after changing the masters
+    a.mul_(2.0)
+    y_stale, _ = linear_forward(desc, x, a, b, case.scaling, False, _native.PATH_TCGEN05, shadow=shadow)
+    assert torch.equal(y_stale, y1)
+    ShadowTable([shadow]).refresh()
+    y_new, _ = linear_forward(desc, x, a, b, case.scaling, False, _native.PATH_TCGEN05, shadow=shadow)
+    y_plain, _ = linear_forward(desc, x, a, b, case.scaling, False, _native.PATH_TCGEN05)
+    assert torch.equal(y_new, y_plain) and not torch.equal(y_new, y1)

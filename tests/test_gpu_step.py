@@ -294,3 +294,29 @@ def test_rope_kernel_matches_torch(native_library):
     torch.autograd.backward([q, k], [gq, gk])
     torch.autograd.backward([q_ref, k_ref], [gq.float(), gk.float()])
     assert (ql.grad.float() - qr.grad).abs().max() <= 3e-2 and (kl.grad.float() - kr.grad).abs().max() <= 3e-2
+
+
+def test_step_with_lora_shadows_equals_step_without(native_library):
+    """The adapters' bf16 operands refreshed behind each optimizer step, against converting them in front of every
+    call: the same kernels see the same operands, so losses and adapters agree bit for bit over several steps."""
+    from molt_b200 import _native
+    from molt_b200.qlora_step import DecoderShape, QLoRAStep
+
+    shape = DecoderShape(layers=2, hidden=128, heads=4, kv_heads=2, head_dim=32, intermediate=256, vocab=512,
+                         rope_theta=1e4, rank=8, alpha=16.0, nested_absmax=False, seq_len=64, micro_batch=4)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    tokens = torch.randint(0, shape.vocab, (shape.micro_batch, shape.seq_len), device="cuda", generator=gen)
+    targets = torch.roll(tokens, -1, dims=1)
+    runs = []
+    for shadows in (True, False):
+        step = QLoRAStep(shape, torch.device("cuda"), lr=5e-3, lora_shadows=shadows)
+        assert (step.shadows is not None) == shadows
+        if shadows:
+            assert len(step.shadows.shadows) == 2 * 7
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            losses = [step.run(tokens, targets).clone() for _ in range(4)]
+        runs.append((torch.stack(losses), step.optimizer.flat.clone()))
+    assert torch.equal(runs[0][0], runs[1][0])
+    assert torch.equal(runs[0][1], runs[1][1])
+    assert float(runs[0][0][-1]) < float(runs[0][0][0])
+    assert _native.read_status() == 0
