@@ -320,3 +320,84 @@ def test_step_with_lora_shadows_equals_step_without(native_library):
     assert torch.equal(runs[0][1], runs[1][1])
     assert float(runs[0][0][-1]) < float(runs[0][0][0])
     assert _native.read_status() == 0
+
+
+@pytest.mark.parametrize("joint", [False, True])
+def test_static_cuda_microbatch_replays_the_fused_ops(native_library, joint):
+    """The reference's captured micro-batch runner (training/static_cuda_graph.py:139-308) around a small stack of
+    NF4-LoRA linears: replays give the eager loss and gradients, gradients accumulate until zero_grad, inputs of
+    another signature are refused."""
+    from molt_b200.core.errors import CapabilityError
+    from molt_b200.methods import quantize_nf4
+    from molt_b200.modules import NF4LoRALinear
+    from molt_b200.training import StaticCudaMicrobatch
+
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    layers = []
+    for n, k in ((256, 128), (128, 256)):
+        packed, state = quantize_nf4(torch.randn(n, k, device="cuda", generator=gen) * 0.05, 64, True)
+        lin = NF4LoRALinear(packed, state, 8, 16.0)
+        with torch.no_grad():
+            lin.lora_B["default"].weight.normal_(0.0, 0.02, generator=gen)
+        layers.append(lin)
+    params = [p for lin in layers for p in lin.parameters() if p.requires_grad]
+    assert len(params) == 4
+
+    def loss_of(x, target):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            h = layers[1](torch.nn.functional.silu(layers[0](x)))
+        return ((h.float() - target) ** 2).mean()
+
+    x = torch.randn(96, 128, device="cuda", generator=gen).bfloat16()
+    target = torch.randn(96, 128, device="cuda", generator=gen)
+    x2 = torch.randn(96, 128, device="cuda", generator=gen).bfloat16()
+    eager = []
+    for inputs in ((x, target), (x2, target)):
+        for p in params:
+            p.grad = None
+        loss = loss_of(*inputs)
+        loss.backward()
+        eager.append((loss.detach().clone(), [p.grad.clone() for p in params]))
+    runner = StaticCudaMicrobatch(loss_of, (x, target), params, warmup_steps=2, joint_forward_backward=joint)
+    assert [s.shape for s in runner.signatures] == [(96, 128), (96, 128)]
+    assert all(float(p.grad.abs().sum()) == 0.0 for p in params)
+    for (loss_ref, grads_ref), inputs in zip(eager, ((x, target), (x2, target))):
+        runner.zero_grad()
+        loss = runner.replay(*inputs)
+        torch.cuda.synchronize()
+        assert torch.equal(loss, loss_ref)
+        assert all(torch.equal(p.grad, g) for p, g in zip(params, grads_ref))
+    runner.replay(x2, target)                      # a second replay accumulates, like a second eager backward
+    torch.cuda.synchronize()
+    assert all(torch.allclose(p.grad, 2 * g, rtol=1e-6, atol=0) for p, g in zip(params, eager[1][1]))
+    with pytest.raises(ValueError):
+        runner.replay(x[:10], target)
+    with pytest.raises(ValueError):
+        runner.replay(x)
+    with pytest.raises(RuntimeError):
+        (runner.replay_forward if joint else runner.replay_staged)(*(() if not joint else (x, target)))
+    runner.close()
+    with pytest.raises(ValueError):
+        StaticCudaMicrobatch(loss_of, (x, target), params, warmup_steps=0)
+    with pytest.raises(CapabilityError):
+        StaticCudaMicrobatch(loss_of, (x.cpu(), target), params)
+    from molt_b200 import _native
+    assert _native.read_status() == 0
+
+
+def test_bnb_format_checkpoint_feeds_the_kernels(native_library, tmp_path):
+    """A double-quantised NF4 weight written in the bitsandbytes state-dict layout, read back from a .safetensors file
+    and handed to the fused linear, gives what the original quant state gives."""
+    from molt_b200.methods import quantize_nf4, scheduled_nf4_lora
+    from molt_b200.training import bnb_nf4_weight, export_bnb_nf4_weight, read_safetensors, write_safetensors
+
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    packed, state = quantize_nf4(torch.randn(320, 192, device="cuda", generator=gen) * 0.03, 64, True)
+    name = "model.layers.3.mlp.up_proj.weight"
+    write_safetensors(tmp_path / "m.safetensors", export_bnb_nf4_weight(name, packed, state))
+    packed2, state2 = bnb_nf4_weight(read_safetensors(tmp_path / "m.safetensors"), name, device="cuda")
+    a = torch.randn(8, 192, device="cuda", generator=gen) * 0.01
+    b = torch.randn(320, 8, device="cuda", generator=gen) * 0.01
+    for m in (4, 40, 300):
+        x = torch.randn(m, 192, device="cuda", generator=gen).bfloat16()
+        assert torch.equal(scheduled_nf4_lora(x, packed2, a, b, state2, 2.0), scheduled_nf4_lora(x, packed, a, b, state, 2.0))
