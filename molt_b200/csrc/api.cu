@@ -192,7 +192,8 @@ static int pick_path(int requested, const molt_nf4_desc* w, int rank, int64_t m,
   return MOLT_OK;
 }
 
-// fp32 absmax for the tcgen05 kernels: the descriptor's own array, or the nested form resolved into the arena.
+// fp32 absmax for the tcgen05 GEMM: the descriptor's own array; NULL for a double-quantised absmax whose second-level
+// block size is a power of two (the kernel reads that form itself); any other nested form resolved into the arena.
 // With `deferred` the resolve is not launched here: *deferred gets the buffer and the caller folds the work into its
 // next preparation kernel.
 static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s, const float** out,
@@ -200,6 +201,10 @@ static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s,
   if (deferred != nullptr) *deferred = nullptr;
   if (w->absmax_kind == MOLT_ABSMAX_F32) {
     *out = reinterpret_cast<const float*>(w->absmax);
+    return MOLT_OK;
+  }
+  if (make_view(w).block2_shift >= 0) {   // the GEMM's decoders read this double-quantised form themselves
+    *out = nullptr;
     return MOLT_OK;
   }
   const int64_t blocks = (w->n * w->k + w->blocksize - 1) / w->blocksize;

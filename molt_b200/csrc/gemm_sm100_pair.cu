@@ -105,7 +105,12 @@ constexpr uint32_t smem_bytes(int load_stages, int b_stages, int store_bufs, boo
 
 struct Params {
   const uint8_t* packed; // [n, k / 2] packed codes
-  const float* absmax;   // fp32 [n * k / 64]
+  const float* absmax;   // fp32 [n * k / 64], or NULL when the decoders read the double-quantised form themselves:
+  const uint8_t* absmax_u8;   //   8-bit codes [n * k / 64]
+  const float* absmax2;       //   fp32 absmax of every 2^block2_shift of them
+  const float* code2;         //   256-entry table
+  float offset;
+  int block2_shift;
   int32_t* status;
   long long m, n, k;
   int num_kb;
@@ -561,32 +566,68 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
       pair_tile_coords<kSub>(item.tile, p.tiles_m, p.tiles_n, tm, tn);
       const int col0 = tn * BN + (int)rank * BNH;   // first B row (forward: weight row; backward: weight column)
       // forward : absmax[(col0 + i) * kpr + kb]            backward: absmax[(kb * 64 + j) * kpr + col0 / 64 + a]
-      const float* scale_ptr;
-      long long scale_step;
+      long long scale_at, scale_step;   // index of the segment's absmax in block 0, and its step per block
       bool scale_ok;
       if (!BACKWARD) {
         const long long row = (long long)col0 + u;
         scale_ok = row < p.n;
-        scale_ptr = p.absmax + (scale_ok ? row : 0) * kblocks_per_row;
+        scale_at = (scale_ok ? row : 0) * kblocks_per_row;
         scale_step = 1;
       } else {
         const long long colblk = (long long)(col0 >> 6) + seg_a;
         scale_ok = colblk < kblocks_per_row;
-        scale_ptr = p.absmax + (long long)seg_j * kblocks_per_row + (scale_ok ? colblk : 0);
+        scale_at = (long long)seg_j * kblocks_per_row + (scale_ok ? colblk : 0);
         scale_step = (long long)BK * kblocks_per_row;
       }
+      // fp32 absmax: one load.  Double-quantised absmax: code2[u8] * absmax2 + offset with a separate multiply and
+      // add (the dequantiser's bits); the 8-bit code and the second-level absmax are fetched one round of the
+      // prefetch earlier than the table entry, so that no load waits for another.
+      const bool nested = p.absmax == nullptr;
+      auto load_raw = [&](int kb, uint32_t& code, float& second) {
+        code = 0u;
+        second = 0.f;
+        if (kb < p.num_kb && scale_ok) {
+          const long long at = scale_at + (long long)kb * scale_step;
+          code = __ldg(p.absmax_u8 + at);
+          second = __ldg(p.absmax2 + (at >> p.block2_shift));
+        }
+      };
+      auto resolve = [&](int kb, uint32_t code, float second) -> float {
+        return (kb < p.num_kb && scale_ok) ? __fadd_rn(__fmul_rn(__ldg(p.code2 + code), second), p.offset) : 0.f;
+      };
       auto load_scale = [&](int kb) -> float {
-        return (kb < p.num_kb && scale_ok) ? __ldg(scale_ptr + (long long)kb * scale_step) : 0.f;
+        if (nested) {
+          uint32_t code;
+          float second;
+          load_raw(kb, code, second);
+          return resolve(kb, code, second);
+        }
+        return (kb < p.num_kb && scale_ok) ? __ldg(p.absmax + scale_at + (long long)kb * scale_step) : 0.f;
       };
       // the group's first block of this item: running block number g_tile + (kb - kb0) is congruent to grp
       const int kb_first = item.kb0 + ((grp - g_tile) % kDecodeGroups + kDecodeGroups) % kDecodeGroups;
       float cur[kPrefetch];
+      uint32_t raw_code[kPrefetch];     // nested only: the round after `cur`
+      float raw_second[kPrefetch];
 #pragma unroll
-      for (int q = 0; q < kPrefetch; ++q) cur[q] = load_scale(kb_first + kDecodeGroups * q);
+      for (int q = 0; q < kPrefetch; ++q) {
+        cur[q] = load_scale(kb_first + kDecodeGroups * q);
+        raw_code[q] = 0u;
+        raw_second[q] = 0.f;
+        if (nested) load_raw(kb_first + kDecodeGroups * (kPrefetch + q), raw_code[q], raw_second[q]);
+      }
       for (int kb0 = kb_first; kb0 < item.kb1 && ok; kb0 += kDecodeGroups * kPrefetch) {
         float nxt[kPrefetch];
 #pragma unroll
-        for (int q = 0; q < kPrefetch; ++q) nxt[q] = load_scale(kb0 + kDecodeGroups * (kPrefetch + q));
+        for (int q = 0; q < kPrefetch; ++q) {
+          const int kb_next = kb0 + kDecodeGroups * (kPrefetch + q);
+          if (nested) {
+            nxt[q] = resolve(kb_next, raw_code[q], raw_second[q]);
+            load_raw(kb_next + kDecodeGroups * kPrefetch, raw_code[q], raw_second[q]);
+          } else {
+            nxt[q] = load_scale(kb_next);
+          }
+        }
 #pragma unroll
         for (int q = 0; q < kPrefetch; ++q) {
           const int kb = kb0 + kDecodeGroups * q;
@@ -902,6 +943,20 @@ int sm100_gemm(bool backward, const WeightView& w, const float* absmax_f32, cons
   Params p;
   p.packed = w.packed;
   p.absmax = absmax_f32;
+  p.absmax_u8 = nullptr;
+  p.absmax2 = nullptr;
+  p.code2 = nullptr;
+  p.offset = 0.f;
+  p.block2_shift = 0;
+  if (absmax_f32 == nullptr) {   // the decoders read the double-quantised absmax themselves
+    if (w.absmax_kind != MOLT_ABSMAX_NESTED || w.block2_shift < 0)
+      return fail(MOLT_E_RUNTIME, "tcgen05 GEMM: no fp32 absmax given and the weight's own cannot be read in the kernel");
+    p.absmax_u8 = reinterpret_cast<const uint8_t*>(w.absmax);
+    p.absmax2 = w.absmax2;
+    p.code2 = w.code2;
+    p.offset = w.offset;
+    p.block2_shift = w.block2_shift;
+  }
   p.m = m;
   p.n = w.n;
   p.k = w.k;
@@ -936,6 +991,11 @@ int sm100_dense_gemm(bool backward, const __nv_bfloat16* weight, long long n, lo
   Params p;
   p.packed = nullptr;
   p.absmax = nullptr;
+  p.absmax_u8 = nullptr;
+  p.absmax2 = nullptr;
+  p.code2 = nullptr;
+  p.offset = 0.f;
+  p.block2_shift = 0;
   p.m = m;
   p.n = n;
   p.k = k;

@@ -350,3 +350,30 @@ def test_lora_shadows_give_the_same_bits_as_the_per_call_conversion(native_libra
     y_new, _ = linear_forward(desc, x, a, b, case.scaling, False, _native.PATH_TCGEN05, shadow=shadow)
     y_plain, _ = linear_forward(desc, x, a, b, case.scaling, False, _native.PATH_TCGEN05)
     assert torch.equal(y_new, y_plain) and not torch.equal(y_new, y1)
+
+
+@pytest.mark.parametrize("n,k,m,rank", [(1536, 1024, 300, 16), (2560, 1024, 2048, 8), (256, 4096, 700, 64)])
+def test_gemm_reads_a_double_quantised_absmax_itself(native_library, n, k, m, rank):
+    """The tensor-core GEMM's decoders resolve code2[u8] * absmax2 + offset on the fly (no fp32 copy of the absmax is
+    made first): same bits as the resolved array, so forward and backward equal the calls on the resolved descriptor."""
+    from molt_b200.methods._linear import linear_backward, linear_forward, weight_desc
+    from molt_b200.methods.quant_state import QuantState
+
+    case = make_case(n, k, m, rank, nested=True, order="high-first", seed=99)
+    nested_desc = weight_desc(case.packed, case.state)
+    plain = QuantState(absmax=case.scales_f32.cuda(), shape=(n, k), nibble_order="high-first")
+    plain_desc = weight_desc(case.packed, plain)
+    a, b = case.a.cuda(), case.b.cuda()
+    x, dy = case.x.cuda().bfloat16(), case.dy.cuda().bfloat16()
+    count = native_library.molt_launch_count
+    results = []
+    for desc in (nested_desc, plain_desc):
+        c0 = count()
+        y, t = linear_forward(desc, x, a, b, case.scaling, True, _native.PATH_TCGEN05)
+        grads = linear_backward(desc, x, dy, a, b, case.scaling, t, True, True, path=_native.PATH_TCGEN05)
+        results.append((y, *grads, count() - c0))
+    assert all(torch.equal(u, v) for u, v in zip(results[0][:4], results[1][:4]))
+    assert results[0][4] == results[1][4]          # and no extra launch for the nested form
+    assert_clean_status()
+    y_ref, dx_ref, _, _ = oracle_results(case)
+    assert oracle.rel_frobenius(results[0][0], y_ref) <= TOL and oracle.rel_frobenius(results[0][1], dx_ref) <= TOL

@@ -351,13 +351,16 @@ def test_static_cuda_microbatch_replays_the_fused_ops(native_library, joint):
     x = torch.randn(96, 128, device="cuda", generator=gen).bfloat16()
     target = torch.randn(96, 128, device="cuda", generator=gen)
     x2 = torch.randn(96, 128, device="cuda", generator=gen).bfloat16()
-    eager = []
-    for inputs in ((x, target), (x2, target)):
-        for p in params:
+    def eager_pass(*inputs):   # nothing of its autograd graph outlives the call (a live graph would pin the
+        for p in params:       # gradient-accumulation nodes to this stream and break the capture below)
             p.grad = None
         loss = loss_of(*inputs)
         loss.backward()
-        eager.append((loss.detach().clone(), [p.grad.clone() for p in params]))
+        return loss.detach().clone(), [p.grad.clone() for p in params]
+
+    eager = [eager_pass(x, target), eager_pass(x2, target)]
+    for p in params:
+        p.grad = None
     runner = StaticCudaMicrobatch(loss_of, (x, target), params, warmup_steps=2, joint_forward_backward=joint)
     assert [s.shape for s in runner.signatures] == [(96, 128), (96, 128)]
     assert all(float(p.grad.abs().sum()) == 0.0 for p in params)
