@@ -377,3 +377,34 @@ def test_gemm_reads_a_double_quantised_absmax_itself(native_library, n, k, m, ra
     assert_clean_status()
     y_ref, dx_ref, _, _ = oracle_results(case)
     assert oracle.rel_frobenius(results[0][0], y_ref) <= TOL and oracle.rel_frobenius(results[0][1], dx_ref) <= TOL
+
+
+def _fuzz_cases(count, seed):
+    gen = torch.Generator().manual_seed(seed)
+
+    def pick(values):
+        return values[int(torch.randint(0, len(values), (1,), generator=gen))]
+
+    cases = []
+    for index in range(count):
+        n = 64 * pick([1, 2, 3, 5, 8, 13, 24, 40])
+        k = 64 * pick([1, 2, 3, 4, 7, 16, 24, 36])
+        m = pick([1, 2, 7, 8, 9, 16, 31, 64, 100, 128, 129, 255, 257, 511, 640, 1100])
+        rank = pick([1, 4, 8, 16, 17, 32, 48, 64])
+        cases.append((n, k, m, rank, bool(pick([0, 1])), pick(["low-first", "high-first"]), pick([0.25, 1.0, 2.0]), 5000 + index))
+    return cases
+
+
+@pytest.mark.parametrize("n,k,m,rank,nested,order,scaling,seed", _fuzz_cases(36, 20261125))
+def test_seeded_random_shapes_on_the_auto_path(native_library, n, k, m, rank, nested, order, scaling, seed):
+    """Randomly drawn (seeded) aligned shapes, token counts on both sides of every path boundary, ranks with tails, both
+    nibble orders and both absmax forms, on whatever path AUTO takes: Y, dX, dA, dB against the oracle."""
+    case = make_case(n, k, m, rank, seed=seed, scaling=scaling, nested=nested, order=order)
+    y_ref, dx_ref, da_ref, db_ref = oracle_results(case)
+    y, t = run_forward(case, _native.PATH_AUTO, keep_t=True)
+    dx, da, db = run_backward(case, _native.PATH_AUTO, t)
+    torch.cuda.synchronize()
+    assert_clean_status()
+    errors = {"y": oracle.rel_frobenius(y, y_ref), "dx": oracle.rel_frobenius(dx, dx_ref),
+              "da": oracle.rel_frobenius(da, da_ref), "db": oracle.rel_frobenius(db, db_ref)}
+    assert all(v <= TOL for v in errors.values()), errors
