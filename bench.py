@@ -746,10 +746,14 @@ def extras(lib, device, desc, packed, state, lora_a, lora_b, peaks):
         xin = x.detach().requires_grad_()
         mlp.fused(xin, rematerialize_up=True).backward(dy)
 
-    ms = event_time_ms(block_step, iters=5, warmup=2)
+    eager_ms = event_time_ms(block_step, iters=5, warmup=2)   # through Python autograd: includes host launch gaps
+    # the same step replayed as a CUDA graph, as the step driver (and the reference's trainer) runs it: device time
+    ms = graph_time_ms([block_step], replays=10)
     flops = 3 * linear_flops(rows, inter, hidden)
     out["mlp_block_config3"] = {"ms": ms, "tflops_algorithmic": flops / ms / 1e9,
-                                "frac_bf16_peak": flops / ms / 1e9 / peaks["bf16_tflops"], "replay_up": True}
+                                "frac_bf16_peak": flops / ms / 1e9 / peaks["bf16_tflops"], "replay_up": True,
+                                "timing": "one forward+backward of the block captured as a CUDA graph, replayed 10 times",
+                                "ms_eager_autograd": eager_ms}
     return out
 
 

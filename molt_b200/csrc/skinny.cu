@@ -104,12 +104,12 @@ __global__ void __launch_bounds__(256) lora_shadow_refresh_kernel(const molt_lor
 // ------------------------------------------------------------------------------------------------
 // warps per CTA of 16 rows: they split the contraction; 16 where the partial sums still fit in 48 KB of shared memory
 constexpr int rowsum_warps(int rp) { return rp <= 32 ? 16 : 8; }   // 32 warps measured slower than 16
-template <int RP>
-__global__ void __launch_bounds__(rowsum_warps(RP) * 32) rowsum_mma_kernel(const __nv_bfloat16* __restrict__ in,
+template <int RP, int kRowsumWarps, int kUnroll>
+__global__ void __launch_bounds__(kRowsumWarps * 32) rowsum_mma_kernel(const __nv_bfloat16* __restrict__ in,
                                                          const __nv_bfloat16* __restrict__ wt, long long m_total,
                                                          long long cols, __nv_bfloat16* __restrict__ out) {
   constexpr int NT = RP / 8;
-  constexpr int kRowsumWarps = rowsum_warps(RP);
+  static_assert(kRowsumWarps <= rowsum_warps(RP), "the partial sums of all warps must fit in 48 KB");
   // the GEMM that follows in the stream may begin its set-up (it waits for this grid before it touches global memory)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ float partial[kRowsumWarps][16][RP + 1];
@@ -125,22 +125,26 @@ __global__ void __launch_bounds__(rowsum_warps(RP) * 32) rowsum_mma_kernel(const
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
   const long long chunks = cols / 32;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  // Two chunks per trip: the four activation loads (the HBM stream) are requested before anything is used.  Default
-  // caching on purpose: a 128-byte line is shared by two neighbouring warps (64 bytes each).
-  constexpr int kUnroll = 2;
-  for (long long c0 = warp; c0 < chunks; c0 += kRowsumWarps * kUnroll) {
+  // kUnroll NEIGHBOURING chunks per trip, so that a warp asks for whole 128-byte lines of its rows (64 bytes per
+  // chunk); the activation loads of a trip (the HBM stream) are requested before anything is used.
+#ifdef MOLT_ROWSUM_FAR_CHUNKS   // the previous assignment: chunks c and c + W to a warp (a line is shared by two warps)
+  constexpr int kFirst = 1, kNext = kRowsumWarps;
+#else
+  constexpr int kFirst = kUnroll, kNext = 1;
+#endif
+  for (long long c0 = warp * kFirst; c0 < chunks; c0 += kRowsumWarps * kUnroll) {
     uint4 lo[kUnroll], hi[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const long long col = (c0 + kRowsumWarps * u) * 32 + t * 8;
-      const bool in_range = c0 + kRowsumWarps * u < chunks;
+      const long long col = (c0 + kNext * u) * 32 + t * 8;
+      const bool in_range = c0 + kNext * u < chunks;
       lo[u] = (lo_ok && in_range) ? __ldg(reinterpret_cast<const uint4*>(in + r_lo * cols + col)) : zero;
       hi[u] = (hi_ok && in_range) ? __ldg(reinterpret_cast<const uint4*>(in + r_hi * cols + col)) : zero;
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      if (c0 + kRowsumWarps * u < chunks) {
-        const long long col = (c0 + kRowsumWarps * u) * 32 + t * 8;
+      if (c0 + kNext * u < chunks) {
+        const long long col = (c0 + kNext * u) * 32 + t * 8;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
           const uint4 b = __ldg(reinterpret_cast<const uint4*>(wt + (long long)(j * 8 + g) * cols + col));
@@ -397,14 +401,33 @@ int rowsum_mma(const __nv_bfloat16* in, const __nv_bfloat16* wt, int rp, long lo
                __nv_bfloat16* out, cudaStream_t s) {
   if (m == 0) return MOLT_OK;
   const unsigned grid = (unsigned)((m + 15) / 16);
-  switch (rp) {
-    case 16: rowsum_mma_kernel<16><<<grid, rowsum_warps(16) * 32, 0, s>>>(in, wt, m, cols, out); break;
-    case 32: rowsum_mma_kernel<32><<<grid, rowsum_warps(32) * 32, 0, s>>>(in, wt, m, cols, out); break;
-    case 48: rowsum_mma_kernel<48><<<grid, rowsum_warps(48) * 32, 0, s>>>(in, wt, m, cols, out); break;
-    case 64: rowsum_mma_kernel<64><<<grid, rowsum_warps(64) * 32, 0, s>>>(in, wt, m, cols, out); break;
-    default: return fail(MOLT_E_CAPABILITY, "rowsum_mma: padded rank %d unsupported", rp);
+  // Warps per CTA of 16 rows.  A warp takes every W-th 32-column chunk, two per trip: with few columns a CTA of 16
+  // warps is over after one or two trips and is all set-up and final sum, so narrow inputs get smaller CTAs (more of
+  // them per SM, more trips each).
+#ifdef MOLT_ROWSUM_W
+  const int want = MOLT_ROWSUM_W;
+#else
+  const int want = cols <= 2048 ? 8 : 16;
+#endif
+  const int cap = rowsum_warps(rp);
+  const int warps = want < cap ? want : cap;
+#ifdef MOLT_ROWSUM_U
+  const bool deep = MOLT_ROWSUM_U == 4;
+#else
+  const bool deep = cols <= 2048;   // four chunks per trip measured faster for narrow inputs, two for wide ones
+#endif
+#define MOLT_ROWSUM_CASE(RP, W)                                                        \
+  if (rp == RP && warps == W) {                                                        \
+    if (deep) rowsum_mma_kernel<RP, W, 4><<<grid, W * 32, 0, s>>>(in, wt, m, cols, out); \
+    else rowsum_mma_kernel<RP, W, 2><<<grid, W * 32, 0, s>>>(in, wt, m, cols, out);    \
+    return launch_status("rowsum_mma_kernel");                                         \
   }
-  return launch_status("rowsum_mma_kernel");
+  MOLT_ROWSUM_CASE(16, 4) MOLT_ROWSUM_CASE(16, 8) MOLT_ROWSUM_CASE(16, 16)
+  MOLT_ROWSUM_CASE(32, 4) MOLT_ROWSUM_CASE(32, 8) MOLT_ROWSUM_CASE(32, 16)
+  MOLT_ROWSUM_CASE(48, 4) MOLT_ROWSUM_CASE(48, 8)
+  MOLT_ROWSUM_CASE(64, 4) MOLT_ROWSUM_CASE(64, 8)
+#undef MOLT_ROWSUM_CASE
+  return fail(MOLT_E_CAPABILITY, "rowsum_mma: padded rank %d unsupported", rp);
 }
 
 int colsum_splits(long long m, long long cols) {
