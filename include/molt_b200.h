@@ -300,6 +300,20 @@ int molt_mlp_bwd(const molt_lora_proj* gate, const molt_lora_proj* up, const mol
                  float* const grads[6], int accumulate, int64_t m, void* workspace, size_t workspace_bytes,
                  uintptr_t stream);
 
+/* The same pair with the block's three low-rank inputs kept between them: t_out / t_saved is one buffer of
+ * [3][m][64] bf16 (T = bf16(in . bf16(A)^T) of gate, up and down, zero padded to 64 columns), 3 * m * 128 bytes.
+ * Given t_saved the backward recomputes none of them, and rebuilds h = silu(gate) * up in the same pass that forms
+ * dgate and dup (after dh = dY . deq(W_down) + ..., which needs no h) instead of a pass of its own in front.  Same
+ * results as molt_mlp_fwd / molt_mlp_bwd bit for bit; NULL gives exactly those.  The reference saves no such tensor
+ * (methods/gated_replay.py:307-323 keeps x, gate and optionally up); it is 384 bytes per token. */
+int molt_mlp_fwd_t(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down, const void* x,
+                   void* gate_out, void* up_out, void* y, void* t_out, int64_t m, void* workspace,
+                   size_t workspace_bytes, uintptr_t stream);
+int molt_mlp_bwd_t(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down, const void* x,
+                   const void* gate_saved, const void* up_saved, const void* t_saved, const void* dy, void* dx,
+                   float* const grads[6], int accumulate, int64_t m, void* workspace, size_t workspace_bytes,
+                   uintptr_t stream);
+
 #ifdef __cplusplus
 }
 #endif

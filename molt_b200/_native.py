@@ -35,7 +35,7 @@ EXPORTS = (
     "molt_add_rmsnorm_bwd", "molt_rope", "molt_adamw_step", "molt_dense_gemm", "molt_nf4_lora_fwd_prepared",
     "molt_nf4_lora_bwd_prepared", "molt_lora_shadow_refresh",
     "molt_dense_gemm_workspace_bytes", "molt_ce_softmax_grad", "molt_mlp_workspace_bytes", "molt_mlp_fwd",
-    "molt_mlp_bwd",
+    "molt_mlp_bwd", "molt_mlp_fwd_t", "molt_mlp_bwd_t",
 )
 
 
@@ -165,6 +165,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.molt_mlp_fwd.argtypes = [proj, proj, proj, vp, vp, vp, vp, i64, vp, sz, up]
     lib.molt_mlp_bwd.restype = i32
     lib.molt_mlp_bwd.argtypes = [proj, proj, proj, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, vp, sz, up]
+    lib.molt_mlp_fwd_t.restype = i32
+    lib.molt_mlp_fwd_t.argtypes = [proj, proj, proj, vp, vp, vp, vp, vp, i64, vp, sz, up]
+    lib.molt_mlp_bwd_t.restype = i32
+    lib.molt_mlp_bwd_t.argtypes = [proj, proj, proj, vp, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, vp, sz, up]
 
 
 def library() -> ctypes.CDLL:

@@ -222,7 +222,10 @@ static int resolved_absmax(const molt_nf4_desc* w, Arena& arena, cudaStream_t s,
 // ---- forward ---------------------------------------------------------------------------------------
 static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lora_a, const float* lora_b,
                          float scaling, int rank, void* y, int64_t m, void* t_out, Arena& arena, int path,
-                         cudaStream_t s, int flags = 0, const molt_lora_shadow* shadow = nullptr) {
+                         cudaStream_t s, int flags = 0, const molt_lora_shadow* shadow = nullptr,
+                         const void* t_in = nullptr) {
+  // t_in: T = bf16(x . bf16(A)^T) [m, 64] kept from an earlier call on the same x (tensor-core path only; the other
+  // paths form it themselves)
   const WeightView view = make_view(w);
   const int rp = padded_rank(rank);
   auto* xb = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -259,8 +262,10 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
     return sm100_skinny_forward(sview, xb, lora_a, lora_b, scaling, rank, yb, (int)m,
                                 reinterpret_cast<__nv_bfloat16*>(t_out), ws, bytes, flags, s);
   }
-  __nv_bfloat16* t = t_out != nullptr ? reinterpret_cast<__nv_bfloat16*>(t_out)
-                                      : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));
+  const bool t_given = t_in != nullptr && path == MOLT_PATH_TCGEN05 && t_out == nullptr;
+  __nv_bfloat16* t = t_given ? const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(t_in))
+                     : t_out != nullptr ? reinterpret_cast<__nv_bfloat16*>(t_out)
+                                        : reinterpret_cast<__nv_bfloat16*>(arena.take((size_t)m * 64 * 2));
   if (path == MOLT_PATH_GENERAL) {
     if (arena.dry) return MOLT_OK;
     MOLT_REQUIRE(arena.fits(), MOLT_E_VALUE, "molt_nf4_lora_fwd: workspace too small");
@@ -285,7 +290,8 @@ static int lora_fwd_impl(const molt_nf4_desc* w, const void* x, const float* lor
   if (int rc = lora_prep(lora_a, lora_b, scaling, rank, rp, w->n, w->k, shadowed ? nullptr : a16, shadowed ? nullptr : bs,
                          nullptr, &view, to_resolve, s))
     return rc;
-  if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t, s)) return rc;
+  if (!t_given)
+    if (int rc = rowsum_mma(xb, a16, rp, m, w->k, t, s)) return rc;
   return sm100_gemm(false, view, absmax, xb, t, bs, rp, yb, m, split, flags, s);
 }
 
@@ -632,8 +638,9 @@ static int check_block(const char* who, const molt_lora_proj* gate, const molt_l
 }
 
 static int mlp_fwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
-                        const void* x, void* gate_out, void* up_out, void* y, int64_t m, Arena& arena,
+                        const void* x, void* gate_out, void* up_out, void* y, void* t_out, int64_t m, Arena& arena,
                         cudaStream_t s) {
+  // t_out: optional [3][m][64] bf16, the low-rank inputs T of gate, up and down, for the backward
   const int64_t inter = gate->w->n;
   void* up_buf = up_out != nullptr ? up_out : arena.take((size_t)m * inter * 2);
   void* hidden = arena.take((size_t)m * inter * 2);
@@ -650,7 +657,9 @@ static int mlp_fwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, co
       if (int rc = molt_swiglu_fwd(gate_out, up_buf, hidden, m * inter, MOLT_DTYPE_BF16, reinterpret_cast<uintptr_t>(s)))
         return rc;
     if (int rc = lora_fwd_impl(projs[i]->w, ins[i], projs[i]->lora_a, projs[i]->lora_b, projs[i]->scaling,
-                               projs[i]->rank, outs[i], m, nullptr, arena, chosen, s, 0, projs[i]->shadow))
+                               projs[i]->rank, outs[i], m,
+                               t_out != nullptr ? reinterpret_cast<unsigned char*>(t_out) + (size_t)i * m * 128 : nullptr,
+                               arena, chosen, s, 0, projs[i]->shadow))
       return rc;
     if (arena.used > high) high = arena.used;
   }
@@ -659,9 +668,16 @@ static int mlp_fwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, co
 }
 
 static int mlp_bwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
-                        const void* x, const void* gate_saved, const void* up_saved, const void* dy, void* dx,
-                        float* const grads[6], int accumulate, int64_t m, Arena& arena, cudaStream_t s) {
+                        const void* x, const void* gate_saved, const void* up_saved, const void* t_saved,
+                        const void* dy, void* dx, float* const grads[6], int accumulate, int64_t m, Arena& arena,
+                        cudaStream_t s) {
+  // t_saved: optional [3][m][64] bf16 from the forward (see mlp_fwd_impl).  With it no low-rank input is recomputed,
+  // and h = silu(gate) * up is rebuilt by the SAME pass that forms dgate and dup (it is only needed for the down
+  // projection's adapter gradients, which can wait until dh exists).
   const int64_t inter = gate->w->n, hidden_width = gate->w->k;
+  auto kept_t = [&](int i) -> const void* {
+    return t_saved != nullptr ? reinterpret_cast<const unsigned char*>(t_saved) + (size_t)i * m * 128 : nullptr;
+  };
   const size_t act = (size_t)m * inter * 2;
   void* up_buf = up_saved != nullptr ? nullptr : arena.take(act);   // replayed `up`, later reused for dup
   void* dup_buf = up_saved != nullptr ? arena.take(act) : up_buf;
@@ -677,35 +693,54 @@ static int mlp_bwd_impl(const molt_lora_proj* gate, const molt_lora_proj* up, co
   if (up_saved == nullptr) {
     if (int rc = pick_path(MOLT_PATH_AUTO, up->w, up->rank, m, true, &chosen)) return rc;
     if (int rc = lora_fwd_impl(up->w, x, up->lora_a, up->lora_b, up->scaling, up->rank, up_buf, m, nullptr, arena,
-                               chosen, s, 0, up->shadow))
+                               chosen, s, 0, up->shadow, kept_t(1)))
       return rc;
     up_val = up_buf;
     if (arena.used > high) high = arena.used;
   }
-  // 2. rebuild h = silu(gate) * up (:373-375)
-  if (!arena.dry)
-    if (int rc = molt_swiglu_fwd(gate_saved, up_val, hidden, m * inter, MOLT_DTYPE_BF16, st)) return rc;
-  // 3. down projection backward (:376-384)
-  arena.used = mark;
-  if (int rc = pick_path(MOLT_PATH_AUTO, down->w, down->rank, m, false, &chosen)) return rc;
-  if (int rc = lora_bwd_impl(down->w, hidden, dy, down->lora_a, down->lora_b, down->scaling, down->rank, dh, grads[4],
-                             grads[5], m, nullptr, accumulate, arena, chosen, s, 0, down->shadow))
-    return rc;
-  if (arena.used > high) high = arena.used;
-  // 4. dup = dh * silu(gate), dgate = silu'(gate) * dh * up (:385-387); dgate overwrites dh
-  if (!arena.dry)
-    if (int rc = molt_swiglu_bwd(dh, gate_saved, up_val, dh, dup_buf, nullptr, m * inter, MOLT_DTYPE_BF16, st)) return rc;
+  if (t_saved == nullptr) {
+    // 2. rebuild h = silu(gate) * up (:373-375)
+    if (!arena.dry)
+      if (int rc = molt_swiglu_fwd(gate_saved, up_val, hidden, m * inter, MOLT_DTYPE_BF16, st)) return rc;
+    // 3. down projection backward (:376-384)
+    arena.used = mark;
+    if (int rc = pick_path(MOLT_PATH_AUTO, down->w, down->rank, m, false, &chosen)) return rc;
+    if (int rc = lora_bwd_impl(down->w, hidden, dy, down->lora_a, down->lora_b, down->scaling, down->rank, dh, grads[4],
+                               grads[5], m, nullptr, accumulate, arena, chosen, s, 0, down->shadow))
+      return rc;
+    if (arena.used > high) high = arena.used;
+    // 4. dup = dh * silu(gate), dgate = silu'(gate) * dh * up (:385-387); dgate overwrites dh
+    if (!arena.dry)
+      if (int rc = molt_swiglu_bwd(dh, gate_saved, up_val, dh, dup_buf, nullptr, m * inter, MOLT_DTYPE_BF16, st)) return rc;
+  } else {
+    // 2'. dh = dY . deq(W_down) + (dY . sB_down) . A_down: needs no h
+    arena.used = mark;
+    if (int rc = pick_path(MOLT_PATH_AUTO, down->w, down->rank, m, false, &chosen)) return rc;
+    if (int rc = lora_bwd_impl(down->w, nullptr, dy, down->lora_a, down->lora_b, down->scaling, down->rank, dh, nullptr,
+                               nullptr, m, nullptr, accumulate, arena, chosen, s, 0, down->shadow))
+      return rc;
+    if (arena.used > high) high = arena.used;
+    // 3'. one pass over dh, gate, up: dgate (over dh), dup and h
+    if (!arena.dry)
+      if (int rc = molt_swiglu_bwd(dh, gate_saved, up_val, dh, dup_buf, hidden, m * inter, MOLT_DTYPE_BF16, st)) return rc;
+    // 4'. the down projection's adapter gradients from h, dY and the kept T
+    arena.used = mark;
+    if (int rc = lora_bwd_impl(down->w, hidden, dy, down->lora_a, down->lora_b, down->scaling, down->rank, nullptr,
+                               grads[4], grads[5], m, kept_t(2), accumulate, arena, chosen, s, 0, down->shadow))
+      return rc;
+    if (arena.used > high) high = arena.used;
+  }
   // 5. gate and up projection backwards, dx = dx_gate + dx_up (:155-186)
   arena.used = mark;
   if (int rc = pick_path(MOLT_PATH_AUTO, gate->w, gate->rank, m, false, &chosen)) return rc;
   if (int rc = lora_bwd_impl(gate->w, x, dh, gate->lora_a, gate->lora_b, gate->scaling, gate->rank, dx, grads[0],
-                             grads[1], m, nullptr, accumulate, arena, chosen, s, 0, gate->shadow))
+                             grads[1], m, kept_t(0), accumulate, arena, chosen, s, 0, gate->shadow))
     return rc;
   if (arena.used > high) high = arena.used;
   arena.used = mark;
   if (int rc = pick_path(MOLT_PATH_AUTO, up->w, up->rank, m, false, &chosen)) return rc;
   if (int rc = lora_bwd_impl(up->w, x, dup_buf, up->lora_a, up->lora_b, up->scaling, up->rank, dx_up, grads[2],
-                             grads[3], m, nullptr, accumulate, arena, chosen, s, 0, up->shadow))
+                             grads[3], m, kept_t(1), accumulate, arena, chosen, s, 0, up->shadow))
     return rc;
   if (arena.used > high) high = arena.used;
   arena.used = high;
@@ -722,38 +757,53 @@ extern "C" size_t molt_mlp_workspace_bytes(int op, const molt_lora_proj* gate, c
   float* fake_grads[6];
   for (int i = 0; i < 6; ++i) fake_grads[i] = reinterpret_cast<float*>(fake);
   int rc = MOLT_E_VALUE;
-  if (op == MOLT_OP_MLP_FWD) rc = mlp_fwd_impl(gate, up, down, fake, fake, up_given ? fake : nullptr, fake, m, arena, 0);
+  if (op == MOLT_OP_MLP_FWD) rc = mlp_fwd_impl(gate, up, down, fake, fake, up_given ? fake : nullptr, fake, nullptr, m, arena, 0);
   else if (op == MOLT_OP_MLP_BWD)
-    rc = mlp_bwd_impl(gate, up, down, fake, fake, up_given ? fake : nullptr, fake, fake, fake_grads, 0, m, arena, 0);
+    rc = mlp_bwd_impl(gate, up, down, fake, fake, up_given ? fake : nullptr, nullptr, fake, fake, fake_grads, 0, m, arena, 0);
   return rc == MOLT_OK ? arena.used + 256 : 0;
+}
+
+extern "C" int molt_mlp_fwd_t(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
+                              const void* x, void* gate_out, void* up_out, void* y, void* t_out, int64_t m,
+                              void* workspace, size_t workspace_bytes, uintptr_t stream) {
+  if (int rc = check_block("molt_mlp_fwd", gate, up, down)) return rc;
+  MOLT_REQUIRE(m >= 0, MOLT_E_VALUE, "molt_mlp_fwd: negative token count");
+  MOLT_REQUIRE(x && gate_out && y && workspace, MOLT_E_VALUE, "molt_mlp_fwd: NULL tensor pointer");
+  MOLT_REQUIRE(aligned16(x) && aligned16(gate_out) && aligned16(y) && (up_out == nullptr || aligned16(up_out)) &&
+                   (t_out == nullptr || aligned16(t_out)),
+               MOLT_E_VALUE, "molt_mlp_fwd: tensors must be 16-byte aligned");
+  if (m == 0) return MOLT_OK;
+  Arena arena(workspace, workspace_bytes);
+  return mlp_fwd_impl(gate, up, down, x, gate_out, up_out, y, t_out, m, arena, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int molt_mlp_fwd(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
                             const void* x, void* gate_out, void* up_out, void* y, int64_t m, void* workspace,
                             size_t workspace_bytes, uintptr_t stream) {
-  if (int rc = check_block("molt_mlp_fwd", gate, up, down)) return rc;
-  MOLT_REQUIRE(m >= 0, MOLT_E_VALUE, "molt_mlp_fwd: negative token count");
-  MOLT_REQUIRE(x && gate_out && y && workspace, MOLT_E_VALUE, "molt_mlp_fwd: NULL tensor pointer");
-  MOLT_REQUIRE(aligned16(x) && aligned16(gate_out) && aligned16(y) && (up_out == nullptr || aligned16(up_out)),
-               MOLT_E_VALUE, "molt_mlp_fwd: tensors must be 16-byte aligned");
+  return molt_mlp_fwd_t(gate, up, down, x, gate_out, up_out, y, nullptr, m, workspace, workspace_bytes, stream);
+}
+
+extern "C" int molt_mlp_bwd_t(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
+                              const void* x, const void* gate_saved, const void* up_saved, const void* t_saved,
+                              const void* dy, void* dx, float* const grads[6], int accumulate, int64_t m,
+                              void* workspace, size_t workspace_bytes, uintptr_t stream) {
+  if (int rc = check_block("molt_mlp_bwd", gate, up, down)) return rc;
+  MOLT_REQUIRE(m >= 0, MOLT_E_VALUE, "molt_mlp_bwd: negative token count");
+  MOLT_REQUIRE(x && gate_saved && dy && dx && grads && workspace, MOLT_E_VALUE, "molt_mlp_bwd: NULL tensor pointer");
+  for (int i = 0; i < 6; ++i) MOLT_REQUIRE(grads[i] != nullptr, MOLT_E_VALUE, "molt_mlp_bwd: NULL gradient pointer");
+  MOLT_REQUIRE(aligned16(x) && aligned16(gate_saved) && aligned16(dy) && aligned16(dx) &&
+                   (up_saved == nullptr || aligned16(up_saved)) && (t_saved == nullptr || aligned16(t_saved)),
+               MOLT_E_VALUE, "molt_mlp_bwd: tensors must be 16-byte aligned");
   if (m == 0) return MOLT_OK;
   Arena arena(workspace, workspace_bytes);
-  return mlp_fwd_impl(gate, up, down, x, gate_out, up_out, y, m, arena, reinterpret_cast<cudaStream_t>(stream));
+  return mlp_bwd_impl(gate, up, down, x, gate_saved, up_saved, t_saved, dy, dx, grads, accumulate, m, arena,
+                      reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int molt_mlp_bwd(const molt_lora_proj* gate, const molt_lora_proj* up, const molt_lora_proj* down,
                             const void* x, const void* gate_saved, const void* up_saved, const void* dy, void* dx,
                             float* const grads[6], int accumulate, int64_t m, void* workspace, size_t workspace_bytes,
                             uintptr_t stream) {
-  if (int rc = check_block("molt_mlp_bwd", gate, up, down)) return rc;
-  MOLT_REQUIRE(m >= 0, MOLT_E_VALUE, "molt_mlp_bwd: negative token count");
-  MOLT_REQUIRE(x && gate_saved && dy && dx && grads && workspace, MOLT_E_VALUE, "molt_mlp_bwd: NULL tensor pointer");
-  for (int i = 0; i < 6; ++i) MOLT_REQUIRE(grads[i] != nullptr, MOLT_E_VALUE, "molt_mlp_bwd: NULL gradient pointer");
-  MOLT_REQUIRE(aligned16(x) && aligned16(gate_saved) && aligned16(dy) && aligned16(dx) &&
-                   (up_saved == nullptr || aligned16(up_saved)),
-               MOLT_E_VALUE, "molt_mlp_bwd: tensors must be 16-byte aligned");
-  if (m == 0) return MOLT_OK;
-  Arena arena(workspace, workspace_bytes);
-  return mlp_bwd_impl(gate, up, down, x, gate_saved, up_saved, dy, dx, grads, accumulate, m, arena,
-                      reinterpret_cast<cudaStream_t>(stream));
+  return molt_mlp_bwd_t(gate, up, down, x, gate_saved, up_saved, nullptr, dy, dx, grads, accumulate, m, workspace,
+                        workspace_bytes, stream);
 }

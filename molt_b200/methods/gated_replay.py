@@ -207,13 +207,17 @@ class _GatedMLPNF4LoRA(torch.autograd.Function):
         keep_up = not bool(rematerialize_up)
         up_out = torch.empty((m, inter), dtype=torch.bfloat16, device=device) if keep_up else None
         y = torch.empty((m, int(descs[2].n)), dtype=torch.bfloat16, device=device)
+        # the three low-rank inputs (x A^T of gate and up, h A^T of down; 384 bytes per token) are kept for the backward,
+        # which then recomputes none of them
+        needs_backward = any(ctx.needs_input_grad)
+        low_rank = torch.empty((3, m, 64), dtype=torch.bfloat16, device=device) if needs_backward else None
         if m:
             nbytes = lib.molt_mlp_workspace_bytes(_native.OP_MLP_FWD, projs[0], projs[1], projs[2], m, int(keep_up))
             ws = _native.workspace(nbytes, device)
             with torch.cuda.device(device):
-                _native.check(lib.molt_mlp_fwd(projs[0], projs[1], projs[2], x2.data_ptr(), gate_out.data_ptr(),
-                                               _native.ptr(up_out), y.data_ptr(), m, ws.data_ptr(), ws.numel(),
-                                               _native.stream_handle(device)))
+                _native.check(lib.molt_mlp_fwd_t(projs[0], projs[1], projs[2], x2.data_ptr(), gate_out.data_ptr(),
+                                                 _native.ptr(up_out), y.data_ptr(), _native.ptr(low_rank), m, ws.data_ptr(),
+                                                 ws.numel(), _native.stream_handle(device)))
         ctx.descs = descs
         ctx.states = (gate_state, up_state, down_state)
         ctx.scalings = scalings
@@ -228,6 +232,9 @@ class _GatedMLPNF4LoRA(torch.autograd.Function):
             saved.append(norm_weight)
         if keep_up:
             saved.append(up_out)
+        ctx.keep_low_rank = low_rank is not None
+        if low_rank is not None:
+            saved.append(low_rank)
         ctx.save_for_backward(*saved)
         return y.reshape(*x.shape[:-1], y.shape[-1])
 
@@ -244,6 +251,7 @@ class _GatedMLPNF4LoRA(torch.autograd.Function):
         else:
             x2 = kept_input
         up_saved = rest.pop(0) if ctx.keep_up else None
+        low_rank = rest.pop(0) if ctx.keep_low_rank else None
         dy2 = _as_rows(grad_output)
         if dy2.dtype != torch.bfloat16:
             dy2 = dy2.to(torch.bfloat16)
@@ -264,10 +272,10 @@ class _GatedMLPNF4LoRA(torch.autograd.Function):
                                                   int(up_saved is not None))
             ws = _native.workspace(nbytes, device)
             with torch.cuda.device(device):
-                _native.check(lib.molt_mlp_bwd(projs[0], projs[1], projs[2], x2.data_ptr(), gate_out.data_ptr(),
-                                               _native.ptr(up_saved), dy2.data_ptr(), dx.data_ptr(), pointers,
-                                               int(use_slots), m, ws.data_ptr(), ws.numel(),
-                                               _native.stream_handle(device)))
+                _native.check(lib.molt_mlp_bwd_t(projs[0], projs[1], projs[2], x2.data_ptr(), gate_out.data_ptr(),
+                                                 _native.ptr(up_saved), _native.ptr(low_rank), dy2.data_ptr(),
+                                                 dx.data_ptr(), pointers, int(use_slots), m, ws.data_ptr(), ws.numel(),
+                                                 _native.stream_handle(device)))
         elif not use_slots:
             for g in grads:
                 g.zero_()

@@ -221,3 +221,60 @@ def test_grad_arena_receives_kernel_gradients_in_place(native_library):
         assert oracle.rel_frobenius(grad, 2 * ref[key]) <= TOL, key
     arena.zero()
     assert float(arena.flat.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("m", [5, 40, 200, 700])
+@pytest.mark.parametrize("keep_up", [False, True])
+def test_block_with_kept_low_rank_inputs_equals_the_plain_block(native_library, m, keep_up):
+    """molt_mlp_fwd_t / molt_mlp_bwd_t (low-rank inputs kept, h rebuilt by the backward's own SwiGLU pass) against
+    molt_mlp_fwd / molt_mlp_bwd: same kernels on the same operands in another order, so every output agrees bit for bit,
+    on whatever path the token count selects."""
+    import ctypes
+
+    from molt_b200 import _native
+    from molt_b200.methods._linear import weight_desc_for_tokens
+    from molt_b200.methods.gated_replay import _proj_struct
+
+    hidden, inter, rank = 128, 320, 16
+    mlp, _ = _mlp(hidden, inter, rank=rank, seed=41)
+    lins = (mlp.gate_proj, mlp.up_proj, mlp.down_proj)
+    descs = [weight_desc_for_tokens(l.base_layer.weight.data, l.base_layer.weight.quant_state, m) for l in lins]
+    adapters = [(l.lora_A["default"].weight.detach().contiguous(), l.lora_B["default"].weight.detach().contiguous()) for l in lins]
+    projs = [_proj_struct(descs[i], adapters[i][0], adapters[i][1], 2.0) for i in range(3)]
+    lib = native_library
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(m, hidden, device="cuda", generator=gen).bfloat16()
+    dy = torch.randn(m, hidden, device="cuda", generator=gen).bfloat16()
+    stream = _native.stream_handle(x.device)
+    results = []
+    for kept in (False, True):
+        gate = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16)
+        up = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16) if keep_up else None
+        y = torch.empty(m, hidden, device="cuda", dtype=torch.bfloat16)
+        dx = torch.empty(m, hidden, device="cuda", dtype=torch.bfloat16)
+        low = torch.zeros(3, m, 64, device="cuda", dtype=torch.bfloat16) if kept else None
+        grads = [torch.zeros_like(t, dtype=torch.float32) for pair in adapters for t in pair]
+        pointers = (ctypes.c_void_p * 6)(*[g.data_ptr() for g in grads])
+        nbytes = max(lib.molt_mlp_workspace_bytes(op, projs[0], projs[1], projs[2], m, int(keep_up))
+                     for op in (_native.OP_MLP_FWD, _native.OP_MLP_BWD))
+        ws = torch.empty(nbytes, device="cuda", dtype=torch.uint8)
+        if kept:
+            _native.check(lib.molt_mlp_fwd_t(projs[0], projs[1], projs[2], x.data_ptr(), gate.data_ptr(), _native.ptr(up),
+                                             y.data_ptr(), low.data_ptr(), m, ws.data_ptr(), nbytes, stream))
+            _native.check(lib.molt_mlp_bwd_t(projs[0], projs[1], projs[2], x.data_ptr(), gate.data_ptr(), _native.ptr(up),
+                                             low.data_ptr(), dy.data_ptr(), dx.data_ptr(), pointers, 0, m, ws.data_ptr(),
+                                             nbytes, stream))
+        else:
+            _native.check(lib.molt_mlp_fwd(projs[0], projs[1], projs[2], x.data_ptr(), gate.data_ptr(), _native.ptr(up),
+                                           y.data_ptr(), m, ws.data_ptr(), nbytes, stream))
+            _native.check(lib.molt_mlp_bwd(projs[0], projs[1], projs[2], x.data_ptr(), gate.data_ptr(), _native.ptr(up),
+                                           dy.data_ptr(), dx.data_ptr(), pointers, 0, m, ws.data_ptr(), nbytes, stream))
+        torch.cuda.synchronize()
+        results.append((y, dx, gate, *grads, low))
+    for index, (plain, kept) in enumerate(zip(results[0][:-1], results[1][:-1])):
+        assert torch.equal(plain, kept), index
+    low = results[1][-1]
+    assert torch.equal(low[0][:, :rank], (x.float() @ adapters[0][0].bfloat16().float().t()).bfloat16()) or \
+        oracle.rel_frobenius(low[0][:, :rank], x.float().cpu() @ adapters[0][0].bfloat16().float().cpu().t()) <= TOL
+    assert not low[:, :, rank:].any()
+    assert_clean_status()
