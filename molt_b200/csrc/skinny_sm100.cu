@@ -507,8 +507,10 @@ __global__ void __maxnreg__(64) skinny_lowrank_kernel(const __nv_bfloat16* __res
 
 // y[tok, row] = bf16(sum of the parts of the row's tile, in CTA order, + sum_j bf16(s B[row, j]) bf16(T[tok, j])),
 // T = sum of its K slices, rounded to bf16.  Grid (row tiles, groups of 16 tokens); a block has one thread per (row,
-// group of kTok tokens), i.e. 128 * 16 / kTok threads: the kernel is a chain of dependent round trips to memory with
-// little arithmetic, so it wants many warps per SM rather than long threads.  The blocks of tile 0 also write T
+// group of kTok tokens), i.e. 128 * 16 / kTok threads.  The kernel is nothing but round trips to memory with a little
+// arithmetic behind them, so everything it reads is asked for up front and together: the slices of T, the tile's
+// adapter rows (contiguous in memory: read coalesced and staged in shared memory, rounded once) and the parts of the
+// tile (addresses of up to four parts are formed before any of them is read).  The blocks of tile 0 also write T
 // (bf16, [m, 64], zero padded) when the caller wants it.
 template <int kTok>
 __global__ void __launch_bounds__(BR * 16 / kTok) skinny_finish_kernel(const float* __restrict__ partial, int nt, int max_parts,
@@ -518,7 +520,9 @@ __global__ void __launch_bounds__(BR * 16 / kTok) skinny_finish_kernel(const flo
                                                                       int rank, long long n, __nv_bfloat16* __restrict__ y,
                                                                       __nv_bfloat16* __restrict__ t_out) {
   constexpr int kThreadsF = BR * 16 / kTok;
+  constexpr int kPartsAtOnce = 4;
   __shared__ float t_s[16][64];
+  __shared__ float b_s[BR][64 + 1];   // bf16(s B) of the tile's rows, as fp32 (row pitch 65: no bank conflicts by row)
   const int tile = blockIdx.x;
   const int r = threadIdx.x & (BR - 1);
   const int tok0 = blockIdx.y * 16, tokq = tok0 + (threadIdx.x / BR) * kTok;   // first token of the block / of this thread
@@ -529,26 +533,64 @@ __global__ void __launch_bounds__(BR * 16 / kTok) skinny_finish_kernel(const flo
   const long long unit0 = (long long)tile * nb, unit1 = unit0 + nb;
   const int first = (int)(((unit0 + 1) * ranges.ctas - 1) / units);
   const int last = (int)((unit1 * ranges.ctas - 1) / units);
+
+  // ---- requests: the first parts of the tile ----
+  float acc[kTok];
+#pragma unroll
+  for (int t = 0; t < kTok; ++t) acc[t] = 0.f;
+  float got[kPartsAtOnce][kTok];
+  auto request_parts = [&](int c0) {
+#pragma unroll
+    for (int q = 0; q < kPartsAtOnce; ++q) {
+      const int c = c0 + q;
+      const bool live = row_ok && c <= last;
+      const int slot = live ? tile - range_begin(ranges, c) / nb : 0;
+      const float* src = partial + ((size_t)(live ? c : 0) * max_parts + slot) * (size_t)(nt * BR) + r;
+#pragma unroll
+      for (int t = 0; t < kTok; ++t) got[q][t] = (live && tokq + t < m) ? __ldcg(src + (size_t)(tokq + t) * BR) : 0.f;
+    }
+  };
+  request_parts(first);
+  // ---- requests: T's slices and the tile's adapter rows, then into shared memory ----
   for (int i = threadIdx.x; i < 16 * rank; i += kThreadsF) {
     const int t = i / rank, j = i - t * rank;
     float total = 0.f;
     if (tok0 + t < m) {
+      float slice[kLowrankSlices];
 #pragma unroll
-      for (int ks = 0; ks < kLowrankSlices; ++ks) total += __ldcg(low_part + ((size_t)ks * m_pad + tok0 + t) * 64 + j);
+      for (int ks = 0; ks < kLowrankSlices; ++ks) slice[ks] = __ldcg(low_part + ((size_t)ks * m_pad + tok0 + t) * 64 + j);
+#pragma unroll
+      for (int ks = 0; ks < kLowrankSlices; ++ks) total += slice[ks];
     }
     t_s[t][j] = __bfloat162float(__float2bfloat16_rn(total));
   }
-  float acc[kTok];
-#pragma unroll
-  for (int t = 0; t < kTok; ++t) acc[t] = 0.f;
-  if (row_ok) {
-    for (int c = first; c <= last; ++c) {
-      const int slot = tile - range_begin(ranges, c) / nb;
-      const float* src = partial + ((size_t)c * max_parts + slot) * (size_t)(nt * BR) + r;
-#pragma unroll
-      for (int t = 0; t < kTok; ++t)
-        if (tokq + t < m) acc[t] += __ldcg(src + (size_t)(tokq + t) * BR);
+  {
+    const long long rows_here = n - (long long)tile * BR < BR ? n - (long long)tile * BR : BR;
+    const float* b0 = lora_b + (long long)tile * BR * rank;        // rows_here * rank contiguous floats
+    const int count = (int)rows_here * rank;
+    if ((rank & 3) == 0 && (reinterpret_cast<uintptr_t>(b0) & 15) == 0) {
+      for (int i = threadIdx.x * 4; i < count; i += kThreadsF * 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(b0 + i));
+        const int br = i / rank, bj = i - br * rank;                 // four consecutive columns of one row
+        b_s[br][bj] = __bfloat162float(__float2bfloat16_rn(scaling * v.x));
+        b_s[br][bj + 1] = __bfloat162float(__float2bfloat16_rn(scaling * v.y));
+        b_s[br][bj + 2] = __bfloat162float(__float2bfloat16_rn(scaling * v.z));
+        b_s[br][bj + 3] = __bfloat162float(__float2bfloat16_rn(scaling * v.w));
+      }
+    } else {
+      for (int i = threadIdx.x; i < count; i += kThreadsF) {
+        const int br = i / rank, bj = i - br * rank;
+        b_s[br][bj] = __bfloat162float(__float2bfloat16_rn(scaling * __ldg(b0 + i)));
+      }
     }
+  }
+  // ---- the parts, in CTA order ----
+  for (int c0 = first; c0 <= last; c0 += kPartsAtOnce) {
+    if (c0 != first) request_parts(c0);
+#pragma unroll
+    for (int q = 0; q < kPartsAtOnce; ++q)
+#pragma unroll
+      for (int t = 0; t < kTok; ++t) acc[t] += got[q][t];          // absent parts and tokens were read as zero
   }
   __syncthreads();
   if (t_out != nullptr && tile == 0) {   // T itself, zero padded to 64 columns
@@ -562,8 +604,7 @@ __global__ void __launch_bounds__(BR * 16 / kTok) skinny_finish_kernel(const flo
   for (int j0 = 0; j0 < rank; j0 += 16) {
     float b[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
-      b[j] = j0 + j < rank ? __bfloat162float(__float2bfloat16_rn(scaling * __ldg(lora_b + row * rank + j0 + j))) : 0.f;
+    for (int j = 0; j < 16; ++j) b[j] = j0 + j < rank ? b_s[r][j0 + j] : 0.f;
 #pragma unroll
     for (int t = 0; t < kTok; ++t) {
       float sum = 0.f;
@@ -575,6 +616,134 @@ __global__ void __launch_bounds__(BR * 16 / kTok) skinny_finish_kernel(const flo
 #pragma unroll
   for (int t = 0; t < kTok; ++t)
     if (tokq + t < m) y[(size_t)(tokq + t) * n + row] = __float2bfloat16_rn(acc[t]);
+}
+
+// The same for more than 16 tokens, with a thread owning four neighbouring rows and four tokens (a warp = the tile's
+// 128 rows x four tokens; block = four warps = the 16 tokens of its group): a part is read with one 16-byte load per
+// lane and token (512 contiguous bytes per warp), an output row segment is written 8 bytes per lane, and a value of T
+// read from shared memory serves four rows.  Sums are formed in the same order as in the kernel above.
+__global__ void __launch_bounds__(BR) skinny_finish_quad_kernel(const float* __restrict__ partial, int nt, int max_parts,
+                                                                Ranges ranges, int nb, long long units,
+                                                                const float* __restrict__ low_part, int m, int m_pad,
+                                                                const float* __restrict__ lora_b, float scaling, int rank,
+                                                                long long n, __nv_bfloat16* __restrict__ y,
+                                                                __nv_bfloat16* __restrict__ t_out) {
+  constexpr int kThreadsF = BR;
+  constexpr int kPartsAtOnce = 4;
+  __shared__ __align__(16) float t_s[16][64];
+  __shared__ __align__(16) float b_t[64][BR];   // bf16(s B) of the tile's rows, as fp32, transposed: [column][row]
+  const int tile = blockIdx.x;
+  const int rq = threadIdx.x & 31, tq = threadIdx.x >> 5;
+  const int tok0 = blockIdx.y * 16, tokq = tok0 + tq * 4;
+  const long long row = (long long)tile * BR + rq * 4;              // first of this thread's four rows
+  const bool row_ok = row < n;                                      // n is a multiple of 64: a quad is all in or all out
+  const long long unit0 = (long long)tile * nb, unit1 = unit0 + nb;
+  const int first = (int)(((unit0 + 1) * ranges.ctas - 1) / units);
+  const int last = (int)((unit1 * ranges.ctas - 1) / units);
+
+  float acc[4][4];   // [token][row]
+#pragma unroll
+  for (int t = 0; t < 4; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+  float4 got[kPartsAtOnce][4];
+  auto request_parts = [&](int c0) {
+#pragma unroll
+    for (int q = 0; q < kPartsAtOnce; ++q) {
+      const int c = c0 + q;
+      const bool live = row_ok && c <= last;
+      const int slot = live ? tile - range_begin(ranges, c) / nb : 0;
+      const float* src = partial + ((size_t)(live ? c : 0) * max_parts + slot) * (size_t)(nt * BR) + rq * 4;
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        got[q][t] = (live && tokq + t < m) ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(tokq + t) * BR))
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  request_parts(first);
+  for (int i = threadIdx.x; i < 16 * rank; i += kThreadsF) {
+    const int t = i / rank, j = i - t * rank;
+    float total = 0.f;
+    if (tok0 + t < m) {
+      float slice[kLowrankSlices];
+#pragma unroll
+      for (int ks = 0; ks < kLowrankSlices; ++ks) slice[ks] = __ldcg(low_part + ((size_t)ks * m_pad + tok0 + t) * 64 + j);
+#pragma unroll
+      for (int ks = 0; ks < kLowrankSlices; ++ks) total += slice[ks];
+    }
+    t_s[t][j] = __bfloat162float(__float2bfloat16_rn(total));
+  }
+  {
+    const long long rows_here = n - (long long)tile * BR < BR ? n - (long long)tile * BR : BR;
+    const float* b0 = lora_b + (long long)tile * BR * rank;        // rows_here * rank contiguous floats
+    const int count = (int)rows_here * rank;
+    if ((rank & 3) == 0 && (reinterpret_cast<uintptr_t>(b0) & 15) == 0) {
+      for (int i = threadIdx.x * 4; i < count; i += kThreadsF * 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(b0 + i));
+        const int br = i / rank, bj = i - br * rank;
+        b_t[bj][br] = __bfloat162float(__float2bfloat16_rn(scaling * v.x));
+        b_t[bj + 1][br] = __bfloat162float(__float2bfloat16_rn(scaling * v.y));
+        b_t[bj + 2][br] = __bfloat162float(__float2bfloat16_rn(scaling * v.z));
+        b_t[bj + 3][br] = __bfloat162float(__float2bfloat16_rn(scaling * v.w));
+      }
+    } else {
+      for (int i = threadIdx.x; i < count; i += kThreadsF) {
+        const int br = i / rank, bj = i - br * rank;
+        b_t[bj][br] = __bfloat162float(__float2bfloat16_rn(scaling * __ldg(b0 + i)));
+      }
+    }
+  }
+  for (int c0 = first; c0 <= last; c0 += kPartsAtOnce) {
+    if (c0 != first) request_parts(c0);
+#pragma unroll
+    for (int q = 0; q < kPartsAtOnce; ++q)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        acc[t][0] += got[q][t].x; acc[t][1] += got[q][t].y; acc[t][2] += got[q][t].z; acc[t][3] += got[q][t].w;
+      }
+  }
+  __syncthreads();
+  if (t_out != nullptr && tile == 0) {   // T itself, zero padded to 64 columns
+    for (int i = threadIdx.x; i < 16 * 64; i += kThreadsF) {
+      const int t = i >> 6, j = i & 63;
+      if (tok0 + t < m) t_out[(size_t)(tok0 + t) * 64 + j] = __float2bfloat16_rn(j < rank ? t_s[t][j] : 0.f);
+    }
+  }
+  if (!row_ok || tokq >= m) return;
+  for (int j0 = 0; j0 < rank; j0 += 16) {
+    float sum[4][4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sum[t][i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j0 + j < rank) {   // (uniform) columns past the rank add nothing, as multiplying by zero would
+        float tv[4];
+        const float4 b4 = *reinterpret_cast<const float4*>(&b_t[j0 + j][rq * 4]);   // this thread's four rows
+        const float b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) tv[t] = t_s[tq * 4 + t][j0 + j];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sum[t][i] = fmaf(b[i], tv[t], sum[t][i]);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[t][i] += sum[t][i];
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t)
+    if (tokq + t < m) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc[t][0], acc[t][1]), hi = __floats2bfloat162_rn(acc[t][2], acc[t][3]);
+      uint2 out;
+      out.x = *reinterpret_cast<uint32_t*>(&lo);
+      out.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(y + (size_t)(tokq + t) * n + row) = out;
+    }
 }
 
 struct Plan {
@@ -717,18 +886,25 @@ int sm100_skinny_forward(const WeightView& w, const __nv_bfloat16* x, const floa
     if (int rc = launch_status("skinny_lowrank_kernel")) return rc;
   }
 
-  // an ordinary launch: placing its blocks early, as a programmatic dependent, was measured to be slower
-  // few tokens: few blocks, so short threads and many warps per block; more tokens: the grid fills the machine anyway
-  // and long threads do less redundant work (adapter row, range arithmetic)
+  // an ordinary launch: placing its blocks early, as a programmatic dependent, was measured to be slower.
+  // Up to 16 tokens: one thread per row and four tokens (512 threads per tile).  More tokens: four rows x four tokens
+  // per thread (16-byte loads and 8-byte stores; 6.0 us against 10.4 us at 64 tokens for one row x sixteen tokens).
   const dim3 fgrid((unsigned)p.tiles, (unsigned)((m + 15) / 16));
   if (m <= 16)
     skinny_finish_kernel<4><<<fgrid, BR * 4, 0, s>>>(partial, pl.nt, pl.max_parts, pl.ranges, p.num_kb,
                                                       (long long)p.tiles * p.num_kb, low_part, m, pl.m_pad, lora_b,
                                                       scaling, rank, w.n, y, t_out);
+#ifdef MOLT_SKINNY_EXP_FINISH_ROWS   // comparison build: a thread owns one row and sixteen tokens
   else
     skinny_finish_kernel<16><<<fgrid, BR, 0, s>>>(partial, pl.nt, pl.max_parts, pl.ranges, p.num_kb,
                                                    (long long)p.tiles * p.num_kb, low_part, m, pl.m_pad, lora_b, scaling,
                                                    rank, w.n, y, t_out);
+#else
+  else
+    skinny_finish_quad_kernel<<<fgrid, BR, 0, s>>>(partial, pl.nt, pl.max_parts, pl.ranges, p.num_kb,
+                                                    (long long)p.tiles * p.num_kb, low_part, m, pl.m_pad, lora_b, scaling,
+                                                    rank, w.n, y, t_out);
+#endif
   return launch_status("skinny_finish_kernel");
 }
 
