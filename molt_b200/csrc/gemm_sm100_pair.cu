@@ -796,7 +796,9 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
         fence_proxy_async();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 0) {
+#ifndef MOLT_PAIR_EXP_NO_STORE   // (timing experiment: the result never leaves the SM)
           if (row0 < p.m) tma_store_2d(&map_out, stage_addr, tn * BN + cg * 64, row0);
+#endif
           tma_store_commit();
         }
         if (kStoreBufs == 2) store_buf ^= 1;
