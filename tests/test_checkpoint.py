@@ -117,3 +117,16 @@ def test_bnb_import_refuses_what_the_path_does_not_cover():
     low_first = QuantState(absmax=state.absmax, shape=state.shape, nibble_order="low-first")
     with pytest.raises(CapabilityError):
         export_bnb_nf4_weight(name, q.packed, low_first)
+
+
+def test_static_microbatch_runner_needs_cuda():
+    """Without a GPU the captured micro-batch runner refuses to be built (reference training/static_cuda_graph.py:156-157)."""
+    from molt_b200.training import StaticCudaMicrobatch, TensorSignature
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    p = torch.nn.Parameter(torch.ones(2))
+    with pytest.raises(CapabilityError):
+        StaticCudaMicrobatch(lambda x: (x * p).sum(), (torch.ones(2),), [p])
+    sig = TensorSignature.of(torch.zeros(3, 4, dtype=torch.bfloat16))
+    assert sig.shape == (3, 4) and sig.dtype == torch.bfloat16 and sig == TensorSignature((3, 4), torch.bfloat16, torch.device("cpu"))
