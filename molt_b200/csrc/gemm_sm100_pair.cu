@@ -117,6 +117,7 @@ struct Params {
   int ext_steps;         // rp / 16, 0 = no low-rank block
   int tiles_m, tiles_n;  // pair tiles: 256 tokens x 256 columns
   int full_tiles;        // tiles on the static schedule (whole waves); the tiles after them are split along the contraction
+  int tail_pairs;        // pairs that share the split tiles (>= 1)
   float* split_partial;  // [pairs][2 parts][2 CTAs][128 rows][256 columns] fp32 partial accumulators of the split tiles
   int nibble_high_first;
   long long wait_cycles; // limit of every bounded wait, in SM clock cycles
@@ -211,6 +212,7 @@ struct WorkPlan {
   int num_pairs, pair_id, blocks;   // blocks per tile, the low-rank block included
   int full_tiles, num_tiles;
   int tail_units;                   // blocks of all split tiles (at most pairs x blocks: fits easily)
+  int tail_pairs;                   // the first tail_pairs pairs share them (every part costs a partial tile of traffic)
   int tail_begin, tail_end;         // this pair's range of them
 };
 struct WorkItem {
@@ -219,7 +221,8 @@ struct WorkItem {
   bool valid;
 };
 __host__ __device__ __forceinline__ int tail_range_begin(const WorkPlan& w, int pair) {
-  return w.tail_units * pair / w.num_pairs;   // at most pairs^2 x blocks < 2^31 (the host checks)
+  const int q = pair < w.tail_pairs ? pair : w.tail_pairs;
+  return w.tail_units * q / w.tail_pairs;   // at most pairs^2 x blocks < 2^31 (the host checks)
 }
 __device__ __forceinline__ void tail_item(const WorkPlan& w, WorkItem& it) {
   if (it.u >= w.tail_end) {
@@ -314,6 +317,7 @@ nf4_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap map_in, const __g
     plan_s.full_tiles = p.full_tiles;
     plan_s.num_tiles = p.tiles_m * p.tiles_n;
     plan_s.tail_units = (plan_s.num_tiles - p.full_tiles) * plan_s.blocks;
+    plan_s.tail_pairs = p.tail_pairs;
     plan_s.tail_begin = tail_range_begin(plan_s, plan_s.pair_id);
     plan_s.tail_end = tail_range_begin(plan_s, plan_s.pair_id + 1);
     for (int s = 0; s < kLoadStages; ++s) mbar_init(bar_ldfull(s), 1);
@@ -839,11 +843,11 @@ __global__ void __launch_bounds__(256) split_fixup_kernel(const float* __restric
   if (row >= m || col >= out_cols) return;
   const int sub = r / (2 * BM), cta = (r % (2 * BM)) / BM, local = r % BM;
   const int unit0 = tail_tile * plan.blocks, unit1 = unit0 + plan.blocks;
-  int first = (int)(((long long)unit0 * plan.num_pairs) / plan.tail_units);   // the pair whose range holds unit0
-  while (first + 1 < plan.num_pairs && tail_range_begin(plan, first + 1) <= unit0) ++first;
+  int first = (int)(((long long)unit0 * plan.tail_pairs) / plan.tail_units);   // the pair whose range holds unit0
+  while (first + 1 < plan.tail_pairs && tail_range_begin(plan, first + 1) <= unit0) ++first;
   while (first > 0 && tail_range_begin(plan, first) > unit0) --first;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int c = first; c < plan.num_pairs && tail_range_begin(plan, c) < unit1; ++c) {
+  for (int c = first; c < plan.tail_pairs && tail_range_begin(plan, c) < unit1; ++c) {
     const int start = tail_range_begin(plan, c) > unit0 ? tail_range_begin(plan, c) : unit0;
     const float* src = partial + split_slot_offset(c, start == unit0 ? 1 : 0, sub, cta, subs) + (size_t)local * BN + cgroup * 8;
     const float4 lo = __ldcg(reinterpret_cast<const float4*>(src)), hi = __ldcg(reinterpret_cast<const float4*>(src + 4));
@@ -1065,9 +1069,25 @@ int run_pair_gemm(bool backward, bool dense, pair::Params& p, const CUtensorMap&
   // Whole waves run the static schedule; the tiles of a split last wave leave the kernel as fp32 partial tiles.
   p.full_tiles = (int)tiles;
   p.split_partial = nullptr;
+  p.tail_pairs = (int)pairs;
   if (split) {
     p.full_tiles = (int)(tiles - tiles % pairs);
     p.split_partial = reinterpret_cast<float*>(split_ws);
+#ifndef MOLT_PAIR_EXP_ALL_TAIL_PAIRS
+    // How many pairs share the split tiles: every part of a tile is written and read back as a whole fp32 tile
+    // (512 KB tall, 256 KB short: about 0.19 / 0.10 us of HBM time), so a few blocks more per pair can be cheaper than
+    // a part more.  A pair's range may span at most two tiles, hence at least `rem` pairs.
+    const long long rem = tiles % pairs, units = rem * blocks;
+    const double block_us = subs == 2 ? 0.80 : 0.58, part_us = subs == 2 ? 0.19 : 0.10;
+    double best_us = -1.0;
+    for (long long tp = rem; tp <= pairs; ++tp) {
+      const double us = (double)((units + tp - 1) / tp) * block_us + (double)(tp + rem) * part_us;
+      if (best_us < 0.0 || us < best_us) {
+        best_us = us;
+        p.tail_pairs = (int)tp;
+      }
+    }
+#endif
   }
   const int grid = (int)pairs * 2;
   constexpr int BS = kBStagesDefault, SB = 1, GR = kDecodeGroupsDefault;
@@ -1126,6 +1146,7 @@ int run_pair_gemm(bool backward, bool dense, pair::Params& p, const CUtensorMap&
     plan.full_tiles = p.full_tiles;
     plan.num_tiles = (int)tiles;
     plan.tail_units = (int)(tiles - p.full_tiles) * plan.blocks;
+    plan.tail_pairs = p.tail_pairs;
     plan.tail_begin = plan.tail_end = 0;
     dim3 fgrid((unsigned)(2 * BM * subs * (BN / 8) / 256), (unsigned)(tiles - p.full_tiles));
     split_fixup_kernel<<<fgrid, 256, 0, s>>>(p.split_partial, plan, p.tiles_m, p.tiles_n, subs, m, out_cols, out);
